@@ -1,0 +1,141 @@
+// C ABI of libtileccl_b200.so.  Python binds it with ctypes
+// (tileccl_b200/_native.py); any other host language can do the same.
+// Every function returns 0 on success and a non-zero code on failure, in which
+// case tccl_last_error() describes what went wrong (thread-local string).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCCL_MAX_RANKS 8
+
+const char* tccl_last_error(void);
+const char* tccl_version(void);
+
+// --------------------------------------------------------------------------
+// Device / topology query (csrc/runtime/device.cc)
+// --------------------------------------------------------------------------
+typedef struct TcclDeviceProps {
+  char name[128];
+  int32_t ordinal;
+  int32_t cc_major, cc_minor;
+  int32_t sm_count;
+  int32_t warp_size;
+  int32_t max_smem_per_block_optin;
+  int32_t l2_bytes;
+  int32_t clock_khz, mem_clock_khz, mem_bus_bits;
+  int32_t vmm_supported;
+  int32_t posix_fd_handles;
+  int32_t fabric_handles;
+  int32_t multicast_supported;
+  int64_t total_mem;
+} TcclDeviceProps;
+
+int tccl_device_count(int32_t* count);
+int tccl_device_props(int32_t ordinal, TcclDeviceProps* out);
+// access[i * n + j] = 1 when device i can map device j's memory; atomics likewise.
+int tccl_peer_matrix(int32_t n, int32_t* access, int32_t* native_atomics);
+
+// --------------------------------------------------------------------------
+// Symmetric heap over cuMem VMM (csrc/runtime/symm_heap.cc)
+// --------------------------------------------------------------------------
+typedef struct TcclHeapInfo {
+  uint64_t window_base;   // address of rank 0's heap in this process
+  uint64_t stride;        // bytes between ranks (granularity-rounded heap size)
+  uint64_t mc_base;       // multicast alias of this rank's heap offsets, 0 = none
+  uint64_t requested_size;
+  uint64_t granularity;
+  int32_t rank, world_size;
+  int32_t device;
+  int32_t mode;           // 0 local_only, 1 single_process, 2 multiprocess
+  int32_t transport;      // 0 none, 1 vmm_single_process, 2 vmm_fd, 3 vmm_fabric
+  int32_t nvls_bound;
+} TcclHeapInfo;
+
+// One process maps every rank (rank r lives on device devices[r]); returns one
+// handle per rank that share the same window.
+int tccl_heap_create_local(int32_t world_size, uint64_t size, const int32_t* devices,
+                           int32_t want_nvls, void** handles_out);
+// One process per rank.  Collective: every rank calls it with the same job id;
+// allocation handles travel as file descriptors over abstract Unix sockets.
+int tccl_heap_create_multiprocess(int32_t rank, int32_t world_size, uint64_t size, int32_t device,
+                                  const char* job_id, int32_t want_nvls, int32_t timeout_ms,
+                                  void** handle_out);
+int tccl_heap_info(void* handle, TcclHeapInfo* out);
+int tccl_heap_destroy(void* handle);
+
+// 256-byte aligned bump allocation inside the heap (never freed individually).
+int tccl_heap_alloc(void* handle, uint64_t bytes, uint64_t* offset_out);
+int tccl_heap_reset(void* handle);
+int tccl_heap_bytes_allocated(void* handle, uint64_t* out);
+
+// Rendezvous layer on its own (host only): all-gathers one (payload, fd) per rank
+// over abstract Unix sockets.  fds_out[r] is a descriptor valid in the caller.
+int tccl_bootstrap_allgather(int32_t rank, int32_t world_size, const char* job_id,
+                             int32_t timeout_ms, uint64_t payload, int32_t fd,
+                             uint64_t* payloads_out, int32_t* fds_out);
+
+// --------------------------------------------------------------------------
+// Fused tcgen05 GEMM family (csrc/kernels/gemm_sm100.cu)
+// --------------------------------------------------------------------------
+typedef struct TcclGemmDesc {
+  int32_t mode;        // 0 gemm, 1 push-all, 2 reduce-scatter, 3 all-scatter
+  int32_t dtype;       // 0 fp16, 1 bf16 (inputs and outputs; accumulation is fp32)
+  int32_t b_kmajor;    // 0: B is [K, N] row-major; 1: B is [N, K] row-major
+  int32_t epi_op;      // 0 none, 1 SiLU-gate
+  int32_t push_mode;   // 0 st.global, 1 TMA store, 2 multimem.st
+  int32_t rank, world_size;
+  int32_t split_axis;  // reduce-scatter: 0 = owners split rows of C, 1 = columns
+  int64_t a_rows;      // rows of A that may be read
+  int64_t b_cols;      // columns of B that may be read
+  int64_t k;
+  uint64_t a_ptr; int64_t lda;   // leading dimensions in elements
+  uint64_t b_ptr; int64_t ldb;
+  int64_t sub_m, sub_n;          // accumulator extent of one owner's sub-problem
+  uint64_t out_ptr[TCCL_MAX_RANKS];
+  uint64_t out_mc_ptr;
+  int64_t ldo;                   // elements
+  int64_t out_rows, out_cols;    // extent of one destination sub-matrix
+  int64_t out_slot_elems;        // elements between slots (reduce-scatter staging), else 0
+  int32_t out_slots;             // >= 1
+  int32_t group_m_tiles;
+  uint64_t sig_local; int64_t heap_stride; int32_t sig_stride;
+  int32_t rot_m_tiles;
+  uint64_t stage_local;
+  uint64_t a_gate; int32_t a_gate_rows_per_rank;
+  int32_t scatter_col_begin, scatter_col_end;
+  int32_t grid;                  // 0 = one CTA per SM
+  uint64_t status;               // uint32[8] in device memory, may be 0
+  uint64_t trace;                // uint64[tiles] in device memory, may be 0
+  uint64_t wait_budget_ns;       // 0 = default (2 s)
+} TcclGemmDesc;
+
+typedef struct TcclGemmPlanInfo {
+  int32_t grid;
+  int32_t tiles_total;       // tiles in this rank's order
+  int32_t tiles_per_owner;
+  int32_t m_tiles_local, n_tiles_local;
+  int32_t groups;            // TileGroups per owner sub-problem
+  int32_t k_blocks;
+  int32_t smem_bytes;
+} TcclGemmPlanInfo;
+
+int tccl_gemm_plan_create(const TcclGemmDesc* desc, void** plan_out);
+int tccl_gemm_plan_info(void* plan, TcclGemmPlanInfo* out);
+// epoch: 1, 2, 3 ... per launch on the plan's signal block (ignored by mode 0).
+// tile_end < 0 runs to the last tile.
+int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, int32_t tile_begin,
+                          int32_t tile_end, int32_t wait_incoming, uint64_t stream);
+int tccl_gemm_plan_destroy(void* plan);
+
+// Consumer side of the TileGroup protocol as its own launch: waits until
+// sig[src * sig_stride + g] >= targets[g] for every src != skip_src.
+int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src, int32_t n_groups,
+                     uint64_t targets, int32_t skip_src, uint64_t status, uint64_t budget_ns,
+                     int32_t rank, uint64_t stream);
+
+#ifdef __cplusplus
+}
+#endif

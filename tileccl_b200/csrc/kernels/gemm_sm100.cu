@@ -1,0 +1,511 @@
+// Persistent warp-specialised tcgen05 GEMM for sm_100a, with the collective
+// that follows it fused into the epilogue.
+//
+// One CTA per SM.  Roles:
+//   warp 0      TMA producer: A / B tiles -> 4-stage shared-memory ring (local memory only)
+//   warp 1      MMA issuer:   tcgen05.mma (128 x 256 x 16, fp32 accumulators in TMEM)
+//   warp 2      TMEM allocator / deallocator
+//   warp 3      incoming-TileGroup waiter (push-all mode)
+//   warps 4..7  epilogue: tcgen05.ld -> (reduce | SiLU-gate) -> cast -> swizzled staging in
+//               shared memory -> TMA store to the local destination and, per mode, stores
+//               to peer GPUs' memory, followed by a release-add on the peers' TileGroup
+//               counters.
+//
+// What replaces what in the reference: the plain mode is its persistent GEMM
+// (tileccl/kernels/gemm.py:52-167); push-all is the GEMM-output all-gather
+// (tileccl/ops.py:1700-1790, a host loop of torch.mm + tile all-gather there);
+// reduce-scatter is tileccl/ops.py:1793-1896; all-scatter is the wg_specialized
+// pattern (tileccl/patterns/wg_specialized.py:210-352) with the communication role
+// played by the epilogue warps instead of dedicated SMs.
+//
+// Peer traffic is stores only (plain st.global, TMA store, or multimem.st);
+// operands are always TMA-loaded from this GPU's own memory, without multicast.
+#include "gemm_sm100.cuh"
+
+#include "../device/ptx.cuh"
+#include "../device/tile_compute.cuh"
+#include "../device/tile_sync.cuh"
+
+namespace tileccl {
+
+namespace {
+
+struct TileCoord {
+  int a_row0, b_col0;   // operand coordinates
+  int out_x, out_y;     // destination-local coordinates (elements)
+  int owner;            // reduce-scatter: rank that owns the tile; else this rank
+  int lm;               // tile row inside the owner's sub-problem (TileGroup = lm / group_m_tiles)
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const FusedGemmParams& p, int t) {
+  TileCoord c;
+  const int tpo = p.m_tiles_local * p.n_tiles_local;
+  int oi = 0, rem = t;
+  if (p.owners > 1) {
+    oi = t / tpo;
+    rem = t - oi * tpo;
+  }
+  int lm = rem / p.n_tiles_local;
+  const int ln = rem - lm * p.n_tiles_local;
+  if (p.owners == 1 && p.rot_m_tiles != 0) {
+    lm += p.rot_m_tiles;
+    if (lm >= p.m_tiles_local) lm -= p.m_tiles_local;
+  }
+  c.owner = p.owners > 1 ? (p.rank + 1 + oi) % p.world_size : p.rank;
+  c.lm = lm;
+  c.a_row0 = lm * kBM;
+  c.b_col0 = ln * kBN;
+  if (p.owners > 1) {
+    if (p.split_axis == 0) c.a_row0 += c.owner * p.a_rows_per_owner;
+    else c.b_col0 += c.owner * p.b_cols_per_owner;
+  }
+  c.out_y = lm * kBM;
+  c.out_x = p.epi_op == kEpiSiluGate ? ln * (kBN / 2) : ln * kBN;
+  return c;
+}
+
+__device__ __forceinline__ uint32_t* peer_counter(const FusedGemmParams& p, int dest_rank,
+                                                  int src_slot, int group) {
+  int64_t a = static_cast<int64_t>(p.sig_local) +
+              static_cast<int64_t>(dest_rank - p.rank) * p.heap_stride;
+  return reinterpret_cast<uint32_t*>(a) + src_slot * p.sig_stride + group;
+}
+
+// m-tiles in TileGroup g of a sub-problem with `m_tiles` tile rows.
+__device__ __forceinline__ int group_m_count(const FusedGemmParams& p, int g) {
+  int left = p.m_tiles_local - g * p.group_m_tiles;
+  return left < p.group_m_tiles ? left : p.group_m_tiles;
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, int x, int y, int z,
+                                             uint32_t smem_src) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::
+          "l"(reinterpret_cast<uint64_t>(m)),
+      "r"(x), "r"(y), "r"(z), "r"(smem_src)
+      : "memory");
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzled tiles need 1024-byte aligned bases.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_epi = smem_base + kSmemPipe;
+  const uint32_t smem_ctl = smem_epi + kSmemEpi;
+  uint8_t* ctl_generic = smem_raw + (smem_ctl - smem_u32(smem_raw));
+
+  const uint32_t bar_full = smem_ctl;                         // kStages x 8 B
+  const uint32_t bar_empty = bar_full + 8 * kStages;          // kStages x 8 B
+  const uint32_t bar_acc_full = bar_empty + 8 * kStages;      // kAccBufs x 8 B
+  const uint32_t bar_acc_empty = bar_acc_full + 8 * kAccBufs; // kAccBufs x 8 B
+  const uint32_t bar_drain = bar_acc_empty + 8 * kAccBufs;    // 8 B
+  const uint32_t tmem_slot = bar_drain + 8;                   // 4 B
+  volatile uint32_t* tmem_slot_g =
+      reinterpret_cast<volatile uint32_t*>(ctl_generic + (tmem_slot - smem_ctl));
+  volatile uint32_t* abort_flag = tmem_slot_g + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < kAccBufs; ++a) {
+      mbar_init(bar_acc_full + 8 * a, 1);
+      mbar_init(bar_acc_empty + 8 * a, kEpiWarps);
+    }
+    mbar_init(bar_drain, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, kAccBufs * kBN);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot_g;
+
+  WaitBudget wb;
+  wb.start(p.wait_budget_ns, abort_flag);
+
+  const int first = p.tile_begin + static_cast<int>(blockIdx.x);
+  const int step = static_cast<int>(gridDim.x);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one_sync()) {
+      tma_prefetch_desc(&p.tma_a);
+      tma_prefetch_desc(&p.tma_b);
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = first; ok && t < p.tile_end; t += step) {
+        const TileCoord c = decode_tile(p, t);
+        if (p.a_gate != 0) {
+          // Rows of A written by a peer: wait for that peer's arrival counter.
+          int src = c.a_row0 / p.a_gate_rows_per_rank;
+          if (src != p.rank) {
+            uint32_t seen = 0;
+            if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.a_gate) + src, p.a_gate_target,
+                              wb, &seen)) {
+              report_status(status, kStatusTimeoutSignal, 10, p.a_gate_target, seen, p.rank, t);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+          }
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wb)) {
+            report_status(status, kStatusTimeoutMbarrier, 11, 0, 0, p.rank, t);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kStageABytes;
+          const uint32_t bar = bar_full + 8 * stage;
+          mbar_expect_tx(bar, kStageBytes);
+          tma_load_2d(sa, &p.tma_a, kb * kBK, c.a_row0, bar);
+          if (p.b_kmajor) {
+            tma_load_2d(sb, &p.tma_b, kb * kBK, c.b_col0, bar);
+          } else {
+#pragma unroll
+            for (int i = 0; i < kBN / 64; ++i)
+              tma_load_2d(sb + i * (64 * kBK * 2), &p.tma_b, c.b_col0 + i * 64, kb * kBK, bar);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // Let loads that are still in flight land before the CTA retires.
+        for (int s = 0; s < kStages; ++s)
+          for (int it = 0; it < 100000 && !mbar_try_wait(bar_full + 8 * s, 0) &&
+                           !mbar_try_wait(bar_full + 8 * s, 1); ++it) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (elect_one_sync()) {
+      const uint32_t idesc = umma_idesc_f16(p.is_bf16, 0, p.b_kmajor ? 0 : 1, kBM, kBN);
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = first; ok && t < p.tile_end; t += step) {
+        if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, wb)) {
+          report_status(status, kStatusTimeoutMbarrier, 20, 0, 0, p.rank, t);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, wb)) {
+            report_status(status, kStatusTimeoutMbarrier, 21, 0, 0, p.rank, t);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kStageABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            const uint64_t da = umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
+            const uint64_t db =
+                p.b_kmajor ? umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024)
+                           : umma_smem_desc_sw128(sb + k * (kUmmaK * 128), 64 * kBK * 2, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
+        if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+      }
+      if (!ok) {
+        // Outstanding MMAs must finish before TMEM is released.
+        umma_commit(bar_drain);
+        for (int it = 0; it < 1000000 && !mbar_try_wait(bar_drain, 0); ++it) {}
+      }
+    }
+  } else if (warp == 3) {
+    // ---------------------- incoming TileGroup waiter -------------------------
+    if (p.mode == kModePushAll && p.wait_incoming && p.world_size > 1) {
+      const int groups = (p.m_tiles_local + p.group_m_tiles - 1) / p.group_m_tiles;
+      const int total = p.world_size * groups;
+      const uint32_t* sig = reinterpret_cast<const uint32_t*>(p.sig_local);
+      for (int i = blockIdx.x * 32 + lane; i < total; i += gridDim.x * 32) {
+        const int src = i / groups, g = i - src * groups;
+        if (src == p.rank) continue;
+        const uint32_t target =
+            p.epoch * static_cast<uint32_t>(group_m_count(p, g) * p.n_tiles_local * kEpiWarps);
+        uint32_t seen = 0;
+        if (!tile_wait_ge(sig + src * p.sig_stride + g, target, wb, &seen)) {
+          report_status(status, kStatusTimeoutSignal, 30, target, seen, p.rank, i);
+          break;
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    // -------------------------------- epilogue --------------------------------
+    const int q = warp - 4;                       // TMEM lane quarter and 32-row slab
+    const bool bf16 = p.is_bf16 != 0;
+    const uint32_t my_epi = smem_epi + q * (kEpiBufs * kEpiBufBytes);
+    uint8_t* my_epi_g = smem_raw + (my_epi - smem_u32(smem_raw));
+    const int n_chunks = p.epi_op == kEpiSiluGate ? (kBN / 2) / kChunkN : kBN / kChunkN;
+    uint32_t acc = 0, acc_phase = 0;
+    uint32_t buf = 0;
+    bool ok = true;
+    for (int t = first; ok && t < p.tile_end; t += step) {
+      const TileCoord c = decode_tile(p, t);
+      const int group = c.lm / p.group_m_tiles;
+      const bool reduce_here = p.mode == kModeReduceScatter && c.owner == p.rank;
+      const int row = c.out_y + q * kSlabM + lane;   // destination-local row of this thread
+
+      if (reduce_here && p.world_size > 1) {
+        // All peers' partial tiles of this TileGroup must have landed in local staging.
+        const uint32_t target =
+            p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
+                                            p.n_tiles_local * kEpiWarps);
+        uint32_t seen = 0;
+        bool got = true;
+        if (lane == 0)
+          got = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
+                             &seen);
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        if (!got) {
+          if (lane == 0) {
+            report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
+            *abort_flag = 1;
+          }
+          ok = false;
+          break;
+        }
+      }
+
+      if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, wb)) {
+        if (lane == 0) report_status(status, kStatusTimeoutMbarrier, 41, 0, 0, p.rank, t);
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      const uint32_t t_acc = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
+
+      for (int ch = 0; ch < n_chunks; ++ch) {
+        float v[kChunkN];
+        {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_acc + ch * kChunkN, r0);
+          tmem_ld_32x32b_x32(t_acc + ch * kChunkN + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v[i] = __uint_as_float(r0[i]);
+            v[32 + i] = __uint_as_float(r1[i]);
+          }
+        }
+        if (p.epi_op == kEpiSiluGate) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32b_x32(t_acc + kBN / 2 + ch * kChunkN, r0);
+          tmem_ld_32x32b_x32(t_acc + kBN / 2 + ch * kChunkN + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v[i] = apply_elementwise(kOpSilu, v[i]) * __uint_as_float(r0[i]);
+            v[32 + i] = apply_elementwise(kOpSilu, v[32 + i]) * __uint_as_float(r1[i]);
+          }
+        }
+        if (ch == n_chunks - 1) {
+          // Every TMEM read of this accumulator is done: hand it back to the MMA warp.
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        }
+
+        const int col0 = c.out_x + ch * kChunkN;     // destination-local column of v[0]
+        if (reduce_here && p.world_size > 1 && row < p.out_rows) {
+          // Add the other ranks' partials (16-bit, written into this rank's staging).
+          for (int src = 0; src < p.world_size; ++src) {
+            if (src == p.rank) continue;
+            const char* base = reinterpret_cast<const char*>(p.stage_local) +
+                               static_cast<int64_t>(p.stage_parity * p.world_size + src) *
+                                   p.out_slot_bytes +
+                               static_cast<int64_t>(row) * p.out_cols * 2 +
+                               static_cast<int64_t>(col0) * 2;
+#pragma unroll
+            for (int j = 0; j < kChunkN / 8; ++j) {
+              if (col0 + j * 8 < p.out_cols) {
+                uint4 w = ld_remote_v4(base + j * 16);
+                tile_accumulate_16x8(bf16, &v[j * 8], w);
+              }
+            }
+          }
+        }
+
+        // Staging buffer `buf` was last read by the stores committed two chunks ago.
+        if (lane == 0) tma_store_wait_read<kEpiBufs - 1>();
+        __syncwarp();
+        const uint32_t sbuf = my_epi + buf * kEpiBufBytes;
+#pragma unroll
+        for (int j = 0; j < kChunkN / 8; ++j) {
+          const uint4 w = tile_cast_f32x8(bf16, &v[j * 8]);
+          const uint32_t addr = sbuf + lane * 128 + ((j ^ (lane & 7)) << 4);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w.x), "r"(w.y),
+                       "r"(w.z), "r"(w.w)
+                       : "memory");
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+
+        const int y = c.out_y + q * kSlabM;
+        bool push_all = p.mode == kModePushAll;
+        if (p.mode == kModeAllScatter)
+          push_all = col0 >= p.scatter_col_begin && col0 < p.scatter_col_end;
+
+        if (p.mode == kModeReduceScatter && !reduce_here) {
+          // Partial tile -> owner's staging slot for (parity, this rank).
+          const int z = p.stage_parity * p.world_size + p.rank;
+          if (p.push_mode == kPushTma) {
+            if (lane == 0) tma_store_3d(&p.tma_out[c.owner], col0, y, z, sbuf);
+          } else {
+            char* dst = reinterpret_cast<char*>(p.out_ptr[c.owner]) +
+                        static_cast<int64_t>(z) * p.out_slot_bytes;
+            const uint8_t* sg = my_epi_g + buf * kEpiBufBytes;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int idx = lane + 32 * i, r = idx >> 3, j = idx & 7;
+              if (y + r < p.out_rows && col0 + j * 8 < p.out_cols) {
+                const uint4 w = *reinterpret_cast<const uint4*>(sg + r * 128 + ((j ^ (r & 7)) << 4));
+                st_remote_v4(dst + static_cast<int64_t>(y + r) * p.out_ld_bytes +
+                                 static_cast<int64_t>(col0 + j * 8) * 2, w);
+              }
+            }
+          }
+        } else {
+          // Local destination (plain GEMM, own all-gather rows, reduced tile).
+          const int local_slot = p.mode == kModeGemm ? 0 : p.rank;
+          if (lane == 0) tma_store_3d(&p.tma_out[local_slot], col0, y, 0, sbuf);
+          if (push_all && p.world_size > 1) {
+            if (p.push_mode == kPushTma) {
+              if (lane == 0)
+                for (int d = 1; d < p.world_size; ++d)
+                  tma_store_3d(&p.tma_out[(p.rank + d) % p.world_size], col0, y, 0, sbuf);
+            } else {
+              const uint8_t* sg = my_epi_g + buf * kEpiBufBytes;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int idx = lane + 32 * i, r = idx >> 3, j = idx & 7;
+                if (y + r < p.out_rows && col0 + j * 8 < p.out_cols) {
+                  const uint4 w =
+                      *reinterpret_cast<const uint4*>(sg + r * 128 + ((j ^ (r & 7)) << 4));
+                  const int64_t off = static_cast<int64_t>(y + r) * p.out_ld_bytes +
+                                      static_cast<int64_t>(col0 + j * 8) * 2;
+                  if (p.push_mode == kPushMultimem) {
+                    multimem_st_v4(reinterpret_cast<char*>(p.out_mc_ptr) + off, w);
+                  } else {
+                    for (int d = 1; d < p.world_size; ++d)
+                      st_remote_v4(
+                          reinterpret_cast<char*>(p.out_ptr[(p.rank + d) % p.world_size]) + off, w);
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (lane == 0) tma_store_commit();
+        buf ^= 1u;
+      }
+
+      // ---- TileGroup signalling: this slab of this tile is now on its way ----
+      const bool signals = p.world_size > 1 && p.sig_local != 0 &&
+                           (p.mode == kModePushAll || p.mode == kModeAllScatter ||
+                            (p.mode == kModeReduceScatter && !reduce_here));
+      if (signals) {
+        if (lane == 0) tma_store_wait_all<0>();   // bulk stores of this thread are complete
+        fence_proxy_async_all();
+        fence_acq_rel_sys();                      // every lane's peer stores are ordered first
+        __syncwarp();
+        if (lane == 0) {
+          if (p.mode == kModeReduceScatter) {
+            red_release_sys_add(peer_counter(p, c.owner, 0, group), 1u);
+          } else {
+            for (int d = 1; d < p.world_size; ++d)
+              red_release_sys_add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, group), 1u);
+          }
+        }
+      }
+      if (p.trace != 0 && q == 0 && lane == 0)
+        reinterpret_cast<uint64_t*>(p.trace)[t] = globaltimer_ns();
+
+      if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
+    }
+    if (lane == 0) tma_store_wait_all<0>();
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kAccBufs * kBN);
+  }
+}
+
+// Waits (bounded) until counters reach their targets: the consumer side of the
+// TileGroup protocol when it runs as its own launch.  counter i = (src, g) with
+// src-major layout; targets[g] is per group; entries of `skip_src` are ignored.
+__global__ void wait_groups_kernel(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
+                                   const uint32_t* targets, int skip_src, uint32_t* status,
+                                   uint64_t budget_ns, int rank) {
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  WaitBudget wb;
+  wb.start(budget_ns, &abort_word);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_src * n_groups;
+       i += gridDim.x * blockDim.x) {
+    const int src = i / n_groups, g = i - src * n_groups;
+    if (src == skip_src) continue;
+    uint32_t seen = 0;
+    if (!tile_wait_ge(sig + src * sig_stride + g, targets[g], wb, &seen)) {
+      report_status(status, kStatusTimeoutSignal, 50, targets[g], seen, rank, i);
+      abort_word = 1;
+      return;
+    }
+  }
+}
+
+cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream) {
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 64 && !attr_set[dev]) {
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemTotal);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  fused_gemm_sm100_kernel<<<grid, kThreads, kSmemTotal, stream>>>(p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
+                               const uint32_t* targets, int skip_src, uint32_t* status,
+                               uint64_t budget_ns, int rank, cudaStream_t stream) {
+  int total = n_src * n_groups;
+  int threads = 128;
+  int blocks = (total + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  wait_groups_kernel<<<blocks, threads, 0, stream>>>(sig, sig_stride, n_src, n_groups, targets,
+                                                     skip_src, status, budget_ns, rank);
+  return cudaGetLastError();
+}
+
+}  // namespace tileccl

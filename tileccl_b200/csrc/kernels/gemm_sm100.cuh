@@ -1,0 +1,91 @@
+// Parameter block and constants shared by the fused tcgen05 GEMM kernel family
+// (kernels/gemm_sm100.cu) and its host-side plan builder (gemm_plan.cc).
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace tileccl {
+
+// CTA tile and pipeline shape.
+static constexpr int kBM = 128;       // rows of C per tile (= UMMA M, one TMEM lane per row)
+static constexpr int kBN = 256;       // columns of C per tile (= UMMA N, fp32 TMEM columns)
+static constexpr int kBK = 64;        // K elements per stage (64 x 2 B = one 128-byte swizzle row)
+static constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
+static constexpr int kStages = 4;     // TMA -> MMA ring depth
+static constexpr int kAccBufs = 2;    // TMEM accumulator double buffer (2 x 256 columns)
+static constexpr int kEpiWarps = 4;   // epilogue warps (one per 32-lane TMEM quarter)
+static constexpr int kThreads = 256;  // warp 0 TMA, 1 MMA, 2 TMEM alloc, 3 waiter, 4-7 epilogue
+static constexpr int kChunkN = 64;    // epilogue column chunk (64 x 2 B = 128 B)
+static constexpr int kSlabM = 32;     // rows per epilogue warp
+
+static constexpr int kStageABytes = kBM * kBK * 2;
+static constexpr int kStageBBytes = kBN * kBK * 2;
+static constexpr int kStageBytes = kStageABytes + kStageBBytes;
+static constexpr int kEpiBufBytes = kSlabM * kChunkN * 2;  // 4 KiB per (warp, buffer)
+static constexpr int kEpiBufs = 2;
+static constexpr int kSmemPipe = kStages * kStageBytes;
+static constexpr int kSmemEpi = kEpiWarps * kEpiBufs * kEpiBufBytes;
+static constexpr int kSmemCtl = 256;
+static constexpr int kSmemTotal = kSmemPipe + kSmemEpi + kSmemCtl + 1024;  // + alignment slack
+
+static constexpr int kMaxRanks = 8;
+
+enum GemmMode : int {
+  kModeGemm = 0,       // out[0] = A @ B
+  kModePushAll = 1,    // every tile is stored to out[d] for all d (all-gather of the product)
+  kModeReduceScatter = 2,  // tile goes to its owner's staging slot; owner tiles are reduced
+  kModeAllScatter = 3,  // tile stored locally; tiles inside this rank's column slice go to all
+};
+enum PushMode : int {
+  kPushStores = 0,  // peer copies with 16-byte st.global from the staged tile
+  kPushTma = 1,     // peer copies with one TMA store per destination
+  kPushMultimem = 2,  // one multimem.st per 16 bytes reaches every rank (needs NVLS)
+};
+enum EpilogueOp : int {
+  kEpiNone = 0,
+  kEpiSiluGate = 1,  // out[:, j] = silu(acc[:, j]) * acc[:, 128 + j] per 256-column tile
+};
+
+struct alignas(64) FusedGemmParams {
+  CUtensorMap tma_a;                  // A as [rows, K], box {64, 128}, 128B swizzle
+  CUtensorMap tma_b;                  // B as [N, K] box {64, 256} or [K, N] box {64, 64}
+  CUtensorMap tma_out[kMaxRanks];     // 3-D {cols, rows, slots}, box {64, 32, 1}
+  // raw views of the same destinations for the non-TMA push modes
+  uint64_t out_ptr[kMaxRanks];
+  uint64_t out_mc_ptr;                // multicast alias of the destination (push mode 2)
+  int64_t out_ld_bytes;
+  int64_t out_slot_bytes;             // bytes between staging slots (z coordinate)
+  int32_t out_rows, out_cols;         // extent of one destination sub-matrix
+  // problem
+  int32_t mode, push_mode, epi_op, is_bf16, b_kmajor;
+  int32_t rank, world_size;
+  int32_t k_blocks;
+  int32_t m_tiles_local, n_tiles_local;   // tiles of one owner's sub-problem
+  int32_t owners;                          // 1, or world_size for reduce-scatter
+  int32_t split_axis;                      // reduce-scatter: 0 = owners split rows, 1 = columns
+  int32_t a_rows_per_owner, b_cols_per_owner;
+  int32_t tile_begin, tile_end;            // half-open range of the rank's tile order to run
+  int32_t rot_m_tiles;                     // plain GEMM: first m-tile to visit (others follow, wrapping)
+  // TileGroup signalling (counters only ever grow)
+  uint64_t sig_local;                 // this rank's counter array (uint32[sig_srcs][sig_stride])
+  int64_t heap_stride;                // bytes between ranks' heaps: peer copy = sig_local + (d - rank) * stride
+  int32_t sig_stride;                 // counters per source rank
+  int32_t group_m_tiles;              // tile rows per TileGroup
+  uint32_t epoch;                     // 1, 2, 3 ... per launch on this signal block
+  int32_t wait_incoming;              // push-all: also wait for every peer's groups before exit
+  // reduce-scatter staging on this rank: [2 parities][world_size][out_rows][out_cols]
+  uint64_t stage_local;
+  int32_t stage_parity;
+  // A-operand gating (all-gather feeding this GEMM): uint32[world_size] arrival counters
+  uint64_t a_gate;
+  uint32_t a_gate_target;
+  int32_t a_gate_rows_per_rank;
+  // column slice pushed by all-scatter
+  int32_t scatter_col_begin, scatter_col_end;
+  // diagnostics
+  uint64_t status;                    // uint32[kStatusWords]
+  uint64_t wait_budget_ns;
+  uint64_t trace;                     // optional uint64[3 * tiles]: start / ready / done timestamps
+};
+
+}  // namespace tileccl

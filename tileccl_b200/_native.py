@@ -139,7 +139,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_gemm_plan_info": [vp, C.POINTER(GemmPlanInfo)],
         "tccl_gemm_plan_launch": [vp, u32, u32, i32, i32, i32, u64],
         "tccl_gemm_plan_destroy": [vp],
-        "tccl_wait_groups": [u64, i32, i32, i32, u64, i32, u64, u64, i32, u64],
+        "tccl_wait_groups": [u64, i32, i32, i32, u64, u32, i32, u64, u64, i32, u64],
         "tccl_device_count": [C.POINTER(i32)],
         "tccl_device_props": [i32, C.POINTER(DeviceProps)],
         "tccl_peer_matrix": [i32, C.POINTER(i32), C.POINTER(i32)],
@@ -150,6 +150,8 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_heap_alloc": [vp, u64, C.POINTER(u64)],
         "tccl_heap_reset": [vp],
         "tccl_heap_bytes_allocated": [vp, C.POINTER(u64)],
+        "tccl_collective_launch": [i32, i32, i32, i32, i32, i32, i32, u32, u64, u64, u64, u64, u64,
+                                   u64, C.c_int64, u64, i32, u64, u64, u64],
         "tccl_bootstrap_allgather": [i32, i32, C.c_char_p, i32, u64, i32, C.POINTER(u64),
                                      C.POINTER(i32)],
     }

@@ -131,10 +131,23 @@ int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, in
 int tccl_gemm_plan_destroy(void* plan);
 
 // Consumer side of the TileGroup protocol as its own launch: waits until
-// sig[src * sig_stride + g] >= targets[g] for every src != skip_src.
+// sig[src * sig_stride + g] >= per_epoch[g] * epoch for every src != skip_src.
 int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src, int32_t n_groups,
-                     uint64_t targets, int32_t skip_src, uint64_t status, uint64_t budget_ns,
-                     int32_t rank, uint64_t stream);
+                     uint64_t per_epoch, uint32_t epoch, int32_t skip_src, uint64_t status,
+                     uint64_t budget_ns, int32_t rank, uint64_t stream);
+
+// --------------------------------------------------------------------------
+// Tile collectives on heap buffers (csrc/kernels/collectives.cu)
+// op: 0 all-gather, 1 reduce-scatter, 2 all-reduce (two-shot), 3 all-reduce (one-shot),
+//     4 broadcast, 5 scatter.  dtype: 0 fp16, 1 bf16, 2 fp32, 3 raw bytes (copy ops only).
+// phase_mask: bit 0 announce, bit 1 move data, bit 2 wait for completion (7 = whole call).
+// --------------------------------------------------------------------------
+int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
+                           int32_t root, int32_t use_multimem, int32_t phase_mask, uint32_t epoch,
+                           uint64_t src, uint64_t dst, uint64_t staging, uint64_t counters,
+                           uint64_t mc_base, uint64_t heap_base, int64_t heap_stride,
+                           uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
+                           uint64_t stream);
 
 #ifdef __cplusplus
 }

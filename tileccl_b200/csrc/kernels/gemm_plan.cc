@@ -14,8 +14,9 @@
 namespace tileccl {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
-                               const uint32_t* targets, int skip_src, uint32_t* status,
-                               uint64_t budget_ns, int rank, cudaStream_t stream);
+                               const uint32_t* per_epoch, uint32_t epoch, int skip_src,
+                               uint32_t* status, uint64_t budget_ns, int rank,
+                               cudaStream_t stream);
 
 namespace {
 
@@ -224,11 +225,13 @@ extern "C" int tccl_gemm_plan_destroy(void* plan) {
 }
 
 extern "C" int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src, int32_t n_groups,
-                                uint64_t targets, int32_t skip_src, uint64_t status,
-                                uint64_t budget_ns, int32_t rank, uint64_t stream) {
-  TCCL_CHECK_ARG(sig != 0 && targets != 0, "null argument");
+                                uint64_t per_epoch, uint32_t epoch, int32_t skip_src,
+                                uint64_t status, uint64_t budget_ns, int32_t rank,
+                                uint64_t stream) {
+  TCCL_CHECK_ARG(sig != 0 && per_epoch != 0, "null argument");
   TCCL_CHECK_CUDA(launch_wait_groups(reinterpret_cast<const uint32_t*>(sig), sig_stride, n_src,
-                                     n_groups, reinterpret_cast<const uint32_t*>(targets), skip_src,
+                                     n_groups, reinterpret_cast<const uint32_t*>(per_epoch), epoch,
+                                     skip_src,
                                      reinterpret_cast<uint32_t*>(status),
                                      budget_ns ? budget_ns : 2000000000ull, rank,
                                      reinterpret_cast<cudaStream_t>(stream)));

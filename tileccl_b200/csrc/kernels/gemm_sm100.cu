@@ -459,10 +459,11 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 
 // Waits (bounded) until counters reach their targets: the consumer side of the
 // TileGroup protocol when it runs as its own launch.  counter i = (src, g) with
-// src-major layout; targets[g] is per group; entries of `skip_src` are ignored.
+// src-major layout; the target of group g is per_epoch[g] * epoch (counters only
+// grow, one per_epoch[g] per launch); entries of `skip_src` are ignored.
 __global__ void wait_groups_kernel(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
-                                   const uint32_t* targets, int skip_src, uint32_t* status,
-                                   uint64_t budget_ns, int rank) {
+                                   const uint32_t* per_epoch, uint32_t epoch, int skip_src,
+                                   uint32_t* status, uint64_t budget_ns, int rank) {
   __shared__ uint32_t abort_word;
   if (threadIdx.x == 0) abort_word = 0;
   __syncthreads();
@@ -473,8 +474,9 @@ __global__ void wait_groups_kernel(const uint32_t* sig, int sig_stride, int n_sr
     const int src = i / n_groups, g = i - src * n_groups;
     if (src == skip_src) continue;
     uint32_t seen = 0;
-    if (!tile_wait_ge(sig + src * sig_stride + g, targets[g], wb, &seen)) {
-      report_status(status, kStatusTimeoutSignal, 50, targets[g], seen, rank, i);
+    const uint32_t target = per_epoch[g] * epoch;
+    if (!tile_wait_ge(sig + src * sig_stride + g, target, wb, &seen)) {
+      report_status(status, kStatusTimeoutSignal, 50, target, seen, rank, i);
       abort_word = 1;
       return;
     }
@@ -497,14 +499,15 @@ cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t s
 }
 
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
-                               const uint32_t* targets, int skip_src, uint32_t* status,
-                               uint64_t budget_ns, int rank, cudaStream_t stream) {
+                               const uint32_t* per_epoch, uint32_t epoch, int skip_src,
+                               uint32_t* status, uint64_t budget_ns, int rank,
+                               cudaStream_t stream) {
   int total = n_src * n_groups;
   int threads = 128;
   int blocks = (total + threads - 1) / threads;
   if (blocks < 1) blocks = 1;
-  wait_groups_kernel<<<blocks, threads, 0, stream>>>(sig, sig_stride, n_src, n_groups, targets,
-                                                     skip_src, status, budget_ns, rank);
+  wait_groups_kernel<<<blocks, threads, 0, stream>>>(sig, sig_stride, n_src, n_groups, per_epoch,
+                                                     epoch, skip_src, status, budget_ns, rank);
   return cudaGetLastError();
 }
 

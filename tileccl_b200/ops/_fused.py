@@ -1,0 +1,368 @@
+"""Engine behind the fused GEMM + collective operators.
+
+Turns tensors and a context into native plans (``kernels/fused_gemm.py``), owns
+the per-operator symmetric workspaces (TileGroup counters, reduce-scatter
+staging), advances epochs, and decides how the launches of one call are ordered:
+
+* one process per GPU: a single launch per call; waiting for peers happens
+  inside the kernel (bounded);
+* one process driving one GPU per rank: the same launches, issued rank after
+  rank; kernels on different GPUs overlap, so in-kernel waits are still fine;
+* several ranks emulated on one GPU: kernels of different ranks must not wait
+  on each other inside a launch, so the calls of all ranks are collected and
+  then replayed phase by phase (all producers, then all consumers).  The
+  reference has the same rendezvous for its single-process mode
+  (tileccl/ops.py:85-92, 1572-1658).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from .. import _native
+from ..kernels import fused_gemm as fg
+
+MAX_GROUPS = 64           # TileGroup counters per source rank in a signal block
+_DEFAULT_PUSH = {"stores": fg.PUSH_STORES, "tma": fg.PUSH_TMA, "multimem": fg.PUSH_MULTIMEM}
+
+
+# --------------------------------------------------------------------------
+# per-context state
+# --------------------------------------------------------------------------
+def op_state(ctx, key) -> dict:
+    """Mutable state of one (operator, shapes, buffers) combination on one rank."""
+    table = ctx._state.setdefault("ops", {})
+    st = table.get(key)
+    if st is None:
+        st = {"epoch": 0}
+        table[key] = st
+    return st
+
+
+def status_block(ctx) -> torch.Tensor:
+    """uint32[8] device words a kernel writes when one of its waits gives up."""
+    st = ctx._state.get("status")
+    if st is None:
+        st = torch.zeros(fg.STATUS_WORDS, dtype=torch.int32, device=ctx.torch_device)
+        ctx._state["status"] = st
+    return st
+
+
+def check_status(ctx) -> None:
+    """Synchronise and raise :class:`TileCCLTimeoutError` if any kernel gave up waiting."""
+    st = ctx._state.get("status")
+    if st is None:
+        return
+    torch.cuda.synchronize(ctx.torch_device)
+    fg.raise_on_status(st)
+
+
+def wait_budget_ns() -> int:
+    us = os.environ.get("TILECCL_WAIT_BUDGET_US")
+    return int(float(us) * 1000) if us else 0
+
+
+def default_push_mode(ctx) -> int:
+    name = os.environ.get("TILECCL_PUSH_MODE", "").lower()
+    if name in _DEFAULT_PUSH:
+        mode = _DEFAULT_PUSH[name]
+        if mode == fg.PUSH_MULTIMEM and not (ctx.heap is not None and ctx.heap.has_multicast):
+            raise RuntimeError("TILECCL_PUSH_MODE=multimem but no NVLS multicast mapping is bound")
+        return mode
+    return fg.PUSH_STORES
+
+
+def default_group_m_tiles(m_tiles: int) -> int:
+    """Finest TileGroup (one tile row) unless that would need more than MAX_GROUPS counters."""
+    return max(1, -(-m_tiles // MAX_GROUPS))
+
+
+# --------------------------------------------------------------------------
+# launch ordering
+# --------------------------------------------------------------------------
+def run_phases(ctx, key, phases: Sequence[Callable[[], None]]) -> None:
+    """Run this rank's launches now, or park them until every emulated rank has called."""
+    group = ctx.local_group
+    if group is None or not group.emulated or ctx.world_size == 1:
+        for ph in phases:
+            ph()
+        return
+    slot = group.pending.setdefault(key, {})
+    if ctx.rank in slot:
+        raise RuntimeError(
+            f"rank {ctx.rank} called the same collective operator twice before the other emulated "
+            "ranks called it once")
+    slot[ctx.rank] = list(phases)
+    if len(slot) < ctx.world_size:
+        return
+    del group.pending[key]
+    n = max(len(p) for p in slot.values())
+    for i in range(n):
+        for r in range(ctx.world_size):
+            if i < len(slot[r]):
+                slot[r][i]()
+
+
+def _on_device(ctx, fn: Callable[[], None]) -> Callable[[], None]:
+    dev = ctx.torch_device
+
+    def wrapped():
+        with torch.cuda.device(dev):
+            fn()
+
+    return wrapped
+
+
+def _in_kernel_waits_ok(ctx) -> bool:
+    """Whether a kernel of this rank may spin on flags written by other ranks' kernels."""
+    return not ctx.emulated
+
+
+# --------------------------------------------------------------------------
+# workspaces
+# --------------------------------------------------------------------------
+def _signal_state(ctx, signame: str) -> dict:
+    """Counter block + epoch shared by every plan with the same operator name and shapes.
+
+    The epoch belongs to the counters (they only grow), not to a plan: two plans
+    over different buffers of the same shape take turns on one block.
+    """
+    st = op_state(ctx, ("sig", signame))
+    if "sig" not in st:
+        st["sig"] = ctx.workspace(f"sig:{signame}", ctx.world_size * MAX_GROUPS, dtype=torch.int32)
+    return st
+
+
+def _heap_offset_ptrs(ctx, tensor: torch.Tensor, extra_bytes: int = 0) -> list:
+    """Address of `tensor` (+ byte offset) in every rank's heap, as mapped in this process."""
+    heap = ctx.require_heap()
+    off = heap.get_offset(tensor.data_ptr()) + extra_bytes
+    return [heap.peer_base(r) + off for r in range(ctx.world_size)]
+
+
+def _require_2d(name: str, t: torch.Tensor, ctx) -> None:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be a row-major 2-D tensor, got shape {tuple(t.shape)} "
+                         f"strides {tuple(t.stride())}")
+    if t.device != ctx.torch_device:
+        raise ValueError(f"{name} is on {t.device}, expected {ctx.torch_device}")
+
+
+def _b_dims(B: torch.Tensor, b_is_nk: bool) -> tuple:
+    return (B.shape[1], B.shape[0]) if b_is_nk else (B.shape[0], B.shape[1])  # (K, N)
+
+
+# --------------------------------------------------------------------------
+# push-all: C_d[region of this rank] = A @ B for every rank d
+# --------------------------------------------------------------------------
+def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
+             region_row0: int, region_col0: int, b_is_nk: bool = False,
+             group_m_tiles: Optional[int] = None, push_mode: Optional[int] = None,
+             wait: bool = True) -> None:
+    """Product of the local operands, written into the same region of ``C`` on every rank.
+
+    ``C`` must live on the symmetric heap.  ``region_*`` is where this rank's
+    ``[A.rows, N_b]`` block goes inside ``C``.  With ``wait`` the call also
+    makes sure (on the stream) that every peer's block has arrived in the local
+    ``C``.
+    """
+    _require_2d("A", A, ctx)
+    _require_2d("B", B, ctx)
+    _require_2d("C", C, ctx)
+    K, N = _b_dims(B, b_is_nk)
+    Mloc = A.shape[0]
+    if A.shape[1] != K:
+        raise ValueError(f"inner dimensions differ: A {tuple(A.shape)}, B {tuple(B.shape)}")
+    ws, rank = ctx.world_size, ctx.rank
+    if ws > 1 and not ctx.is_symmetric(C):
+        raise ValueError("C must be allocated from the symmetric heap (ctx.zeros / ctx.empty)")
+    push_mode = default_push_mode(ctx) if push_mode is None else push_mode
+    key = ("push_all", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), Mloc, N, K, A.stride(0),
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, region_row0, region_col0, push_mode)
+    st = op_state(ctx, key)
+    m_tiles = -(-Mloc // fg.BLOCK_M)
+    gm = group_m_tiles or default_group_m_tiles(m_tiles)
+    sigst = _signal_state(ctx, f"push_all:{name}:{Mloc}x{N}x{K}:g{gm}") if ws > 1 else st
+    if "plan" not in st:
+        region_bytes = (region_row0 * C.stride(0) + region_col0) * C.element_size()
+        if ws > 1:
+            sig = sigst["sig"]
+            dests = _heap_offset_ptrs(ctx, C, region_bytes)
+            mc = 0
+            if push_mode == fg.PUSH_MULTIMEM:
+                mc = ctx.heap.multicast_ptr(C.data_ptr()) + region_bytes
+            sig_ptr, stride = sig.data_ptr(), ctx.heap.stride
+        else:
+            dests = [C.data_ptr() + region_bytes]
+            mc, sig_ptr, stride = 0, 0, 0
+        st["plan"] = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_PUSH_ALL if ws > 1 else fg.MODE_GEMM, dtype=A.dtype, a_ptr=A.data_ptr(),
+            a_rows=Mloc, lda=A.stride(0), b_ptr=B.data_ptr(), b_cols=N, ldb=B.stride(0), k=K,
+            sub_m=Mloc, sub_n=N, out_ptrs=dests, ldo=C.stride(0), out_rows=Mloc, out_cols=N,
+            b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws, out_mc_ptr=mc,
+            group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
+            status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
+        plan = st["plan"]
+        if ws > 1:
+            per_epoch = [plan.group_m_count(g) * plan.n_tiles_local * fg.EPILOGUE_SLABS
+                         for g in range(plan.groups)]
+            st["per_epoch"] = torch.tensor(per_epoch, dtype=torch.int32, device=ctx.torch_device)
+            st["sig"] = sig
+    plan = st["plan"]
+    sigst["epoch"] += 1
+    epoch = sigst["epoch"]
+    if ws == 1:
+        plan.launch()
+        return
+    fused_wait = wait and _in_kernel_waits_ok(ctx) and not ctx.is_single_process
+    phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, wait_incoming=fused_wait))]
+    if wait and not fused_wait:
+        phases.append(_on_device(ctx, lambda: wait_groups(ctx, st["sig"], plan.groups,
+                                                          st["per_epoch"], epoch)))
+    run_phases(ctx, ("push_all", name, Mloc, N, K, epoch), phases)
+
+
+def wait_groups(ctx, sig: torch.Tensor, n_groups: int, per_epoch: torch.Tensor, epoch: int) -> None:
+    """Stream-ordered wait until every peer's TileGroups of `epoch` have been signalled."""
+    _native.call("tccl_wait_groups", sig.data_ptr(), MAX_GROUPS, ctx.world_size, n_groups,
+                 per_epoch.data_ptr(), epoch & 0xFFFFFFFF, ctx.rank,
+                 status_block(ctx).data_ptr(), wait_budget_ns(), ctx.rank,
+                 torch.cuda.current_stream().cuda_stream)
+
+
+# --------------------------------------------------------------------------
+# reduce-scatter: C_local = sum over ranks of (A_r @ B_r)[this rank's block]
+# --------------------------------------------------------------------------
+def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
+                   split_axis: int, b_is_nk: bool = False, group_m_tiles: Optional[int] = None,
+                   push_mode: Optional[int] = None) -> None:
+    """Every rank multiplies its operands; block ``r`` of the summed product lands on rank ``r``.
+
+    ``split_axis=0``: ``A`` is ``[ws * Mloc, K]``, ``C`` is ``[Mloc, N]`` (row blocks).
+    ``split_axis=1``: ``B`` has ``ws * Nloc`` columns, ``C`` is ``[M, Nloc]`` (column blocks).
+    Partials travel as 16-bit values into a staging area on the owner's heap and are summed
+    there in fp32, in rank order, by the epilogue of the owner's own tiles.
+    """
+    _require_2d("A", A, ctx)
+    _require_2d("B", B, ctx)
+    _require_2d("C", C, ctx)
+    K, N = _b_dims(B, b_is_nk)
+    M = A.shape[0]
+    ws, rank = ctx.world_size, ctx.rank
+    if A.shape[1] != K:
+        raise ValueError(f"inner dimensions differ: A {tuple(A.shape)}, B {tuple(B.shape)}")
+    if split_axis == 0:
+        if M % ws:
+            raise ValueError(f"M={M} is not divisible by world_size={ws}")
+        sub_m, sub_n = M // ws, N
+    else:
+        if N % ws:
+            raise ValueError(f"N={N} is not divisible by world_size={ws}")
+        sub_m, sub_n = M, N // ws
+    if tuple(C.shape) != (sub_m, sub_n):
+        raise ValueError(f"C must be {(sub_m, sub_n)}, got {tuple(C.shape)}")
+    if not C.is_contiguous():
+        raise ValueError("C must be contiguous")
+    push_mode = default_push_mode(ctx) if push_mode is None else push_mode
+    if push_mode == fg.PUSH_MULTIMEM:
+        push_mode = fg.PUSH_STORES  # partials go to one owner, not to everyone
+    key = ("reduce_scatter", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
+           B.stride(0), A.dtype, b_is_nk, split_axis, push_mode)
+    st = op_state(ctx, key)
+    m_tiles = -(-sub_m // fg.BLOCK_M)
+    gm = group_m_tiles or default_group_m_tiles(m_tiles)
+    sigst = (_signal_state(ctx, f"reduce_scatter:{name}:{M}x{N}x{K}:a{split_axis}:g{gm}:{A.dtype}")
+             if ws > 1 else st)
+    if "plan" not in st:
+        if ws > 1:
+            sig = sigst["sig"]
+            if "stage" not in sigst:
+                sigst["stage"] = ctx.workspace(f"stage:{name}:{sub_m}x{sub_n}:{A.dtype}",
+                                               2 * ws * sub_m * sub_n, dtype=A.dtype)
+            stage = sigst["stage"]
+            dests = _heap_offset_ptrs(ctx, stage)
+            dests[rank] = C.data_ptr()
+            sig_ptr, stride, stage_ptr = sig.data_ptr(), ctx.heap.stride, stage.data_ptr()
+            st["sig"], st["stage"] = sig, stage
+        else:
+            dests = [C.data_ptr()]
+            sig_ptr = stride = stage_ptr = 0
+        st["plan"] = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_REDUCE_SCATTER if ws > 1 else fg.MODE_GEMM, dtype=A.dtype,
+            a_ptr=A.data_ptr(), a_rows=M, lda=A.stride(0), b_ptr=B.data_ptr(), b_cols=N,
+            ldb=B.stride(0), k=K, sub_m=sub_m, sub_n=sub_n, out_ptrs=dests, ldo=sub_n,
+            out_rows=sub_m, out_cols=sub_n, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank,
+            world_size=ws, split_axis=split_axis, out_slot_elems=sub_m * sub_n, out_slots=2 * ws,
+            group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
+            stage_local=stage_ptr, status_ptr=status_block(ctx).data_ptr(),
+            wait_budget_ns=wait_budget_ns()))
+    plan = st["plan"]
+    sigst["epoch"] += 1
+    epoch = sigst["epoch"]
+    if ws == 1 or _in_kernel_waits_ok(ctx):
+        phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch))]
+    else:
+        # Emulated ranks: peers' tiles for everybody first, then each owner's own (reducing) tiles.
+        n_remote = plan.tiles_per_owner * (ws - 1)
+        phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, tile_begin=0, tile_end=n_remote)),
+                  _on_device(ctx, lambda: plan.launch(epoch=epoch, tile_begin=n_remote))]
+    run_phases(ctx, ("reduce_scatter", name, M, N, K, split_axis, epoch), phases)
+
+
+# --------------------------------------------------------------------------
+# all-scatter: full product kept locally, this rank's column slice pushed to all
+# --------------------------------------------------------------------------
+def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
+                col_begin: int, col_end: int, b_is_nk: bool = False,
+                push_mode: Optional[int] = None, wait: bool = True) -> None:
+    _require_2d("A", A, ctx)
+    _require_2d("B", B, ctx)
+    _require_2d("C", C, ctx)
+    K, N = _b_dims(B, b_is_nk)
+    M = A.shape[0]
+    ws, rank = ctx.world_size, ctx.rank
+    if ws > 1 and not ctx.is_symmetric(C):
+        raise ValueError("C must be allocated from the symmetric heap (ctx.zeros / ctx.empty)")
+    push_mode = default_push_mode(ctx) if push_mode is None else push_mode
+    key = ("all_scatter", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, push_mode)
+    st = op_state(ctx, key)
+    m_tiles = -(-M // fg.BLOCK_M)
+    gm = default_group_m_tiles(m_tiles)
+    sigst = _signal_state(ctx, f"all_scatter:{name}:{M}x{N}x{K}:g{gm}") if ws > 1 else st
+    if "plan" not in st:
+        if ws > 1:
+            sig = sigst["sig"]
+            dests = _heap_offset_ptrs(ctx, C)
+            mc = ctx.heap.multicast_ptr(C.data_ptr()) if push_mode == fg.PUSH_MULTIMEM else 0
+            sig_ptr, stride = sig.data_ptr(), ctx.heap.stride
+            st["sig"] = sig
+        else:
+            dests, mc, sig_ptr, stride = [C.data_ptr()], 0, 0, 0
+        st["plan"] = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_ALL_SCATTER if ws > 1 else fg.MODE_GEMM, dtype=A.dtype,
+            a_ptr=A.data_ptr(), a_rows=M, lda=A.stride(0), b_ptr=B.data_ptr(), b_cols=N,
+            ldb=B.stride(0), k=K, sub_m=M, sub_n=N, out_ptrs=dests, ldo=C.stride(0), out_rows=M,
+            out_cols=N, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws,
+            out_mc_ptr=mc, group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride,
+            sig_stride=MAX_GROUPS, scatter_col_begin=col_begin, scatter_col_end=col_end,
+            status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
+        plan = st["plan"]
+        if ws > 1:
+            # A tile signals once per slab whether or not it overlaps the pushed slice, so the
+            # count per group is the same as for push-all.
+            per_epoch = [plan.group_m_count(g) * plan.n_tiles_local * fg.EPILOGUE_SLABS
+                         for g in range(plan.groups)]
+            st["per_epoch"] = torch.tensor(per_epoch, dtype=torch.int32, device=ctx.torch_device)
+    plan = st["plan"]
+    sigst["epoch"] += 1
+    epoch = sigst["epoch"]
+    phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch))]
+    if ws > 1 and wait:
+        phases.append(_on_device(ctx, lambda: wait_groups(ctx, st["sig"], plan.groups,
+                                                          st["per_epoch"], epoch)))
+    run_phases(ctx, ("all_scatter", name, M, N, K, epoch), phases)

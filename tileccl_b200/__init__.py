@@ -31,26 +31,6 @@ _LAZY_SUBMODULES = ("ops", "patterns", "planning", "primitives", "sync", "memory
 
 
 @dataclass
-class LocalGroup:
-    """The contexts created together by :func:`init_local` (one process, many ranks).
-
-    ``emulated`` is true when some ranks share a GPU.  Kernels of different
-    ranks must then never wait on each other inside a launch, so multi-rank
-    operators stage their per-rank calls in ``pending`` and run them phase by
-    phase once every rank has called (see ``ops._rendezvous``).
-    """
-
-    world_size: int
-    devices: list
-    contexts: list = field(default_factory=list)
-    pending: dict = field(default_factory=dict)
-
-    @property
-    def emulated(self) -> bool:
-        return len(set(self.devices)) < len(self.devices)
-
-
-@dataclass
 class TileCCLContext:
     rank: int
     world_size: int
@@ -59,7 +39,7 @@ class TileCCLContext:
     backend: Any = field(repr=False, default=None)
     topology: Any = field(default=None, repr=False)
     heap: Any = field(default=None, repr=False)
-    local_group: Optional[LocalGroup] = field(default=None, repr=False)
+    local_group: Any = field(default=None, repr=False)
     _workspace_cache: dict = field(default_factory=dict, repr=False)
     _state: dict = field(default_factory=dict, repr=False)
 
@@ -85,6 +65,8 @@ class TileCCLContext:
                 f"{self.rank}/{self.world_size}")
         self.heap = heap
         self.device = str(heap.device)
+        if getattr(heap, "local_group", None) is not None:
+            self.local_group = heap.local_group
         self._workspace_cache.clear()
         self._state.clear()
         return self
@@ -299,14 +281,12 @@ def init_local(world_size: int, heap_size: int, *, backend: str = "auto",
 
     name = _resolve_backend_name(backend)
     heaps = SymmetricHeap.create_all(int(heap_size), world_size, name, devices=devices)
-    group = LocalGroup(world_size=world_size, devices=[h.device.index for h in heaps])
     ctxs = []
     for r, heap in enumerate(heaps):
         ctx = _build_context(name, r, world_size, force_backend, device=str(heap.device))
-        ctx.local_group = group
         ctx.attach_heap(heap)
         ctxs.append(ctx)
-    group.contexts = ctxs
+    heaps[0].local_group.contexts = ctxs
     return ctxs
 
 
@@ -341,5 +321,5 @@ def __getattr__(name: str):
 
 
 __all__ = ["__version__", "init", "init_local", "get_rank", "get_world_size", "current_context",
-           "describe_runtime_support", "TileCCLContext", "LocalGroup", "Tile", "SymmetricHeap",
+           "describe_runtime_support", "TileCCLContext", "Tile", "SymmetricHeap",
            "patterns", "ops", "planning"]

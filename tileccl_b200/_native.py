@@ -150,8 +150,10 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_heap_alloc": [vp, u64, C.POINTER(u64)],
         "tccl_heap_reset": [vp],
         "tccl_heap_bytes_allocated": [vp, C.POINTER(u64)],
-        "tccl_collective_launch": [i32, i32, i32, i32, i32, i32, i32, u32, u64, u64, u64, u64, u64,
+        "tccl_collective_launch": [i32, i32, i32, i32, i32, i32, i32, i32, u32, u64, u64, u64, u64, u64,
                                    u64, C.c_int64, u64, i32, u64, u64, u64],
+        "tccl_prim_test": [i32, i32, i32, i32, i32, u64, u64, u64, u64, u64, u64, u32, u32, u64, u64,
+                           u64],
         "tccl_bootstrap_allgather": [i32, i32, C.c_char_p, i32, u64, i32, C.POINTER(u64),
                                      C.POINTER(i32)],
     }

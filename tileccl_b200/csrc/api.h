@@ -143,11 +143,25 @@ int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src, int32_t n_
 // phase_mask: bit 0 announce, bit 1 move data, bit 2 wait for completion (7 = whole call).
 // --------------------------------------------------------------------------
 int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
-                           int32_t root, int32_t use_multimem, int32_t phase_mask, uint32_t epoch,
+                           int32_t root, int32_t use_multimem, int32_t phase_mask, int32_t elem_size,
+                           uint32_t epoch,
                            uint64_t src, uint64_t dst, uint64_t staging, uint64_t counters,
                            uint64_t mc_base, uint64_t heap_base, int64_t heap_stride,
                            uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
                            uint64_t stream);
+
+// --------------------------------------------------------------------------
+// Device-primitive test harness (csrc/kernels/prim_test.cu): one launch acts as
+// `rank` and applies one primitive.  op codes: 0 put, 1 get, 2 remote_store,
+// 3 remote_load, 4 signal, 5 wait, 6 poll, 7 signal_add, 8 wait_ge, 9 atomic
+// (sub_op 0 add, 1 cas, 2 xchg, 3 min, 4 max, 5 and, 6 or, 7 xor), 10 barrier,
+// 11 credit (sub_op 0 acquire, 1 release), 12 try_wait, 13 translate,
+// 14 put_mc, 15 get_reduce.  `result` is uint32[4] in device memory.
+// --------------------------------------------------------------------------
+int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t world_size, int32_t peer,
+                   uint64_t window_base, uint64_t stride, uint64_t mc_base, uint64_t a, uint64_t b,
+                   uint64_t n, uint32_t value, uint32_t value2, uint64_t result, uint64_t budget_ns,
+                   uint64_t stream);
 
 #ifdef __cplusplus
 }

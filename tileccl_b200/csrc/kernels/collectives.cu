@@ -51,6 +51,7 @@ struct CollParams {
   int32_t op, dtype, rank, world_size, root;
   int32_t use_multimem;
   int32_t phase_mask;
+  int32_t elem_size;   // bytes per element (scalar fallback granularity)
   uint32_t epoch;
   uint64_t src;        // local address (heap) of the input
   uint64_t dst;        // local address (heap) of the output (== src for in-place ops)
@@ -101,16 +102,35 @@ __device__ __forceinline__ uint4 mc_reduce(int dtype, const void* mc) {
                                         : multimem_ld_reduce_f16x8(mc);
 }
 
-// Grid-stride copy of `bytes` (16-byte aligned on both sides) from local memory to
-// one destination, or to every rank through the multicast alias.
-__device__ __forceinline__ void copy_vec(char* dst, const char* src, uint64_t bytes) {
-  const uint64_t n = bytes >> 4;
+// Grid-stride copy from local memory to one (possibly remote) destination.  Moves
+// 16 bytes per access when both addresses and the length allow it; otherwise one
+// element per access (chunk offsets of odd-sized messages are only element-aligned).
+template <typename T>
+__device__ __forceinline__ void copy_elems(char* dst, const char* src, uint64_t bytes) {
+  const uint64_t n = bytes / sizeof(T);
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
-    st_remote_v4(dst + (i << 4), *reinterpret_cast<const uint4*>(src + (i << 4)));
-  // tail (< 16 bytes) by one thread
-  if (blockIdx.x == 0 && threadIdx.x == 0)
-    for (uint64_t b = n << 4; b < bytes; ++b) dst[b] = src[b];
+    reinterpret_cast<T*>(dst)[i] = reinterpret_cast<const T*>(src)[i];
+}
+__device__ __forceinline__ bool vec_ok(const void* a, const void* b, uint64_t bytes) {
+  return ((reinterpret_cast<uint64_t>(a) | reinterpret_cast<uint64_t>(b) | bytes) & 15u) == 0;
+}
+__device__ __forceinline__ void copy_vec(char* dst, const char* src, uint64_t bytes, int es) {
+  if (vec_ok(dst, src, bytes)) {
+    const uint64_t n = bytes >> 4;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += stride)
+      st_remote_v4(dst + (i << 4), *reinterpret_cast<const uint4*>(src + (i << 4)));
+  } else if (es == 8) {
+    copy_elems<uint64_t>(dst, src, bytes);
+  } else if (es == 4) {
+    copy_elems<uint32_t>(dst, src, bytes);
+  } else if (es == 2) {
+    copy_elems<uint16_t>(dst, src, bytes);
+  } else {
+    copy_elems<uint8_t>(dst, src, bytes);
+  }
 }
 __device__ __forceinline__ void copy_vec_mc(char* mc_dst, const char* src, uint64_t bytes) {
   const uint64_t n = bytes >> 4;
@@ -191,7 +211,7 @@ __global__ void __launch_bounds__(512) collective_kernel(const CollParams p) {
         } else {
           for (int d = 0; d < ws; ++d) {
             const int r = (rank + d) % ws;
-            copy_vec(peer<char>(p, p.dst, r) + rank * bytes, src, bytes);
+            copy_vec(peer<char>(p, p.dst, r) + rank * bytes, src, bytes, p.elem_size);
           }
         }
       } else if (p.op == kBroadcast) {
@@ -200,14 +220,14 @@ __global__ void __launch_bounds__(512) collective_kernel(const CollParams p) {
             copy_vec_mc(mcast<char>(p, p.dst), src, bytes);
           } else {
             for (int d = 1; d < ws; ++d)
-              copy_vec(peer<char>(p, p.dst, (rank + d) % ws), src, bytes);
+              copy_vec(peer<char>(p, p.dst, (rank + d) % ws), src, bytes, p.elem_size);
           }
         }
       } else if (p.op == kScatter) {
         if (is_root) {
           for (int d = 0; d < ws; ++d) {
             const int r = (rank + d) % ws;
-            copy_vec(peer<char>(p, p.dst, r), src + r * bytes, bytes);
+            copy_vec(peer<char>(p, p.dst, r), src + r * bytes, bytes, p.elem_size);
           }
         }
       } else if (p.op == kReduceScatter || p.op == kAllReduceTwoShot) {
@@ -220,7 +240,10 @@ __global__ void __launch_bounds__(512) collective_kernel(const CollParams p) {
           chunk_off = rank * chunk;
           my_bytes = chunk_off >= bytes ? 0 : (bytes - chunk_off < chunk ? bytes - chunk_off : chunk);
         }
-        const uint64_t n = my_bytes >> 4;
+        // Chunk offsets of a reduce-scatter are only element-aligned when the chunk is not a
+        // multiple of 16 bytes: then everything goes through the scalar loop below.
+        const bool aligned = ((chunk_off | reinterpret_cast<uint64_t>(dst)) & 15u) == 0;
+        const uint64_t n = aligned ? (my_bytes >> 4) : 0;
         for (uint64_t i = gtid; i < n; i += gstride) {
           uint4 out;
           const uint64_t off = chunk_off + (i << 4);
@@ -247,10 +270,10 @@ __global__ void __launch_bounds__(512) collective_kernel(const CollParams p) {
               if (r < ws) st_remote_v4(peer<char>(p, p.dst, r) + off, out);
           }
         }
-        // element tail (< 16 bytes): one thread, scalar
-        if ((my_bytes & 15) && gtid == 0) {
+        // scalar remainder: the < 16-byte tail, or the whole chunk when it is unaligned
+        if ((n << 4) < my_bytes) {
           const int es = p.dtype == kF32 ? 4 : 2;
-          for (uint64_t b = n << 4; b < my_bytes; b += es) {
+          for (uint64_t b = (n << 4) + gtid * es; b < my_bytes; b += gstride * es) {
             float a = 0.f;
             for (int r = 0; r < ws; ++r) {
               const char* q = peer<char>(p, p.src, r) + chunk_off + b;
@@ -318,7 +341,10 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const CollParams
 
   if (p.phase_mask & 1) {
     // publish a snapshot of the local buffer, then announce it
-    copy_vec(reinterpret_cast<char*>(stage), buf, bytes);
+    copy_vec(reinterpret_cast<char*>(stage), buf, bytes & ~static_cast<uint64_t>(15), 16);
+    if ((bytes & 15) && gtid == 0)
+      for (uint64_t b = bytes & ~static_cast<uint64_t>(15); b < bytes; ++b)
+        reinterpret_cast<char*>(stage)[b] = buf[b];
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -369,7 +395,7 @@ using namespace tileccl;
 
 extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
                                       int32_t root, int32_t use_multimem, int32_t phase_mask,
-                                      uint32_t epoch, uint64_t src, uint64_t dst, uint64_t staging,
+                                      int32_t elem_size, uint32_t epoch, uint64_t src, uint64_t dst, uint64_t staging,
                                       uint64_t counters, uint64_t mc_base, uint64_t heap_base,
                                       int64_t heap_stride, uint64_t bytes, int32_t grid,
                                       uint64_t status, uint64_t budget_ns, uint64_t stream) {
@@ -378,6 +404,9 @@ extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, i
   TCCL_CHECK_ARG(rank >= 0 && rank < world_size && root >= 0 && root < world_size, "bad rank/root");
   TCCL_CHECK_ARG(counters != 0, "missing counter block");
   TCCL_CHECK_ARG(grid >= 1, "grid must be >= 1");
+  TCCL_CHECK_ARG(elem_size == 1 || elem_size == 2 || elem_size == 4 || elem_size == 8,
+                 "elem_size must be 1, 2, 4 or 8");
+  TCCL_CHECK_ARG(bytes % elem_size == 0, "byte count is not a whole number of elements");
   TCCL_CHECK_ARG((src % 16) == 0 && (dst % 16) == 0, "buffers must be 16-byte aligned");
   if (use_multimem) TCCL_CHECK_ARG(mc_base != 0, "multimem requested without a multicast mapping");
   if (op == kAllGather || op == kScatter || op == kReduceScatter)
@@ -386,6 +415,7 @@ extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, i
   CollParams p;
   p.op = op; p.dtype = dtype; p.rank = rank; p.world_size = world_size; p.root = root;
   p.use_multimem = use_multimem; p.phase_mask = phase_mask; p.epoch = epoch;
+  p.elem_size = elem_size;
   p.src = src; p.dst = dst; p.staging = staging; p.counters = counters; p.mc_base = mc_base;
   p.heap_base = heap_base; p.heap_stride = heap_stride; p.bytes = bytes; p.status = status;
   p.budget_ns = budget_ns ? budget_ns : 2000000000ull;

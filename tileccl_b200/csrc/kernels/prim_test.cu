@@ -1,0 +1,140 @@
+// Small kernels that exercise the device primitives one at a time, so that the
+// Python test-suite can check pointer translation, remote load/store, put/get,
+// the signal/wait family, remote atomics and the bounded-wait time-out path
+// against host expectations.  Each launch acts as ONE rank (`window.rank`).
+#include <cuda_runtime.h>
+
+#include "../api.h"
+#include "../device/tile_comm.cuh"
+#include "../device/tile_sync.cuh"
+#include "../runtime/errors.h"
+
+namespace tileccl {
+
+enum PrimOp : int {
+  kPrimPut = 0,          // a: local src, b: symmetric dst, n bytes -> peer
+  kPrimGet = 1,          // a: symmetric src (read from peer), b: local dst
+  kPrimRemoteStore = 2,  // a: local src -> registers -> peer's b
+  kPrimRemoteLoad = 3,   // peer's a -> registers -> local b
+  kPrimSignal = 4,       // raise flag a on peer
+  kPrimWait = 5,         // wait + consume local flag a        (result[0] = 1 ok / 0 timeout)
+  kPrimPoll = 6,         // non-consuming wait on local flag a
+  kPrimSignalAdd = 7,    // counter a on peer += value
+  kPrimWaitGe = 8,       // wait local counter a >= value
+  kPrimAtomic = 9,       // remote atomic `sub_op` on a with value; result[0] = old
+  kPrimBarrier = 10,     // tile_barrier on counter a with epoch = value
+  kPrimCredit = 11,      // sub_op 0: acquire from local pool a; 1: release to peer's pool a
+  kPrimTryWait = 12,     // bounded by `value` polls
+  kPrimTranslate = 13,   // result64[0] = translate_ptr(a, rank, peer)
+  kPrimPutMc = 14,       // a: local src -> multicast alias of b
+  kPrimGetReduce = 15,   // multimem.ld_reduce over a -> local b (sub_op = dtype kind)
+};
+
+struct PrimArgs {
+  SymmWindow w;
+  int32_t op, sub_op, peer;
+  uint32_t value, value2;
+  uint64_t a, b, n;
+  uint64_t result;  // uint32[4] / uint64[2] in device memory
+  uint64_t budget_ns;
+};
+
+__global__ void prim_test_kernel(const PrimArgs x) {
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  WaitBudget wb;
+  wb.start(x.budget_ns, &abort_word);
+  uint32_t* res = reinterpret_cast<uint32_t*>(x.result);
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int rows = 1;
+  TileView va{reinterpret_cast<char*>(x.a), static_cast<int64_t>(x.n), rows, static_cast<int>(x.n)};
+  TileView vb{reinterpret_cast<char*>(x.b), static_cast<int64_t>(x.n), rows, static_cast<int>(x.n)};
+  switch (x.op) {
+    case kPrimPut: tile_put(x.w, va, vb, x.peer, tid, nt); break;
+    case kPrimGet: tile_get(x.w, va, vb, x.peer, tid, nt); break;
+    case kPrimRemoteStore: {
+      uint4 frag[4];
+      tile_load(va, frag, tid, nt);
+      tile_remote_store(x.w, vb, x.peer, frag, tid, nt);
+      break;
+    }
+    case kPrimRemoteLoad: {
+      uint4 frag[4];
+      tile_remote_load(x.w, va, x.peer, frag, tid, nt);
+      tile_store(vb, frag, tid, nt);
+      break;
+    }
+    case kPrimPutMc: tile_put_mc(x.w, va, vb, tid, nt); break;
+    case kPrimGetReduce: tile_get_reduce(x.w, va, vb, x.sub_op, tid, nt); break;
+    default: break;
+  }
+  if (tid != 0) return;
+  uint32_t* fa = reinterpret_cast<uint32_t*>(x.a);
+  switch (x.op) {
+    case kPrimSignal: tile_signal(x.w, fa, x.peer); break;
+    case kPrimWait: res[0] = tile_wait(fa, wb) ? 1u : 0u; break;
+    case kPrimPoll: res[0] = tile_poll(fa, wb) ? 1u : 0u; break;
+    case kPrimTryWait: res[0] = tile_try_wait(fa, static_cast<int>(x.value)) ? 1u : 0u; break;
+    case kPrimSignalAdd: tile_signal_add(x.w, fa, x.value, x.peer); break;
+    case kPrimWaitGe: {
+      uint32_t seen = 0;
+      res[0] = tile_wait_ge(fa, x.value, wb, &seen) ? 1u : 0u;
+      res[1] = seen;
+      break;
+    }
+    case kPrimAtomic: {
+      uint32_t old = 0;
+      switch (x.sub_op) {
+        case 0: old = tile_atomic_add(x.w, fa, x.value, x.peer); break;
+        case 1: old = tile_atomic_cas(x.w, fa, x.value, x.value2, x.peer); break;
+        case 2: old = tile_atomic_xchg(x.w, fa, x.value, x.peer); break;
+        case 3: old = tile_atomic_min(x.w, fa, x.value, x.peer); break;
+        case 4: old = tile_atomic_max(x.w, fa, x.value, x.peer); break;
+        case 5: old = tile_atomic_and(x.w, fa, x.value, x.peer); break;
+        case 6: old = tile_atomic_or(x.w, fa, x.value, x.peer); break;
+        case 7: old = tile_atomic_xor(x.w, fa, x.value, x.peer); break;
+        default: break;
+      }
+      res[0] = old;
+      break;
+    }
+    case kPrimBarrier: res[0] = tile_barrier(x.w, fa, x.value, wb) ? 1u : 0u; break;
+    case kPrimCredit:
+      if (x.sub_op == 0) res[0] = tile_acquire_credit(fa, wb) ? 1u : 0u;
+      else tile_release_credit(x.w, fa, x.peer);
+      break;
+    case kPrimTranslate:
+      reinterpret_cast<uint64_t*>(x.result)[0] =
+          reinterpret_cast<uint64_t>(translate_ptr(x.w, fa, x.w.rank, x.peer));
+      break;
+    default: break;
+  }
+}
+
+}  // namespace tileccl
+
+using namespace tileccl;
+
+extern "C" int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t world_size,
+                              int32_t peer, uint64_t window_base, uint64_t stride, uint64_t mc_base,
+                              uint64_t a, uint64_t b, uint64_t n, uint32_t value, uint32_t value2,
+                              uint64_t result, uint64_t budget_ns, uint64_t stream) {
+  TCCL_CHECK_ARG(rank >= 0 && rank < world_size && peer >= 0 && peer < world_size, "bad rank/peer");
+  TCCL_CHECK_ARG(result != 0, "result buffer required");
+  TCCL_CHECK_ARG(n <= 128 * 4 * 16, "at most 8 KiB per call");
+  if (op == kPrimPutMc || op == kPrimGetReduce)
+    TCCL_CHECK_ARG(mc_base != 0, "multimem primitives need a multicast mapping");
+  PrimArgs x;
+  x.w.base = window_base;
+  x.w.stride = stride;
+  x.w.mc_base = mc_base;
+  x.w.rank = rank;
+  x.w.world_size = world_size;
+  x.op = op; x.sub_op = sub_op; x.peer = peer; x.value = value; x.value2 = value2;
+  x.a = a; x.b = b; x.n = n; x.result = result;
+  x.budget_ns = budget_ns ? budget_ns : 1000000000ull;
+  prim_test_kernel<<<1, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(x);
+  TCCL_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}

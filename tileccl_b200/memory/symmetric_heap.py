@@ -25,7 +25,7 @@ import ctypes as C
 import logging
 import os
 import uuid
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
 import torch
@@ -91,6 +91,26 @@ class PeerMemoryMapEntry:
         }
 
 
+@dataclass
+class LocalGroup:
+    """The ranks that one process drives (``SymmetricHeap.create_all`` / ``init_local``).
+
+    ``emulated`` is true when some ranks share a GPU.  Kernels of different ranks
+    must then never wait on each other inside a launch, so multi-rank operators
+    park their per-rank launches in ``pending`` and replay them phase by phase
+    once every rank has called.
+    """
+
+    world_size: int
+    devices: list
+    contexts: list = field(default_factory=list)
+    pending: dict = field(default_factory=dict)
+
+    @property
+    def emulated(self) -> bool:
+        return len(set(self.devices)) < len(self.devices)
+
+
 class _NativeHandle:
     """Owns one native heap handle; destroying the last one unmaps the window."""
 
@@ -132,6 +152,8 @@ class SymmetricHeap:
         self._allocator: VmmBumpAllocator = create_allocator(allocator_type)
         self._cleaned_up = False
         self._group = _group
+        self.local_group: Optional[LocalGroup] = None
+        self._state: dict = {}
         want_nvls = _want_nvls(nvls)
 
         if _handle is None:
@@ -208,8 +230,12 @@ class SymmetricHeap:
         out = (C.c_void_p * world_size)()
         _native.call("tccl_heap_create_local", world_size, int(size), arr,
                      1 if _want_nvls(nvls) else 0, out)
-        return [cls(size, r, world_size, backend, allocator_type=allocator_type,
-                    _handle=C.c_void_p(out[r])) for r in range(world_size)]
+        heaps = [cls(size, r, world_size, backend, allocator_type=allocator_type,
+                     _handle=C.c_void_p(out[r])) for r in range(world_size)]
+        group = LocalGroup(world_size=world_size, devices=[int(d) for d in devices])
+        for h in heaps:
+            h.local_group = group
+        return heaps
 
     # -------------------------------------------------------------- allocation
     def allocate_tensor(self, shape, dtype: torch.dtype) -> torch.Tensor:
@@ -282,6 +308,15 @@ class SymmetricHeap:
     @property
     def has_multicast(self) -> bool:
         return self._mc_base != 0
+
+    @property
+    def emulated(self) -> bool:
+        """True when this rank shares its GPU with another rank of the same process."""
+        return self.local_group is not None and self.local_group.emulated
+
+    @property
+    def is_single_process(self) -> bool:
+        return self._mode != "multiprocess"
 
     @property
     def size(self) -> int:

@@ -1,0 +1,317 @@
+"""Host launchers of the tile collectives (``csrc/kernels/collectives.cu``).
+
+Same entry points as the reference (tileccl/primitives/collectives.py:1882-2632):
+``allreduce``, ``allgather``, ``broadcast``, ``scatter``, ``reduce_scatter``,
+``resolve_allreduce_execution`` / ``AllReduceExecutionSpec``.  Buffers live on the
+symmetric heap; no NCCL call is made.
+
+Algorithms (all direct, one NVLink hop, any world size 1..8):
+
+=============== =========================================================
+all-gather      push own chunk into every rank's output (multimem.st if NVLS)
+reduce-scatter  pull own chunk from every rank and sum in fp32
+                (multimem.ld_reduce if NVLS)
+all-reduce      <= 256 KiB: one-shot through a double-buffered staging copy;
+                larger: pull-reduce own chunk, push it to every rank
+broadcast       root pushes to everyone
+scatter         root pushes chunk r to rank r
+=============== =========================================================
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import asdict, dataclass
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ..kernels.fused_gemm import STATUS_WORDS, raise_on_status
+
+OP_ALLGATHER = 0
+OP_REDUCE_SCATTER = 1
+OP_ALLREDUCE_TWO_SHOT = 2
+OP_ALLREDUCE_ONE_SHOT = 3
+OP_BROADCAST = 4
+OP_SCATTER = 5
+
+_DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+_COUNTER_WORDS = 32
+_THREADS = 512
+MAX_WORLD_SIZE = 8
+
+# Message regimes of the all-reduce policy (bytes).
+LATENCY_MAX_BYTES = 8 * 1024
+ONE_SHOT_MAX_BYTES = 256 * 1024
+
+
+@dataclass(frozen=True)
+class AllReduceExecutionSpec:
+    """How one all-reduce call will run; part of ``AllReducePlan.to_dict()``."""
+
+    implementation: str       # "noop" | "device_one_shot" | "device_two_shot"
+    protocol: str             # "local_identity" | "staged_snapshot_epoch" | "pull_reduce_push_epoch"
+    kernel_family: str        # "local_identity" | "generic_multi_peer"
+    message_regime: str       # "latency" | "throughput" | "bandwidth"
+    message_bytes: int
+    chunk_elems: int          # elements each rank reduces (two-shot) or the whole message (one-shot)
+    num_chunks: int
+    pipeline_slots: int       # staging parities (one-shot) / 1
+    grid_size: int
+    num_warps: int
+    workspace_bytes: int
+    reuse_handshake: str      # "epoch_parity_double_buffer" | "completion_counter" | "none"
+    cta_policy: str
+    epoch_policy: str
+    use_multimem: bool
+
+    def to_dict(self) -> dict:
+        return asdict(self)
+
+
+# --------------------------------------------------------------------------
+# per-heap state
+# --------------------------------------------------------------------------
+def _sm_count(device: torch.device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def _counters(heap, kind: str) -> dict:
+    st = heap._state.setdefault(("coll", kind), None)
+    if st is None:
+        st = {"counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0}
+        heap._state[("coll", kind)] = st
+    return st
+
+
+def _status(heap) -> torch.Tensor:
+    st = heap._state.get("status")
+    if st is None:
+        st = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=heap.device)
+        heap._state["status"] = st
+    return st
+
+
+def check_status(heap) -> None:
+    """Synchronise and raise if a collective kernel gave up waiting for a peer."""
+    st = heap._state.get("status")
+    if st is not None:
+        torch.cuda.synchronize(heap.device)
+        raise_on_status(st)
+
+
+def _budget_ns() -> int:
+    us = os.environ.get("TILECCL_WAIT_BUDGET_US")
+    return int(float(us) * 1000) if us else 0
+
+
+def _grid_for(nbytes: int, device: torch.device) -> int:
+    vecs = max(1, nbytes // 16)
+    return max(1, min(_sm_count(device), -(-vecs // (_THREADS * 2))))
+
+
+def _use_multimem(heap, nbytes: int) -> bool:
+    if not heap.has_multicast or os.environ.get("TILECCL_DISABLE_NVLS", "0") not in ("", "0"):
+        return False
+    return nbytes % 16 == 0 and nbytes >= 16
+
+
+def _validate(name: str, t: torch.Tensor, heap) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if heap.world_size > MAX_WORLD_SIZE:
+        raise ValueError(f"world_size {heap.world_size} exceeds the supported maximum {MAX_WORLD_SIZE}")
+    if heap.world_size > 1 and not heap.owns_tensor(t):
+        raise ValueError(f"{name} must live on the symmetric heap of rank {heap.rank}")
+    if t.data_ptr() % 16:
+        raise ValueError(f"{name} must be 16-byte aligned")
+
+
+def _run(heap, key, phases) -> None:
+    """Launch now, or (emulated ranks) park until all ranks have called and replay by phase."""
+    group = heap.local_group
+    if group is None or not group.emulated or heap.world_size == 1:
+        for ph in phases:
+            ph()
+        return
+    slot = group.pending.setdefault(key, {})
+    if heap.rank in slot:
+        raise RuntimeError(f"rank {heap.rank} entered collective {key[0]!r} twice before its peers")
+    slot[heap.rank] = phases
+    if len(slot) < heap.world_size:
+        return
+    del group.pending[key]
+    for i in range(max(len(p) for p in slot.values())):
+        for r in range(heap.world_size):
+            if i < len(slot[r]):
+                slot[r][i]()
+
+
+def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbytes: int, *,
+            elem_size: int, root: int = 0, staging: int = 0, use_multimem: bool = False,
+            grid: Optional[int] = None, rv_extra=()) -> None:
+    st = _counters(heap, kind)
+    st["epoch"] += 1
+    epoch = st["epoch"]
+    grid = grid or _grid_for(nbytes, heap.device)
+    status = _status(heap).data_ptr()
+    counters = st["counters"].data_ptr()
+
+    def make(mask: int):
+        def go():
+            with torch.cuda.device(heap.device):
+                _native.call(
+                    "tccl_collective_launch", op, dtype_code, heap.rank, heap.world_size, root,
+                    1 if use_multimem else 0, mask, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, counters,
+                    heap.multicast_base, heap.local_base, heap.stride, nbytes, grid, status,
+                    _budget_ns(), torch.cuda.current_stream().cuda_stream)
+        return go
+
+    if heap.emulated and heap.world_size > 1:
+        phases = [make(1), make(2), make(4)] if op != OP_ALLREDUCE_ONE_SHOT else [make(1), make(2)]
+    else:
+        phases = [make(7)]
+    _run(heap, (kind, nbytes, epoch) + tuple(rv_extra), phases)
+
+
+def _heap_of(heap, ctx):
+    if heap is None and ctx is not None:
+        heap = ctx.heap
+    if heap is None:
+        raise ValueError("a symmetric heap is required")
+    return heap
+
+
+# --------------------------------------------------------------------------
+# launchers
+# --------------------------------------------------------------------------
+def resolve_allreduce_execution(tensor: torch.Tensor, *, heap, op: str = "sum",
+                                ctx=None) -> AllReduceExecutionSpec:
+    heap = _heap_of(heap, ctx)
+    if op != "sum":
+        raise ValueError(f"only op='sum' is supported, got {op!r}")
+    if tensor.dtype not in _DTYPE_CODE:
+        raise TypeError(f"allreduce supports float16, bfloat16 and float32, got {tensor.dtype}")
+    nbytes = tensor.numel() * tensor.element_size()
+    ws = heap.world_size
+    regime = ("latency" if nbytes <= LATENCY_MAX_BYTES
+              else "throughput" if nbytes <= ONE_SHOT_MAX_BYTES else "bandwidth")
+    if ws == 1:
+        return AllReduceExecutionSpec("noop", "local_identity", "local_identity", regime, nbytes,
+                                      tensor.numel(), 1, 1, 0, 0, 0, "none", "none", "none", False)
+    grid = _grid_for(nbytes, heap.device) if tensor.is_cuda else 1
+    if nbytes <= ONE_SHOT_MAX_BYTES:
+        slot = (nbytes + 15) // 16 * 16
+        return AllReduceExecutionSpec(
+            "device_one_shot", "staged_snapshot_epoch", "generic_multi_peer", regime, nbytes,
+            tensor.numel(), 1, 2, grid, _THREADS // 32, 2 * slot + 4 * _COUNTER_WORDS,
+            "epoch_parity_double_buffer", "grid_stride_multi_cta", "monotonic_counter", False)
+    chunk_bytes = (-(-nbytes // ws) + 15) // 16 * 16
+    return AllReduceExecutionSpec(
+        "device_two_shot", "pull_reduce_push_epoch", "generic_multi_peer", regime, nbytes,
+        chunk_bytes // tensor.element_size(), ws, 1, grid, _THREADS // 32, 4 * _COUNTER_WORDS,
+        "completion_counter", "grid_stride_multi_cta", "monotonic_counter",
+        _use_multimem(heap, chunk_bytes))
+
+
+def allreduce(tensor: torch.Tensor, heap=None, op: str = "sum", *, ctx=None,
+              _execution: Optional[AllReduceExecutionSpec] = None) -> torch.Tensor:
+    """In-place sum of ``tensor`` over all ranks."""
+    heap = _heap_of(heap, ctx)
+    _validate("tensor", tensor, heap)
+    ex = _execution or resolve_allreduce_execution(tensor, heap=heap, op=op)
+    if ex.implementation == "noop":
+        return tensor
+    nbytes = ex.message_bytes
+    code = _DTYPE_CODE[tensor.dtype]
+    ptr = tensor.data_ptr()
+    if ex.implementation == "device_one_shot":
+        slot = (nbytes + 15) // 16 * 16
+        stage_key = ("coll_stage", slot)
+        stage = heap._state.get(stage_key)
+        if stage is None:
+            stage = heap.allocate_tensor((2 * slot,), torch.uint8)
+            heap._state[stage_key] = stage
+        _launch(heap, f"allreduce1:{slot}", OP_ALLREDUCE_ONE_SHOT, code, ptr, ptr, nbytes,
+                staging=stage.data_ptr(), grid=ex.grid_size, elem_size=tensor.element_size())
+    else:
+        _launch(heap, "allreduce2", OP_ALLREDUCE_TWO_SHOT, code, ptr, ptr, nbytes,
+                use_multimem=ex.use_multimem, grid=ex.grid_size, elem_size=tensor.element_size())
+    return tensor
+
+
+def allgather(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, ctx=None) -> torch.Tensor:
+    """``output[r * n:(r + 1) * n] = rank r's tensor`` on every rank."""
+    heap = _heap_of(heap, ctx)
+    _validate("tensor", tensor, heap)
+    _validate("output", output, heap)
+    if output.numel() != tensor.numel() * heap.world_size or output.dtype != tensor.dtype:
+        raise ValueError(f"output must hold world_size * {tensor.numel()} elements of {tensor.dtype}")
+    nbytes = tensor.numel() * tensor.element_size()
+    if heap.world_size == 1:
+        output.view(-1).copy_(tensor.view(-1))
+        return output
+    _launch(heap, "allgather", OP_ALLGATHER, 3, tensor.data_ptr(), output.data_ptr(), nbytes,
+            use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
+    return output
+
+
+def reduce_scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, op: str = "sum",
+                   implementation: str = "auto", *, ctx=None) -> torch.Tensor:
+    """``output = sum over ranks of tensor[rank * n:(rank + 1) * n]``."""
+    heap = _heap_of(heap, ctx)
+    if op != "sum":
+        raise ValueError(f"only op='sum' is supported, got {op!r}")
+    if implementation not in ("auto", "device"):
+        raise ValueError("implementation must be 'auto' or 'device' (there is no host reference path)")
+    _validate("tensor", tensor, heap)
+    _validate("output", output, heap)
+    if tensor.dtype not in _DTYPE_CODE:
+        raise TypeError(f"reduce_scatter supports float16, bfloat16 and float32, got {tensor.dtype}")
+    if tensor.numel() != output.numel() * heap.world_size or output.dtype != tensor.dtype:
+        raise ValueError(f"tensor must hold world_size * {output.numel()} elements of {output.dtype}")
+    nbytes = output.numel() * output.element_size()
+    if heap.world_size == 1:
+        output.view(-1).copy_(tensor.view(-1))
+        return output
+    _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype], tensor.data_ptr(),
+            output.data_ptr(), nbytes, use_multimem=_use_multimem(heap, nbytes),
+            elem_size=tensor.element_size())
+    return output
+
+
+def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> torch.Tensor:
+    """Every rank's ``tensor`` becomes ``root``'s (in place)."""
+    heap = _heap_of(heap, ctx)
+    _validate("tensor", tensor, heap)
+    if not 0 <= root < heap.world_size:
+        raise ValueError(f"root={root} out of range for world_size={heap.world_size}")
+    if heap.world_size == 1:
+        return tensor
+    nbytes = tensor.numel() * tensor.element_size()
+    _launch(heap, "broadcast", OP_BROADCAST, 3, tensor.data_ptr(), tensor.data_ptr(), nbytes,
+            root=root, use_multimem=_use_multimem(heap, nbytes), rv_extra=(root,),
+            elem_size=tensor.element_size())
+    return tensor
+
+
+def scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, root: int = 0,
+            ctx=None) -> torch.Tensor:
+    """Rank ``r`` receives ``root``'s ``tensor[r * n:(r + 1) * n]`` in ``output``."""
+    heap = _heap_of(heap, ctx)
+    _validate("tensor", tensor, heap)
+    _validate("output", output, heap)
+    if not 0 <= root < heap.world_size:
+        raise ValueError(f"root={root} out of range for world_size={heap.world_size}")
+    if tensor.numel() != output.numel() * heap.world_size or output.dtype != tensor.dtype:
+        raise ValueError(f"tensor must hold world_size * {output.numel()} elements of {output.dtype}")
+    nbytes = output.numel() * output.element_size()
+    if heap.world_size == 1:
+        output.view(-1).copy_(tensor.view(-1))
+        return output
+    _launch(heap, "scatter", OP_SCATTER, 3, tensor.data_ptr(), output.data_ptr(), nbytes, root=root,
+            rv_extra=(root,), elem_size=tensor.element_size())
+    return output

@@ -154,6 +154,11 @@ def _declare(lib: C.CDLL) -> None:
                                    u64, C.c_int64, u64, i32, u64, u64, u64],
         "tccl_prim_test": [i32, i32, i32, i32, i32, u64, u64, u64, u64, u64, u64, u32, u32, u64, u64,
                            u64],
+        "tccl_plan_tile_groups": [C.c_int64, C.c_int64, C.c_int64, C.c_int64, i32, i32, i32, i32,
+                                  C.c_int64, C.POINTER(C.c_int64), i32, C.POINTER(C.c_int64), i32,
+                                  C.POINTER(i32)],
+        "tccl_plan_group_table": [C.c_int64, C.c_int64, C.POINTER(C.c_int64), i32, i32, i32, i32,
+                                  C.POINTER(i32), C.c_int64],
         "tccl_bootstrap_allgather": [i32, i32, C.c_char_p, i32, u64, i32, C.POINTER(u64),
                                      C.POINTER(i32)],
     }

@@ -151,6 +151,19 @@ int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t worl
                            uint64_t stream);
 
 // --------------------------------------------------------------------------
+// TileGroup planner (csrc/plan/tile_group.cc, host only).  groups_out holds
+// (row_start, row_end, tile_count) triples.
+// --------------------------------------------------------------------------
+int tccl_plan_tile_groups(int64_t M, int64_t N, int64_t tile_bytes, int64_t target_group_tiles,
+                          int32_t max_groups, int32_t block_m, int32_t block_n, int32_t group_m,
+                          int64_t tau_min_bytes, const int64_t* row_boundaries,
+                          int32_t n_boundaries, int64_t* groups_out, int32_t capacity,
+                          int32_t* n_groups_out);
+int tccl_plan_group_table(int64_t M, int64_t N, const int64_t* groups, int32_t n_groups,
+                          int32_t block_m, int32_t block_n, int32_t group_m, int32_t* table_out,
+                          int64_t table_len);
+
+// --------------------------------------------------------------------------
 // Device-primitive test harness (csrc/kernels/prim_test.cu): one launch acts as
 // `rank` and applies one primitive.  op codes: 0 put, 1 get, 2 remote_store,
 // 3 remote_load, 4 signal, 5 wait, 6 poll, 7 signal_add, 8 wait_ge, 9 atomic

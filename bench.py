@@ -54,56 +54,16 @@ def parse_args():
 
 
 # ------------------------------------------------------------------ clocks
-class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+def ClockSampler(gpu_index: int):
+    """NVML sampler thread (SM clock, power, throttle reasons) for the timed region."""
+    sys.path.insert(0, ROOT) if ROOT not in sys.path else None
+    import importlib.util
 
-    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.proc = None
-        self.gpu_index = gpu_index
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.gpu_index), "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        sm, smax, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 8:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                smax.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[4:8]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        # "Under load" = the upper half of the samples (idle samples before/after are lower).
-        sm_sorted = sorted(sm)
-        load = sm_sorted[len(sm_sorted) // 2:]
-        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(smax),
-                "samples": len(sm), "reasons": sorted(reasons)}
+    spec = importlib.util.spec_from_file_location(
+        "_tccl_clocks", os.path.join(ROOT, "tileccl_b200", "utils", "clocks.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.ClockSampler(gpu_index)
 
 
 # ------------------------------------------------------------------ helpers

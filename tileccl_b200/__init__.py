@@ -108,9 +108,10 @@ class TileCCLContext:
         return self.allocate_tensor(_normalize_size(size), dtype)
 
     def zeros(self, *size, dtype):
-        t = self.empty(*size, dtype=dtype)
-        t.zero_()
-        return t
+        """Zero tensor on the heap.  Fresh heap memory is zero already (no memset is issued,
+        so a peer that writes into it early cannot be wiped out); see
+        ``SymmetricHeap.allocate_zeroed``."""
+        return self.require_heap().allocate_zeroed(_normalize_size(size), dtype)
 
     def randn(self, *size, dtype):
         import torch
@@ -126,8 +127,7 @@ class TileCCLContext:
         key = (name, shape, str(dtype))
         t = self._workspace_cache.get(key)
         if t is None:
-            t = self.empty(*shape, dtype=dtype)
-            t.zero_()
+            t = self.require_heap().allocate_zeroed(shape, dtype)
             self._workspace_cache[key] = t
         elif zero:
             t.zero_()

@@ -100,6 +100,10 @@ class GemmDesc(C.Structure):
         ("stage_local", C.c_uint64),
         ("a_gate", C.c_uint64),
         ("a_gate_rows_per_rank", C.c_int32),
+        ("ag_src", C.c_uint64),
+        ("ag_dst", C.c_uint64),
+        ("ag_mc_dst", C.c_uint64),
+        ("ag_bytes", C.c_uint64),
         ("scatter_col_begin", C.c_int32),
         ("scatter_col_end", C.c_int32),
         ("grid", C.c_int32),
@@ -119,6 +123,7 @@ class GemmPlanInfo(C.Structure):
         ("groups", C.c_int32),
         ("k_blocks", C.c_int32),
         ("smem_bytes", C.c_int32),
+        ("push_grid", C.c_int32),
     ]
 
 
@@ -154,6 +159,8 @@ def _declare(lib: C.CDLL) -> None:
                                    u64, C.c_int64, u64, i32, u64, u64, u64],
         "tccl_prim_test": [i32, i32, i32, i32, i32, u64, u64, u64, u64, u64, u64, u32, u32, u64, u64,
                            u64],
+        "tccl_push_region": [u64, u64, C.c_int64, i32, i32, i32, i32, i32, C.c_int64, u64, u32, u64,
+                             u32, i32, i32, u64, u64, u64],
         "tccl_plan_tile_groups": [C.c_int64, C.c_int64, C.c_int64, C.c_int64, i32, i32, i32, i32,
                                   C.c_int64, C.POINTER(C.c_int64), i32, C.POINTER(C.c_int64), i32,
                                   C.POINTER(i32)],

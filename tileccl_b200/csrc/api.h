@@ -105,6 +105,8 @@ typedef struct TcclGemmDesc {
   int32_t rot_m_tiles;
   uint64_t stage_local;
   uint64_t a_gate; int32_t a_gate_rows_per_rank;
+  // all-gather of the A operand pushed by the kernel itself (0 bytes = off)
+  uint64_t ag_src, ag_dst, ag_mc_dst, ag_bytes;
   int32_t scatter_col_begin, scatter_col_end;
   int32_t grid;                  // 0 = one CTA per SM
   uint64_t status;               // uint32[8] in device memory, may be 0
@@ -120,14 +122,17 @@ typedef struct TcclGemmPlanInfo {
   int32_t groups;            // TileGroups per owner sub-problem
   int32_t k_blocks;
   int32_t smem_bytes;
+  int32_t push_grid;         // CTAs of a launch that performs the all-gather push
 } TcclGemmPlanInfo;
 
 int tccl_gemm_plan_create(const TcclGemmDesc* desc, void** plan_out);
 int tccl_gemm_plan_info(void* plan, TcclGemmPlanInfo* out);
 // epoch: 1, 2, 3 ... per launch on the plan's signal block (ignored by mode 0).
-// tile_end < 0 runs to the last tile.
+// tile_end < 0 runs to the last tile.  flags: bit 0 = also wait for every peer's
+// TileGroups before the kernel exits (push-all), bit 1 = perform the all-gather push
+// of the A operand (an empty tile range is then allowed: push only).
 int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, int32_t tile_begin,
-                          int32_t tile_end, int32_t wait_incoming, uint64_t stream);
+                          int32_t tile_end, int32_t flags, uint64_t stream);
 int tccl_gemm_plan_destroy(void* plan);
 
 // Consumer side of the TileGroup protocol as its own launch: waits until
@@ -149,6 +154,17 @@ int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t worl
                            uint64_t mc_base, uint64_t heap_base, int64_t heap_stride,
                            uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
                            uint64_t stream);
+
+// --------------------------------------------------------------------------
+// Region push (csrc/kernels/push_region.cu): copies rows x row_bytes (pitch
+// ld_bytes) of this rank's heap to the same place in every peer's heap, band by
+// band; optionally waits for a local per-band counter (band_ready) first.
+// --------------------------------------------------------------------------
+int tccl_push_region(uint64_t region, uint64_t mc_region, int64_t ld_bytes, int32_t rows,
+                     int32_t row_bytes, int32_t band_rows, int32_t rank, int32_t world_size,
+                     int64_t heap_stride, uint64_t band_ready, uint32_t band_target_per_epoch,
+                     uint64_t counters, uint32_t epoch, int32_t phase_mask, int32_t grid,
+                     uint64_t status, uint64_t budget_ns, uint64_t stream);
 
 // --------------------------------------------------------------------------
 // TileGroup planner (csrc/plan/tile_group.cc, host only).  groups_out holds

@@ -141,6 +141,15 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   p.stage_local = d.stage_local;
   p.a_gate = d.a_gate;
   p.a_gate_rows_per_rank = d.a_gate_rows_per_rank > 0 ? d.a_gate_rows_per_rank : 1;
+  p.ag_src = d.ag_src;
+  p.ag_dst = d.ag_dst;
+  p.ag_mc_dst = d.ag_mc_dst;
+  p.ag_bytes = d.ag_bytes;
+  if (d.ag_bytes != 0) {
+    TCCL_CHECK_ARG(d.ag_bytes % 16 == 0 && d.ag_src % 16 == 0 && d.ag_dst % 16 == 0,
+                   "all-gather push needs 16-byte aligned buffers and size");
+    TCCL_CHECK_ARG(d.a_gate != 0 && d.heap_stride != 0, "all-gather push needs gate counters");
+  }
   p.scatter_col_begin = d.scatter_col_begin;
   p.scatter_col_end = d.scatter_col_end;
   p.status = d.status;
@@ -169,6 +178,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   info.tiles_per_owner = p.m_tiles_local * p.n_tiles_local;
   info.tiles_total = info.tiles_per_owner * p.owners;
   info.grid = grid < info.tiles_total ? grid : info.tiles_total;
+  info.push_grid = grid;
   info.m_tiles_local = p.m_tiles_local;
   info.n_tiles_local = p.n_tiles_local;
   info.groups = groups;
@@ -198,7 +208,7 @@ extern "C" int tccl_gemm_plan_info(void* plan, TcclGemmPlanInfo* out) {
 }
 
 extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gate_target,
-                                     int32_t tile_begin, int32_t tile_end, int32_t wait_incoming,
+                                     int32_t tile_begin, int32_t tile_end, int32_t flags,
                                      uint64_t stream) {
   TCCL_CHECK_ARG(plan_ != nullptr, "null plan");
   GemmPlan* plan = static_cast<GemmPlan*>(plan_);
@@ -206,15 +216,23 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   const int total = plan->info.tiles_total;
   if (tile_end < 0 || tile_end > total) tile_end = total;
   TCCL_CHECK_ARG(tile_begin >= 0 && tile_begin <= tile_end, "bad tile range");
-  if (tile_begin == tile_end) return kOk;
+  const bool ag_push = (flags & 2) != 0 && plan->params.ag_bytes != 0;
+  if (tile_begin == tile_end && !ag_push) return kOk;
   p.tile_begin = tile_begin;
   p.tile_end = tile_end;
   p.epoch = epoch;
   p.stage_parity = static_cast<int32_t>(epoch & 1u);
   p.a_gate_target = a_gate_target;
-  p.wait_incoming = wait_incoming;
+  p.wait_incoming = (flags & 1) ? 1 : 0;
+  p.do_ag_push = ag_push ? 1 : 0;
   int grid = plan->info.grid;
+  if (ag_push) {
+    // Every CTA contributes one arrival to the peers' gate counters, so the grid of a
+    // pushing launch is fixed (the consumers expect epoch * grid arrivals).
+    grid = plan->info.push_grid;
+  } else
   if (grid > tile_end - tile_begin) grid = tile_end - tile_begin;
+  if (grid < 1) grid = 1;
   TCCL_CHECK_CUDA(launch_fused_gemm(p, grid, reinterpret_cast<cudaStream_t>(stream)));
   return kOk;
 }

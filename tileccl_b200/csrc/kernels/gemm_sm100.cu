@@ -236,6 +236,45 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
     }
   } else if (warp == 3) {
+    // ------------------- all-gather push of the A operand ---------------------
+    if (p.ag_bytes != 0 && p.do_ag_push && p.world_size > 1) {
+      const char* src = reinterpret_cast<const char*>(p.ag_src);
+      const uint64_t nvec = p.ag_bytes >> 4;
+      const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 32 * 4;
+      for (uint64_t base = (static_cast<uint64_t>(blockIdx.x) * 32 + lane) * 4; base < nvec;
+           base += stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (base + j < nvec) v[j] = ld_stream_v4(src + ((base + j) << 4));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (base + j >= nvec) continue;
+          const uint64_t off = (base + j) << 4;
+          if (p.ag_mc_dst != 0) {
+            multimem_st_v4(reinterpret_cast<char*>(p.ag_mc_dst) + off, v[j]);
+          } else {
+            for (int d = 1; d < p.world_size; ++d) {
+              const int r = (p.rank + d) % p.world_size;
+              st_remote_v4(reinterpret_cast<char*>(static_cast<int64_t>(p.ag_dst) +
+                                                   static_cast<int64_t>(r - p.rank) * p.heap_stride) +
+                               off, v[j]);
+            }
+          }
+        }
+      }
+      fence_acq_rel_sys();
+      __syncwarp();
+      if (lane == 0) {
+        for (int d = 1; d < p.world_size; ++d) {
+          const int r = (p.rank + d) % p.world_size;
+          red_release_sys_add(
+              reinterpret_cast<uint32_t*>(static_cast<int64_t>(p.a_gate) +
+                                          static_cast<int64_t>(r - p.rank) * p.heap_stride) + p.rank,
+              1u);
+        }
+      }
+    }
     // ---------------------- incoming TileGroup waiter -------------------------
     if (p.mode == kModePushAll && p.wait_incoming && p.world_size > 1) {
       const int groups = (p.m_tiles_local + p.group_m_tiles - 1) / p.group_m_tiles;
@@ -263,6 +302,17 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     uint32_t acc = 0, acc_phase = 0;
     uint32_t buf = 0;
     bool ok = true;
+    bool pend_valid = false;      // lane 0: a tile whose signal has not been sent yet
+    int pend_owner = 0, pend_group = 0;
+    // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
+    auto send_signal = [&](int owner, int g) {
+      if (p.mode == kModeReduceScatter) {
+        red_release_sys_add(peer_counter(p, owner, 0, g), 1u);
+      } else {
+        for (int d = 1; d < p.world_size; ++d)
+          red_release_sys_add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, g), 1u);
+      }
+    };
     for (int t = first; ok && t < p.tile_end; t += step) {
       const TileCoord c = decode_tile(p, t);
       const int group = c.lm / p.group_m_tiles;
@@ -427,26 +477,49 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       const bool signals = p.world_size > 1 && p.sig_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
                             (p.mode == kModeReduceScatter && !reduce_here));
-      if (signals) {
-        if (lane == 0) tma_store_wait_all<0>();   // bulk stores of this thread are complete
+      if (p.push_mode == kPushTma) {
+        // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent one
+        // tile late: by then its bulk groups have completed while the current tile's are
+        // still in flight, so the NVLink round trip stays off the critical path.
+        if (lane == 0) {
+          if (pend_valid) {
+            if (n_chunks == 4) tma_store_wait_all<4>(); else tma_store_wait_all<2>();
+            fence_proxy_async_all();
+            send_signal(pend_owner, pend_group);
+          }
+          pend_valid = signals;
+          pend_owner = c.owner;
+          pend_group = group;
+        }
+      } else if (signals) {
+        if (lane == 0) tma_store_wait_all<0>();   // the local bulk store
         fence_proxy_async_all();
         fence_acq_rel_sys();                      // every lane's peer stores are ordered first
         __syncwarp();
-        if (lane == 0) {
-          if (p.mode == kModeReduceScatter) {
-            red_release_sys_add(peer_counter(p, c.owner, 0, group), 1u);
-          } else {
-            for (int d = 1; d < p.world_size; ++d)
-              red_release_sys_add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, group), 1u);
-          }
-        }
+        if (lane == 0) send_signal(c.owner, group);
+      }
+      // Plain GEMM feeding a consumer kernel on the same GPU (producer / consumer
+      // pattern): publish the slab on this rank's own TileGroup counter.
+      if (p.mode == kModeGemm && p.sig_local != 0) {
+        if (lane == 0) tma_store_wait_all<0>();
+        fence_proxy_async_all();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0)
+          red_release_sys_add(reinterpret_cast<uint32_t*>(p.sig_local) + group, 1u);
       }
       if (p.trace != 0 && q == 0 && lane == 0)
         reinterpret_cast<uint64_t*>(p.trace)[t] = globaltimer_ns();
 
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
-    if (lane == 0) tma_store_wait_all<0>();
+    if (lane == 0) {
+      tma_store_wait_all<0>();
+      if (pend_valid) {
+        fence_proxy_async_all();
+        send_signal(pend_owner, pend_group);
+      }
+    }
   }
 
   tcgen05_fence_before();

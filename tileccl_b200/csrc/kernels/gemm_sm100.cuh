@@ -80,6 +80,13 @@ struct alignas(64) FusedGemmParams {
   uint64_t a_gate;
   uint32_t a_gate_target;
   int32_t a_gate_rows_per_rank;
+  // All-gather of the A operand done by warp 3 of every CTA while the GEMM runs:
+  // this rank's `ag_bytes` at `ag_src` are copied to `ag_dst` in every peer's heap
+  // (ag_dst is the local address of the destination region), then each CTA adds 1
+  // to a_gate[rank] on every peer.  ag_bytes = 0 disables the role.
+  uint64_t ag_src, ag_dst, ag_mc_dst;
+  uint64_t ag_bytes;
+  int32_t do_ag_push;
   // column slice pushed by all-scatter
   int32_t scatter_col_begin, scatter_col_end;
   // diagnostics

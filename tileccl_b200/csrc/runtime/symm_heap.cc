@@ -264,6 +264,12 @@ extern "C" int tccl_heap_create_local(int32_t world_size, uint64_t size, const i
     }
   }
   for (int r = 0; r < world_size; ++r) {
+    // Fresh heap memory is all zeroes (see the multi-process path for why that matters).
+    TCCL_CHECK_CUDA(cudaSetDevice(devices[r]));
+    TCCL_CHECK_CUDA(cudaMemset(reinterpret_cast<void*>(win->base + r * win->stride), 0, win->stride));
+    TCCL_CHECK_CUDA(cudaDeviceSynchronize());
+  }
+  for (int r = 0; r < world_size; ++r) {
     Heap* h = new Heap();
     h->win = win;
     h->rank = r;
@@ -423,6 +429,11 @@ extern "C" int tccl_heap_create_multiprocess(int32_t rank, int32_t world_size, u
       if (win->mc_base) { d.cuMemAddressFree(win->mc_base, stride); win->mc_base = 0; }
     }
   }
+  // The heap starts out zeroed, and is zeroed BEFORE any peer can reach it: flags and
+  // counters carved out of fresh heap memory need no further initialisation (a memset
+  // issued later by the owner could wipe a signal that a faster peer has already sent).
+  TCCL_CHECK_CUDA(cudaMemset(reinterpret_cast<void*>(win->base + rank * stride), 0, stride));
+  TCCL_CHECK_CUDA(cudaDeviceSynchronize());
   if (world_size > 1 && !boot.barrier(7))
     return fail(kErrSystem, "bootstrap (final barrier): " + boot.error());
 

@@ -114,6 +114,10 @@ class FusedGemmSpec:
     stage_local: int = 0
     a_gate: int = 0
     a_gate_rows_per_rank: int = 0
+    ag_src: int = 0
+    ag_dst: int = 0
+    ag_mc_dst: int = 0
+    ag_bytes: int = 0
     scatter_col_begin: int = 0
     scatter_col_end: int = 0
     grid: int = 0
@@ -149,6 +153,8 @@ class FusedGemmPlan:
         d.rot_m_tiles = spec.rot_m_tiles
         d.stage_local = spec.stage_local
         d.a_gate, d.a_gate_rows_per_rank = spec.a_gate, spec.a_gate_rows_per_rank
+        d.ag_src, d.ag_dst, d.ag_mc_dst, d.ag_bytes = (spec.ag_src, spec.ag_dst, spec.ag_mc_dst,
+                                                       spec.ag_bytes)
         d.scatter_col_begin, d.scatter_col_end = spec.scatter_col_begin, spec.scatter_col_end
         d.grid = spec.grid
         d.status = spec.status_ptr
@@ -167,15 +173,17 @@ class FusedGemmPlan:
         self.groups = info.groups
         self.k_blocks = info.k_blocks
         self.smem_bytes = info.smem_bytes
+        self.push_grid = info.push_grid
 
     def launch(self, *, epoch: int = 1, a_gate_target: int = 0, tile_begin: int = 0,
-               tile_end: int = -1, wait_incoming: bool = False,
+               tile_end: int = -1, wait_incoming: bool = False, ag_push: bool = False,
                stream: Optional[torch.cuda.Stream] = None) -> None:
         global LAUNCH_COUNT
         s = stream if stream is not None else torch.cuda.current_stream()
         LAUNCH_COUNT += 1
         _native.call("tccl_gemm_plan_launch", self._handle, epoch & 0xFFFFFFFF,
-                     a_gate_target & 0xFFFFFFFF, tile_begin, tile_end, 1 if wait_incoming else 0,
+                     a_gate_target & 0xFFFFFFFF, tile_begin, tile_end,
+                     (1 if wait_incoming else 0) | (2 if ag_push else 0),
                      s.cuda_stream)
 
     def group_m_count(self, g: int) -> int:

@@ -154,6 +154,7 @@ class SymmetricHeap:
         self._group = _group
         self.local_group: Optional[LocalGroup] = None
         self._state: dict = {}
+        self._dirty = False  # True once reset_allocator() may have exposed used memory
         want_nvls = _want_nvls(nvls)
 
         if _handle is None:
@@ -262,17 +263,32 @@ class SymmetricHeap:
         flat = self._buffer[offset:offset + nbytes]
         return flat.view(dtype).view(shape)
 
-    def allocate_signal_buffer(self, n: int) -> torch.Tensor:
-        """Zeroed int32 flags / counters on the heap."""
-        t = self.allocate_tensor((int(n),), torch.int32)
-        t.zero_()
+    def allocate_zeroed(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor that is zero on every rank before any peer can write to it.
+
+        The heap is zeroed when it is created, before peers can reach it, and bump
+        allocations are never reused, so fresh memory is already zero and no memset
+        is issued: a memset by the owner could run after a faster peer has stored a
+        signal or data here and wipe it.  Only after ``reset_allocator`` may memory
+        be dirty; then every rank zeroes and the ranks meet in a barrier.
+        """
+        t = self.allocate_tensor(shape, dtype)
+        if self._dirty:
+            t.zero_()
+            self.barrier()
         return t
 
+    def allocate_signal_buffer(self, n: int) -> torch.Tensor:
+        """Zeroed int32 flags / counters on the heap (see ``allocate_zeroed``)."""
+        return self.allocate_zeroed((int(n),), torch.int32)
+
     def reset_allocator(self) -> None:
-        """Rewind the bump pointer.  Tensors handed out earlier become aliases."""
+        """Rewind the bump pointer.  Tensors handed out earlier become aliases; every
+        rank must have finished using them (call ``barrier()`` first)."""
         self._check_alive()
         _native.call("tccl_heap_reset", self._native.handle)
         self._ledger.reset()
+        self._dirty = True
 
     # ---------------------------------------------------------------- queries
     def get_heap_bases(self) -> torch.Tensor:

@@ -366,3 +366,104 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
         phases.append(_on_device(ctx, lambda: wait_groups(ctx, st["sig"], plan.groups,
                                                           st["per_epoch"], epoch)))
     run_phases(ctx, ("all_scatter", name, M, N, K, epoch), phases)
+
+
+# --------------------------------------------------------------------------
+# two-kernel all-scatter: GEMM kernel + region-push kernel
+# --------------------------------------------------------------------------
+_COLL_COUNTER_WORDS = 32
+
+
+def _comm_stream(ctx) -> torch.cuda.Stream:
+    s = ctx._state.get("comm_stream")
+    if s is None:
+        with torch.cuda.device(ctx.torch_device):
+            s = torch.cuda.Stream()
+        ctx._state["comm_stream"] = s
+    return s
+
+
+def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
+                   col_begin: int, col_end: int, overlapped: bool, b_is_nk: bool = False,
+                   use_multimem: Optional[bool] = None) -> None:
+    """All-scatter as two kernels: ``C = A @ B`` locally, then columns
+    ``[col_begin, col_end)`` of ``C`` are copied to every peer.
+
+    ``overlapped=False``: the push kernel follows the GEMM in stream order (bulk-synchronous).
+    ``overlapped=True``: the GEMM publishes each finished band of 128 rows on a local counter
+    and the push kernel, on a second stream, sends a band as soon as its counter is complete
+    (producer / consumer).
+    """
+    _require_2d("A", A, ctx)
+    _require_2d("B", B, ctx)
+    _require_2d("C", C, ctx)
+    K, N = _b_dims(B, b_is_nk)
+    M = A.shape[0]
+    ws, rank = ctx.world_size, ctx.rank
+    if ws > 1 and not ctx.is_symmetric(C):
+        raise ValueError("C must be allocated from the symmetric heap (ctx.zeros / ctx.empty)")
+    width = col_end - col_begin
+    if ws > 1 and (width <= 0 or (width * C.element_size()) % 16 or (col_begin * C.element_size()) % 16):
+        raise ValueError("the pushed column slice must start and end on 16-byte boundaries")
+    key = ("gemm_then_push", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, overlapped)
+    st = op_state(ctx, key)
+    m_tiles = -(-M // fg.BLOCK_M)
+    shared = op_state(ctx, ("gemm_then_push:sig", name, M, N, K, overlapped))
+    if "plan" not in st:
+        if ws > 1 and "counters" not in shared:
+            shared["counters"] = ctx.workspace(f"push:{name}:{M}x{N}x{K}:{overlapped}",
+                                               _COLL_COUNTER_WORDS, dtype=torch.int32)
+            shared["bands"] = (torch.zeros(m_tiles, dtype=torch.int32, device=ctx.torch_device)
+                               if overlapped else None)
+        bands = shared.get("bands")
+        st["plan"] = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_GEMM, dtype=A.dtype, a_ptr=A.data_ptr(), a_rows=M, lda=A.stride(0),
+            b_ptr=B.data_ptr(), b_cols=N, ldb=B.stride(0), k=K, sub_m=M, sub_n=N,
+            out_ptrs=[C.data_ptr()], ldo=C.stride(0), out_rows=M, out_cols=N, b_kmajor=b_is_nk,
+            rank=rank, world_size=ws, group_m_tiles=1,
+            sig_local=bands.data_ptr() if (bands is not None and ws > 1) else 0,
+            sig_stride=m_tiles, status_ptr=status_block(ctx).data_ptr(),
+            wait_budget_ns=wait_budget_ns()))
+    plan = st["plan"]
+    if ws == 1:
+        plan.launch()
+        return
+    shared["epoch"] += 1
+    epoch = shared["epoch"]
+    if use_multimem is None:
+        use_multimem = default_push_mode(ctx) == fg.PUSH_MULTIMEM
+    region = C.data_ptr() + col_begin * C.element_size()
+    mc_region = ctx.heap.multicast_ptr(region) if use_multimem else 0
+    bands = shared.get("bands")
+    band_ready = bands.data_ptr() if bands is not None else 0
+    per_band = plan.n_tiles_local * fg.EPILOGUE_SLABS
+    grid = max(1, min(m_tiles, 32))
+    counters = shared["counters"].data_ptr()
+    status = status_block(ctx).data_ptr()
+
+    def push(mask: int, stream=None):
+        def go():
+            s = stream if stream is not None else torch.cuda.current_stream()
+            _native.call("tccl_push_region", region, mc_region, C.stride(0) * C.element_size(), M,
+                         width * C.element_size(), fg.BLOCK_M, rank, ws, ctx.heap.stride,
+                         band_ready, per_band, counters, epoch & 0xFFFFFFFF, mask, grid, status,
+                         wait_budget_ns(), s.cuda_stream)
+        return go
+
+    gemm_launch = _on_device(ctx, lambda: plan.launch(epoch=epoch))
+    if ctx.emulated:
+        phases = [gemm_launch, _on_device(ctx, push(1)), _on_device(ctx, push(2)),
+                  _on_device(ctx, push(4))]
+    elif overlapped:
+        def both():
+            main = torch.cuda.current_stream()
+            comm = _comm_stream(ctx)
+            comm.wait_stream(main)          # operands and C are ready for this call
+            plan.launch(epoch=epoch)        # producer first ...
+            push(7, comm)()                 # ... consumer second, on its own stream
+            main.wait_stream(comm)
+        phases = [_on_device(ctx, both)]
+    else:
+        phases = [gemm_launch, _on_device(ctx, push(7))]
+    run_phases(ctx, ("gemm_then_push", name, M, N, K, overlapped, epoch), phases)

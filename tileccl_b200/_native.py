@@ -166,6 +166,11 @@ def _declare(lib: C.CDLL) -> None:
                                   C.POINTER(i32)],
         "tccl_plan_group_table": [C.c_int64, C.c_int64, C.POINTER(C.c_int64), i32, i32, i32, i32,
                                   C.POINTER(i32), C.c_int64],
+        "tccl_emul_gemm_allgather": [i32, i32, i32, i32, C.c_void_p, C.c_void_p, C.c_void_p, i32, i32,
+                                     i32, i32, i32, i32, i32, C.POINTER(i32)],
+        "tccl_emul_gemm_reducescatter": [i32, i32, i32, i32, C.c_void_p, C.c_void_p, C.c_void_p, i32,
+                                         i32, i32, i32, i32, i32, i32, C.POINTER(i32)],
+        "tccl_plan_tile_order": [i32, i32, i32, i32, i32, i32, C.POINTER(i32), i32],
         "tccl_bootstrap_allgather": [i32, i32, C.c_char_p, i32, u64, i32, C.POINTER(u64),
                                      C.POINTER(i32)],
     }

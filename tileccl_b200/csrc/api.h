@@ -180,6 +180,27 @@ int tccl_plan_group_table(int64_t M, int64_t N, const int64_t* groups, int32_t n
                           int64_t table_len);
 
 // --------------------------------------------------------------------------
+// CPU emulation of the multi-rank fused operators (csrc/cpu_emul/fake_device.cc):
+// one thread per rank, fp32, same tile order and TileGroup signalling as the GPU
+// kernels.  fault_kind: 0 none, 1 never signals, 2 signals every other tile only,
+// 3 rank absent, 4 rank late by fault_delay_ms.  status_out: int32[6] =
+// {code (0 ok, 2 = a wait timed out), where, rank, item, expected, observed}.
+// --------------------------------------------------------------------------
+int tccl_emul_gemm_allgather(int32_t world_size, int32_t M, int32_t N, int32_t K,
+                             const float* A_all, const float* B_all, float* C_all,
+                             int32_t block_m, int32_t block_n, int32_t group_m_tiles,
+                             int32_t fault_rank, int32_t fault_kind, int32_t fault_delay_ms,
+                             int32_t timeout_ms, int32_t* status_out);
+int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32_t N, int32_t K_total,
+                                 const float* A_all, const float* B_all, float* C_all,
+                                 int32_t block_m, int32_t block_n, int32_t group_m_tiles,
+                                 int32_t fault_rank, int32_t fault_kind, int32_t fault_delay_ms,
+                                 int32_t timeout_ms, int32_t* status_out);
+// (owner, tile row, tile column) of every tile in one rank's visiting order.
+int tccl_plan_tile_order(int32_t m_tiles_local, int32_t n_tiles_local, int32_t owners, int32_t rank,
+                         int32_t world_size, int32_t rot_m_tiles, int32_t* out, int32_t capacity);
+
+// --------------------------------------------------------------------------
 // Device-primitive test harness (csrc/kernels/prim_test.cu): one launch acts as
 // `rank` and applies one primitive.  op codes: 0 put, 1 get, 2 remote_store,
 // 3 remote_load, 4 signal, 5 wait, 6 poll, 7 signal_add, 8 wait_ge, 9 atomic

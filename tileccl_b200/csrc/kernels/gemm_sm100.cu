@@ -25,6 +25,7 @@
 #include "../device/ptx.cuh"
 #include "../device/tile_compute.cuh"
 #include "../device/tile_sync.cuh"
+#include "../plan/tile_order.h"
 
 namespace tileccl {
 
@@ -38,29 +39,20 @@ struct TileCoord {
 };
 
 __device__ __forceinline__ TileCoord decode_tile(const FusedGemmParams& p, int t) {
+  const TileOrderShape shape{p.m_tiles_local, p.n_tiles_local, p.owners, p.rank, p.world_size,
+                             p.rot_m_tiles};
+  const TileOrderEntry e = tile_order_decode(shape, t);
   TileCoord c;
-  const int tpo = p.m_tiles_local * p.n_tiles_local;
-  int oi = 0, rem = t;
-  if (p.owners > 1) {
-    oi = t / tpo;
-    rem = t - oi * tpo;
-  }
-  int lm = rem / p.n_tiles_local;
-  const int ln = rem - lm * p.n_tiles_local;
-  if (p.owners == 1 && p.rot_m_tiles != 0) {
-    lm += p.rot_m_tiles;
-    if (lm >= p.m_tiles_local) lm -= p.m_tiles_local;
-  }
-  c.owner = p.owners > 1 ? (p.rank + 1 + oi) % p.world_size : p.rank;
-  c.lm = lm;
-  c.a_row0 = lm * kBM;
-  c.b_col0 = ln * kBN;
+  c.owner = e.owner;
+  c.lm = e.lm;
+  c.a_row0 = e.lm * kBM;
+  c.b_col0 = e.ln * kBN;
   if (p.owners > 1) {
     if (p.split_axis == 0) c.a_row0 += c.owner * p.a_rows_per_owner;
     else c.b_col0 += c.owner * p.b_cols_per_owner;
   }
-  c.out_y = lm * kBM;
-  c.out_x = p.epi_op == kEpiSiluGate ? ln * (kBN / 2) : ln * kBN;
+  c.out_y = e.lm * kBM;
+  c.out_x = p.epi_op == kEpiSiluGate ? e.ln * (kBN / 2) : e.ln * kBN;
   return c;
 }
 

@@ -1,0 +1,93 @@
+"""CPU plumbing: world_size ranks emulated as threads of one process (fp32), checked
+against torch, plus host-side fault injection (no GPU involved)."""
+
+import pytest
+import torch
+
+from tileccl_b200 import emulation as em
+
+
+def _inputs(ws, M, N, K, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return g, (lambda r, c: torch.randn(r, c, generator=g) / K ** 0.5)
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+def test_gemm_allgather_semantics(ws):
+    M, N, K = 512, 256, 128
+    _, rnd = _inputs(ws, M, N, K)
+    A = [rnd(M // ws, K) for _ in range(ws)]
+    B = [rnd(K, N) for _ in range(ws)]
+    C, st = em.gemm_allgather(A, B, block_m=64, block_n=64)
+    assert st.ok
+    ref = torch.cat([A[r] @ B[r] for r in range(ws)])
+    for c in C:
+        torch.testing.assert_close(c, ref, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("ws", [1, 2, 4, 8])
+def test_gemm_reducescatter_semantics(ws):
+    M, N, K = 512, 256, 128
+    _, rnd = _inputs(ws, M, N, K, seed=1)
+    A = [rnd(M, K // ws) for _ in range(ws)]
+    B = [rnd(K // ws, N) for _ in range(ws)]
+    C, st = em.gemm_reducescatter(A, B, block_m=64, block_n=64, group_m_tiles=2)
+    assert st.ok
+    full = sum(A[r] @ B[r] for r in range(ws))
+    for r in range(ws):
+        torch.testing.assert_close(C[r], full[r * M // ws:(r + 1) * M // ws], rtol=1e-4, atol=1e-5)
+
+
+def test_ragged_tiles():
+    ws, M, N, K = 2, 200, 72, 40
+    _, rnd = _inputs(ws, M, N, K, seed=2)
+    A = [rnd(M // ws, K) for _ in range(ws)]
+    B = [rnd(K, N) for _ in range(ws)]
+    C, _ = em.gemm_allgather(A, B, block_m=64, block_n=32)
+    torch.testing.assert_close(C[1], torch.cat([A[r] @ B[r] for r in range(ws)]), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("fault", ["no_signal", "short_signal", "absent"])
+def test_faulty_rank_makes_peers_time_out_allgather(fault):
+    ws, M, N, K = 2, 256, 128, 32
+    _, rnd = _inputs(ws, M, N, K)
+    A = [rnd(M // ws, K) for _ in range(ws)]
+    B = [rnd(K, N) for _ in range(ws)]
+    _, st = em.gemm_allgather(A, B, block_m=64, block_n=64, fault_rank=1, fault=fault,
+                              timeout_ms=100, raise_on_timeout=False)
+    assert st.timed_out and st.rank == 0 and st.observed < st.expected
+    with pytest.raises(em.EmulatedTimeout):
+        em.gemm_allgather(A, B, block_m=64, block_n=64, fault_rank=1, fault=fault, timeout_ms=50)
+
+
+@pytest.mark.parametrize("fault", ["no_signal", "short_signal", "absent"])
+def test_faulty_rank_makes_owner_time_out_reducescatter(fault):
+    ws, M, N, K = 4, 256, 128, 64
+    _, rnd = _inputs(ws, M, N, K)
+    A = [rnd(M, K // ws) for _ in range(ws)]
+    B = [rnd(K // ws, N) for _ in range(ws)]
+    _, st = em.gemm_reducescatter(A, B, block_m=64, block_n=64, fault_rank=2, fault=fault,
+                                  timeout_ms=100, raise_on_timeout=False)
+    assert st.timed_out and st.rank != 2 and st.where == 40
+
+
+def test_late_rank_within_budget_is_fine():
+    ws, M, N, K = 2, 256, 128, 32
+    _, rnd = _inputs(ws, M, N, K)
+    A = [rnd(M // ws, K) for _ in range(ws)]
+    B = [rnd(K, N) for _ in range(ws)]
+    C, st = em.gemm_allgather(A, B, block_m=64, block_n=64, fault_rank=0, fault="late",
+                              fault_delay_ms=100, timeout_ms=3000)
+    assert st.ok
+    _, st = em.gemm_allgather(A, B, block_m=64, block_n=64, fault_rank=0, fault="late",
+                              fault_delay_ms=400, timeout_ms=50, raise_on_timeout=False)
+    assert st.timed_out
+
+
+def test_tile_order_own_tiles_last():
+    order = em.tile_order(2, 2, owners=4, rank=1, world_size=4)
+    owners = [o for o, _, _ in order]
+    assert owners == [2] * 4 + [3] * 4 + [0] * 4 + [1] * 4       # rank+1 first, self last
+    assert [(lm, ln) for _, lm, ln in order[:4]] == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    rot = em.tile_order(4, 1, rot_m_tiles=2)
+    assert [lm for _, lm, _ in rot] == [2, 3, 0, 1]

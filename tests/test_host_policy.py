@@ -1,0 +1,156 @@
+"""Host-side policy objects: contracts, pattern selection, feature gates, support matrix,
+profiling helpers, timeline (CPU only)."""
+
+import json
+import types
+
+import pytest
+import torch
+
+import tileccl_b200
+from tileccl_b200.patterns import (PATTERN_CLASSES, auto_select, resolve_dual_role_scheduler,
+                                   resolve_pattern_execution, resolve_stage_role_scheduler,
+                                   resolve_tile_collective_execution,
+                                   resolve_tile_collective_runtime)
+from tileccl_b200.patterns.auto_select import HardwareInfo, estimate_pattern_times
+from tileccl_b200.planning.runtime import TimelineEvent, TimelineRecorder, events_from_device_trace
+from tileccl_b200.utils import feature_gates as fgates
+from tileccl_b200.utils.profiling import (CommHeatmap, OverlapTimeline, bandwidth_to_normalized,
+                                          format_benchmark_table)
+
+
+def _t(r, c):
+    return torch.empty(r, c)
+
+
+def test_pattern_contract_full_full_and_shard_shard():
+    spec = resolve_pattern_execution(_t(64, 32), _t(32, 128), _t(64, 128), rank=1, world_size=4)
+    assert (spec.M, spec.K, spec.full_N, spec.local_N) == (64, 32, 128, 32)
+    assert (spec.scatter_src_col_offset, spec.scatter_cols, spec.scatter_dst_leading_dim,
+            spec.scatter_dst_col_offset) == (32, 32, 128, 32)
+    assert spec.rhs_layout == spec.output_layout == "full"
+    sh = resolve_pattern_execution(_t(64, 32), _t(32, 32), _t(64, 32), rank=1, world_size=4,
+                                   full_N=128, b_layout="shard", c_layout="shard")
+    assert sh.scatter_dst_col_offset == 0 and sh.scatter_dst_leading_dim == 32
+    assert json.dumps(sh.to_dict())
+
+
+@pytest.mark.parametrize("kw", [
+    dict(b_layout="full"),                                   # layouts must come together
+    dict(b_layout="full", c_layout="shard"),                 # mixed layouts are not a pattern contract
+    dict(b_layout="diag", c_layout="full"),
+    dict(full_N=130),                                        # not divisible by world size
+])
+def test_pattern_contract_rejections(kw):
+    with pytest.raises(ValueError):
+        resolve_pattern_execution(_t(64, 32), _t(32, 128), _t(64, 128), rank=0, world_size=4, **kw)
+
+
+def test_pattern_contract_shape_errors():
+    with pytest.raises(ValueError):
+        resolve_pattern_execution(_t(64, 32), _t(31, 128), _t(64, 128), rank=0, world_size=1)
+    with pytest.raises(ValueError):
+        resolve_pattern_execution(_t(64, 32), _t(32, 128), _t(63, 128), rank=0, world_size=1)
+    with pytest.raises(ValueError):
+        resolve_pattern_execution(torch.empty(4), _t(32, 128), _t(64, 128), rank=0, world_size=1)
+
+
+def test_auto_select_rules():
+    assert auto_select("gemm_allscatter", 128, 4096, 4096, world_size=8) is PATTERN_CLASSES["bulk_sync"]
+    cls = auto_select("gemm_allscatter", 8192, 4096, 4096, world_size=8)
+    assert cls in PATTERN_CLASSES.values() and cls is not PATTERN_CLASSES["bulk_sync"]
+    with pytest.raises(ValueError):
+        auto_select("gemm_everything", 1, 1, 1)
+    ctx = types.SimpleNamespace(rank=0, world_size=8, topology=None)
+    inst = auto_select("gemm_allscatter", 8192, 4096, 4096, world_size=8, ctx=ctx)
+    assert isinstance(inst, tuple(PATTERN_CLASSES.values())) and inst.ctx is ctx
+    times = estimate_pattern_times(8192, 4096, 2048, 8, HardwareInfo())
+    assert times["bulk_sync"] > times["wg_specialized"] > 0
+
+
+def test_role_schedulers():
+    d = resolve_dual_role_scheduler(148)
+    assert d.comm_sms == 0 and d.compute_sms == 148 and d.comm_warps_per_cta == 4
+    d2 = resolve_dual_role_scheduler(148, comm_sm_fraction=0.2)
+    assert d2.comm_sms == 29 and d2.compute_sms + d2.comm_sms == 148
+    assert resolve_dual_role_scheduler(148, compute_sms=100, comm_sms=20).policy == "explicit"
+    with pytest.raises(ValueError):
+        resolve_dual_role_scheduler(148, compute_sms=140, comm_sms=20)
+    s = resolve_stage_role_scheduler(148)
+    assert s.gather_sms == s.scatter_sms == 0 and s.compute_sms == 148
+    ex = resolve_tile_collective_execution("gemm_reducescatter", total_sms=148, rows=2048, world_size=8)
+    assert ex.slot_count == 16 and ex.runtime.wait_mode == "wait_ge"
+    assert len(ex.slot_workspace_names(0)) == 8 and json.dumps(ex.to_dict())
+    with pytest.raises(ValueError):
+        resolve_tile_collective_runtime("nope")
+
+
+def test_feature_gates(monkeypatch):
+    surface = fgates.multiprocess_device_validated_public_surface()
+    assert surface["world_sizes"] == [1, 2, 4, 8] and "vmm_fd" in surface["transports"]
+    assert fgates.multiprocess_device_collectives_enabled()
+    assert fgates.multiprocess_device_remote_access_runtime_supported(transport_strategy="vmm_fd", world_size=8)
+    assert not fgates.multiprocess_device_remote_access_runtime_supported(transport_strategy="vmm_fd", world_size=3)
+    assert "world_size 3" in fgates.multiprocess_device_remote_access_detail(
+        transport_strategy="vmm_fd", world_size=3)
+    monkeypatch.delenv(fgates.FORCE_MULTIPROCESS_TRANSPORT_ENV, raising=False)
+    assert fgates.forced_multiprocess_transport() is None
+    monkeypatch.setenv(fgates.FORCE_MULTIPROCESS_TRANSPORT_ENV, "ctypes_ipc")
+    assert fgates.forced_multiprocess_transport() == "vmm_fd"
+    monkeypatch.setenv(fgates.FORCE_MULTIPROCESS_TRANSPORT_ENV, "carrier_pigeon")
+    with pytest.raises(ValueError):
+        fgates.forced_multiprocess_transport()
+
+
+def test_support_matrix_without_gpu_is_consistent():
+    ctx = tileccl_b200.init(rank=0, world_size=1, force_backend=True)
+    m = ctx.support_matrix()
+    d = m.to_dict()
+    assert d["context"]["world_size"] == 1 and not d["context"]["has_heap"]
+    assert sum(m.summary().values()) == sum(len(d[k]) for k in
+                                            ("ops", "contracts", "execution_paths", "collectives", "memory"))
+    assert d["contracts"]["gemm_allscatter.shard/full"]["state"] == "unsupported"
+    assert ctx.runtime_metadata()["has_heap"] is False
+    with pytest.raises(RuntimeError):
+        ctx.require_heap()
+
+
+def test_profiling_helpers(tmp_path):
+    tl = OverlapTimeline()
+    tl.record("compute", "gemm", 0.0, 10.0)
+    tl.record("comm", "push", 4.0, 12.0)
+    o = tl.compute_overlap()
+    assert o["overlap_ms"] == pytest.approx(6.0) and o["overlap_ratio"] == pytest.approx(0.75)
+    assert o["wall_ms"] == pytest.approx(12.0)
+    with pytest.raises(ValueError):
+        tl.record("comm", "bad", 2.0, 1.0)
+    hm = CommHeatmap(2)
+    hm.record(0, 1, 100)
+    hm.record(1, 0, 50)
+    assert hm.get_traffic_matrix() == [[0, 100], [50, 0]] and hm.balance()["max_min_send_ratio"] == 2.0
+    with pytest.raises(ValueError):
+        hm.record(0, 2, 1)
+    bw = bandwidth_to_normalized(900e9 * 1e-3, 1.0, 900.0)
+    assert bw["gbps"] == pytest.approx(900.0) and bw["fraction_of_peak"] == pytest.approx(1.0)
+    assert "name" in format_benchmark_table([{"name": "a", "ms": 1.0}])
+    tl.export_json(tmp_path / "t.json")
+    hm.export_json(tmp_path / "h.json")
+
+
+def test_timeline_schema_roundtrip(tmp_path):
+    rec = TimelineRecorder(benchmark="gate1", path_name="fused", metadata={"ws": 2})
+    rec.record_span(name="gemm", lane="rank0/compute", start_ms=0.0, end_ms=1.5, category="compute", rank=0)
+    rec.record_marker(name="group0", lane="rank0/signal", at_ms=0.4, rank=0)
+    rec.extend(events_from_device_trace([0, 2_000_000, 1_000_000], lane="rank1/tiles", rank=1))
+    payload = rec.to_payload()
+    assert payload["schema"] == "tileccl.timeline.v1"
+    assert payload["authenticity_checks"] == {"event_count": 4, "all_events_have_source": True,
+                                              "all_events_have_nonnegative_duration": True}
+    assert payload["lane_order"] == ["rank0/compute", "rank0/signal", "rank1/tiles"]
+    rec.write_json(tmp_path / "timeline.json")
+    again = TimelineRecorder.from_payload(json.loads((tmp_path / "timeline.json").read_text()))
+    assert [e.name for e in again.events] == [e.name for e in rec.events]
+    with pytest.raises(ValueError):
+        TimelineEvent("x", "l", 2.0, 1.0)
+    with pytest.raises(ValueError):
+        TimelineEvent("x", "l", 0.0, 1.0, source="")

@@ -1,0 +1,156 @@
+"""Tile collectives and device primitives on ranks driven by one process."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(got, ref):
+    return (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-9)
+
+
+@pytest.fixture(params=[2, 4, 8])
+def ctxs(request):
+    import tileccl_b200 as tccl
+
+    cs = tccl.init_local(request.param, 256 << 20)
+    yield cs
+    for d in range(torch.cuda.device_count()):
+        torch.cuda.synchronize(d)
+    for c in cs:
+        c.heap.cleanup()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("numel", [1024, 8198, 300_000, 2_000_000])
+def test_all_five_collectives(ctxs, dtype, numel):
+    from tileccl_b200 import ops
+    from tileccl_b200.primitives import collectives as coll
+
+    ws = len(ctxs)
+    n = numel // ws * ws
+    tol = 2e-2 if dtype is not torch.float32 else 1e-5
+    xs = [c.randn(n, dtype=dtype) for c in ctxs]
+    orig = [x.clone() for x in xs]
+    total = sum(o.float().cpu() for o in orig)
+    for rep in range(2):                                  # second call reuses counters / staging
+        for r, c in enumerate(ctxs):
+            xs[r].copy_(orig[r])
+        for r, c in enumerate(ctxs):
+            ops.allreduce(xs[r], ctx=c)
+        for r in range(ws):
+            assert _rel(xs[r].cpu(), total) < tol
+    outs = [c.zeros(n * ws, dtype=dtype) for c in ctxs]
+    for r, c in enumerate(ctxs):
+        ops.allgather(orig[r], outs[r], ctx=c) if c.is_symmetric(orig[r]) else ops.allgather(xs[r].copy_(orig[r]), outs[r], ctx=c)
+    cat = torch.cat([o.cpu() for o in orig])
+    for r in range(ws):
+        assert torch.equal(outs[r].cpu(), cat)
+    src = [c.randn(n, dtype=dtype) for c in ctxs]
+    part = [c.zeros(n // ws, dtype=dtype) for c in ctxs]
+    for r, c in enumerate(ctxs):
+        ops.reduce_scatter(src[r], part[r], ctx=c)
+    tot = sum(s.float().cpu() for s in src)
+    for r in range(ws):
+        assert _rel(part[r].cpu(), tot[r * (n // ws):(r + 1) * (n // ws)]) < tol
+    root = ws - 1
+    want = src[root].cpu().clone()
+    for r, c in enumerate(ctxs):
+        ops.broadcast(src[r], ctx=c, root=root)
+    for r in range(ws):
+        assert torch.equal(src[r].cpu(), want)
+    sc = [c.zeros(n // ws, dtype=dtype) for c in ctxs]
+    for r, c in enumerate(ctxs):
+        ops.scatter(xs[r], sc[r], ctx=c, root=0)
+    root_data = xs[0].cpu()
+    for r in range(ws):
+        assert torch.equal(sc[r].cpu(), root_data[r * (n // ws):(r + 1) * (n // ws)])
+    for c in ctxs:
+        coll.check_status(c.heap)
+
+
+def test_allreduce_plan_metadata(ctxs):
+    from tileccl_b200 import ops
+
+    c = ctxs[0]
+    small = ops.build_allreduce_plan(c.zeros(1024, dtype=torch.float16), ctx=c)
+    big = ops.build_allreduce_plan(c.zeros(1 << 20, dtype=torch.float16), ctx=c)
+    assert small.implementation == "device_one_shot" and small.message_regime == "latency"
+    assert big.implementation == "device_two_shot" and big.message_regime == "bandwidth"
+    assert big.to_dict()["num_chunks"] == len(ctxs)
+    with pytest.raises(ValueError):
+        ops.build_allreduce_plan(c.zeros(8, dtype=torch.float16), ctx=c, op="max")
+    with pytest.raises(ValueError):
+        ops.allgather(torch.zeros(8, device=c.torch_device), c.zeros(8 * len(ctxs), dtype=torch.float32), ctx=c)
+
+
+def test_primitives_put_get_signal_wait_atomics(ctxs):
+    from tileccl_b200.primitives import harness
+
+    h0, h1 = ctxs[0].heap, ctxs[1].heap
+    a0 = h0.allocate_tensor((1024,), torch.int32)
+    a1 = h1.allocate_tensor((1024,), torch.int32)
+    f0 = h0.allocate_signal_buffer(8)
+    f1 = h1.allocate_signal_buffer(8)
+    a0.copy_(torch.arange(1024, dtype=torch.int32))
+    a1.zero_()
+    assert harness.translate(h0, a0.data_ptr(), 1) == a1.data_ptr()
+    harness.run(h0, "put", peer=1, a=a0.data_ptr(), b=a0.data_ptr(), nbytes=4096)
+    assert torch.equal(a1.cpu(), a0.cpu())
+    a1.mul_(2)
+    harness.run(h0, "get", peer=1, a=a0.data_ptr(), b=a0.data_ptr(), nbytes=4096)
+    assert torch.equal(a0.cpu(), a1.cpu())
+    a0.add_(1)
+    harness.run(h0, "remote_store", peer=1, a=a0.data_ptr(), b=a0.data_ptr(), nbytes=4096)
+    assert torch.equal(a1.cpu(), a0.cpu())
+    a1.add_(5)
+    harness.run(h0, "remote_load", peer=1, a=a0.data_ptr(), b=a0.data_ptr(), nbytes=4096)
+    assert torch.equal(a0.cpu(), a1.cpu())
+    # flags: signal on the peer, consuming wait, bounded time-out afterwards
+    harness.run(h0, "signal", peer=1, a=f0.data_ptr())
+    assert f1[0].item() == 1
+    assert harness.run(h1, "poll", a=f1.data_ptr())[0] == 1 and f1[0].item() == 1
+    assert harness.run(h1, "wait", a=f1.data_ptr())[0] == 1 and f1[0].item() == 0
+    assert harness.run(h1, "wait", a=f1.data_ptr(), budget_us=2000)[0] == 0      # nothing sets it
+    assert harness.run(h1, "try_wait", a=f1.data_ptr(), value=64)[0] == 0
+    # counters
+    harness.run(h0, "signal_add", peer=1, a=f0.data_ptr() + 4, value=3)
+    assert harness.run(h1, "wait_ge", a=f1.data_ptr() + 4, value=3)[:1] == [1]
+    assert harness.run(h1, "wait_ge", a=f1.data_ptr() + 4, value=5, budget_us=2000)[:2] == [0, 3]
+    # remote atomics on counter word 1 (currently 3)
+    for name, val, expect in (("add", 5, 8), ("max", 100, 100), ("min", 7, 7), ("or", 8, 15),
+                              ("and", 12, 12), ("xor", 5, 9), ("xchg", 42, 42)):
+        harness.atomic(h0, name, f0.data_ptr() + 4, val, 1)
+        assert f1[1].item() == expect, name
+    assert harness.atomic(h0, "cas", f0.data_ptr() + 4, 42, 1, value2=77) == 42 and f1[1].item() == 77
+    assert harness.atomic(h0, "cas", f0.data_ptr() + 4, 1, 1, value2=5) == 77 and f1[1].item() == 77
+    # credits: a pool of 2 on rank 1, a third acquire times out, a remote release refills it
+    f1[2] = 2
+    assert harness.run(h1, "credit", a=f1.data_ptr() + 8, sub_op=0)[0] == 1
+    assert harness.run(h1, "credit", a=f1.data_ptr() + 8, sub_op=0)[0] == 1
+    assert harness.run(h1, "credit", a=f1.data_ptr() + 8, sub_op=0, budget_us=2000)[0] == 0
+    harness.run(h0, "credit", peer=1, a=f0.data_ptr() + 8, sub_op=1)
+    assert harness.run(h1, "credit", a=f1.data_ptr() + 8, sub_op=0)[0] == 1
+
+
+def test_device_timeout_is_reported_and_gpu_stays_usable(ctxs):
+    """A wait that nothing satisfies returns an error status; the context keeps working."""
+    from tileccl_b200.kernels.fused_gemm import TileCCLTimeoutError
+    from tileccl_b200.ops import _fused
+
+    c = ctxs[0]
+    sig = c.workspace("never_signalled", len(ctxs) * _fused.MAX_GROUPS, dtype=torch.int32)
+    per_epoch = torch.ones(1, dtype=torch.int32, device=c.torch_device)
+    import os
+    os.environ["TILECCL_WAIT_BUDGET_US"] = "3000"
+    try:
+        with torch.cuda.device(c.torch_device):
+            _fused.wait_groups(c, sig, 1, per_epoch, 1)
+        with pytest.raises(TileCCLTimeoutError, match="peer signal"):
+            _fused.check_status(c)
+    finally:
+        del os.environ["TILECCL_WAIT_BUDGET_US"]
+    x = torch.ones(16, device=c.torch_device)
+    assert float((x * 2).sum()) == 32.0
+    _fused.check_status(c)          # status was cleared

@@ -294,8 +294,9 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     uint32_t acc = 0, acc_phase = 0;
     uint32_t buf = 0;
     bool ok = true;
-    bool pend_valid = false;      // lane 0: a tile whose signal has not been sent yet
-    int pend_owner = 0, pend_group = 0;
+    // lane 0: the last two tiles whose signals have not been sent yet ([0] = older)
+    bool pend_valid[2] = {false, false};
+    int pend_owner[2] = {0, 0}, pend_group[2] = {0, 0};
     // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
     auto send_signal = [&](int owner, int g) {
       if (p.mode == kModeReduceScatter) {
@@ -470,18 +471,22 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
                             (p.mode == kModeReduceScatter && !reduce_here));
       if (p.push_mode == kPushTma) {
-        // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent one
-        // tile late: by then its bulk groups have completed while the current tile's are
-        // still in flight, so the NVLink round trip stays off the critical path.
+        // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent two
+        // tiles late: by then its bulk groups have completed (data has reached the peer)
+        // while the groups of the two most recent tiles are still in flight, so neither
+        // the NVLink round trip nor the queueing behind other SMs' stores stalls this warp.
         if (lane == 0) {
-          if (pend_valid) {
-            if (n_chunks == 4) tma_store_wait_all<4>(); else tma_store_wait_all<2>();
+          if (pend_valid[0]) {
+            if (n_chunks == 4) tma_store_wait_all<8>(); else tma_store_wait_all<4>();
             fence_proxy_async_all();
-            send_signal(pend_owner, pend_group);
+            send_signal(pend_owner[0], pend_group[0]);
           }
-          pend_valid = signals;
-          pend_owner = c.owner;
-          pend_group = group;
+          pend_valid[0] = pend_valid[1];
+          pend_owner[0] = pend_owner[1];
+          pend_group[0] = pend_group[1];
+          pend_valid[1] = signals;
+          pend_owner[1] = c.owner;
+          pend_group[1] = group;
         }
       } else if (signals) {
         if (lane == 0) tma_store_wait_all<0>();   // the local bulk store
@@ -507,10 +512,9 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     }
     if (lane == 0) {
       tma_store_wait_all<0>();
-      if (pend_valid) {
-        fence_proxy_async_all();
-        send_signal(pend_owner, pend_group);
-      }
+      fence_proxy_async_all();
+      for (int i = 0; i < 2; ++i)
+        if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i]);
     }
   }
 

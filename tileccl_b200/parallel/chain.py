@@ -127,8 +127,7 @@ def allgather_gemm(ctx, input_shard: torch.Tensor, W: torch.Tensor, output: torc
     _fused.reduce_scatter(ctx, "ag_gemm_rs", input_shard, w_rows, local, split_axis=0)
     from ..primitives import collectives
 
-    # Gather the reduced row blocks: every rank's block already sits at its place in `output`.
-    staging = ctx.workspace(f"ag_gemm_rs:block:{mloc}x{N}:{output.dtype}", mloc * N, dtype=output.dtype)
-    staging.view(mloc, N).copy_(local)
-    collectives.allgather(staging, output.view(-1), ctx.heap)
+    # Gather the reduced row blocks in place: every rank's block already sits at its own
+    # position in `output`, so the block itself is the all-gather source.
+    collectives.allgather(local.reshape(-1), output.view(-1), ctx.heap)
     return output

@@ -1,0 +1,137 @@
+"""Worker of tests/test_gpu_multiprocess.py: one rank per GPU under torchrun.
+
+Checks the multi-process heap (fd exchange, NVLS when available), the fused
+operators in every push mode, the collectives with and without NVLS, and the
+TP-MLP block, against references built with NCCL all-gathers of the inputs.
+Exits non-zero on the first mismatch (so that torchrun tears all ranks down)."""
+
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main() -> int:
+    rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    import tileccl_b200 as tccl
+    from tileccl_b200 import ops
+    from tileccl_b200.kernels import fused_gemm as fg
+    from tileccl_b200.models.tp_mlp import TPMLP
+    from tileccl_b200.ops import _fused
+    from tileccl_b200.primitives import collectives as coll
+
+    ctx = tccl.init(heap_size=1 << 30)
+    assert ctx.heap.mode == "multiprocess" and ctx.heap.transport_strategy == "vmm_fd"
+
+    def gather(t):
+        out = [torch.empty_like(t) for _ in range(ws)]
+        dist.all_gather(out, t.contiguous())
+        return out
+
+    def check(name, got, ref, tol):
+        err = (got.float() - ref.float()).abs().max().item() / (ref.float().abs().max().item() + 1e-9)
+        if not err < tol:
+            raise AssertionError(f"[rank {rank}] {name}: rel err {err:.3e} >= {tol}")
+
+    torch.manual_seed(100 + rank)
+    modes = [fg.PUSH_STORES, fg.PUSH_TMA] + ([fg.PUSH_MULTIMEM] if ctx.heap.has_multicast else [])
+    for dtype, tol in ((torch.float16, 5e-3), (torch.bfloat16, 2e-2)):
+        for push in modes:
+            M, N, K = 256 * ws, 1024, 512
+            mloc = M // ws
+            A = ctx.randn(mloc, K, dtype=dtype)
+            A.mul_(K ** -0.5)
+            B = ctx.randn(K, N, dtype=dtype)
+            C = ctx.zeros(M, N, dtype=dtype)
+            for _ in range(3):
+                _fused.push_all(ctx, f"t_ag_{push}", A, B, C, region_row0=rank * mloc, region_col0=0,
+                                push_mode=push)
+            ops.check_status(ctx)
+            As, Bs = gather(A), gather(B)
+            check(f"gemm_allgather push{push} {dtype}", C,
+                  torch.cat([As[r].float() @ Bs[r].float() for r in range(ws)]), tol)
+            dist.barrier()
+            if push == fg.PUSH_MULTIMEM:
+                continue
+            A2 = ctx.randn(M, K // ws, dtype=dtype)
+            A2.mul_(K ** -0.5)
+            B2 = ctx.randn(K // ws, N, dtype=dtype)
+            C2 = torch.zeros(mloc, N, dtype=dtype, device=dev)
+            for _ in range(4):
+                _fused.reduce_scatter(ctx, f"t_rs_{push}", A2, B2, C2, split_axis=0, push_mode=push)
+            ops.check_status(ctx)
+            A2s, B2s = gather(A2), gather(B2)
+            full = sum(A2s[r].float() @ B2s[r].float() for r in range(ws))
+            check(f"gemm_reducescatter push{push} {dtype}", C2, full[rank * mloc:(rank + 1) * mloc], tol)
+            dist.barrier()
+
+    for nvls_off in ("1", "0"):
+        os.environ["TILECCL_DISABLE_NVLS"] = nvls_off
+        for dtype, tol in ((torch.float16, 2e-2), (torch.float32, 1e-5)):
+            for n in (1024, 8198, 1_000_000):
+                n = n // ws * ws
+                x = ctx.randn(n, dtype=dtype)
+                orig = x.clone()
+                ops.allreduce(x, ctx=ctx)
+                ref = orig.float().clone()
+                dist.all_reduce(ref)
+                check(f"allreduce n{n} {dtype} nvls_off={nvls_off}", x, ref, tol)
+                out = ctx.zeros(n * ws, dtype=dtype)
+                x.copy_(orig)
+                ops.allgather(x, out, ctx=ctx)
+                check(f"allgather n{n}", out, torch.cat(gather(orig)), 1e-7)
+                part = ctx.zeros(n // ws, dtype=dtype)
+                ops.reduce_scatter(x, part, ctx=ctx)
+                check(f"reduce_scatter n{n}", part, ref[rank * (n // ws):(rank + 1) * (n // ws)], tol)
+                b = ctx.randn(n, dtype=dtype)
+                bl = gather(b)
+                ops.broadcast(b, ctx=ctx, root=ws - 1)
+                check(f"broadcast n{n}", b, bl[ws - 1], 1e-7)
+                sc = ctx.zeros(n // ws, dtype=dtype)
+                ops.scatter(x, sc, ctx=ctx, root=0)
+                check(f"scatter n{n}", sc, gather(x)[0][rank * (n // ws):(rank + 1) * (n // ws)], 1e-7)
+                dist.barrier()
+    coll.check_status(ctx.heap)
+    os.environ["TILECCL_DISABLE_NVLS"] = "0"
+
+    tokens, hidden, ffn = 128 * ws * 2, 512, 256 * ws
+    mlp = TPMLP(ctx, tokens=tokens, hidden=hidden, ffn=ffn, dtype=torch.bfloat16, seed=3)
+    gen = torch.Generator(device=dev).manual_seed(11)
+    x_full = torch.randn(tokens, hidden, device=dev, generator=gen).bfloat16()   # same on every rank
+    t = tokens // ws
+    mlp.x_local.copy_(x_full[rank * t:(rank + 1) * t])
+    dist.barrier()
+    for _ in range(3):
+        y = mlp.forward()
+    ops.check_status(ctx)
+    ref = torch.zeros(tokens, hidden, device=dev)
+    for wg, wu, wd in zip(gather(mlp.w_gate), gather(mlp.w_up), gather(mlp.w_down)):
+        h = torch.nn.functional.silu(x_full.float() @ wg.float()) * (x_full.float() @ wu.float())
+        ref += h @ wd.float()
+    check("tp_mlp", y, ref[rank * t:(rank + 1) * t], 3e-2)
+    dist.barrier()
+    torch.cuda.synchronize()
+    ctx.heap.cleanup()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("MP_WORKER_OK", flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    try:
+        code = main()
+    except BaseException:
+        traceback.print_exc()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(3)
+    sys.exit(code)

@@ -1,0 +1,28 @@
+"""One process per GPU (torchrun): needs at least two GPUs, skipped otherwise."""
+
+import os
+import socket
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+def test_multiprocess_ranks(ws):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "MP_WORKER_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])

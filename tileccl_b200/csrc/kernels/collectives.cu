@@ -429,3 +429,77 @@ extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, i
   TCCL_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
+
+// ---------------------------------------------------------------------------
+// All-reduce without any allocation (see collectives_noalloc.h for the contract)
+// ---------------------------------------------------------------------------
+#include "collectives_noalloc.h"
+
+// Scratch of the no-allocation entry point: lives in the library image, one copy
+// per GPU that loads the library.  Rank r of a call uses the block at r *
+// TCCL_NOALLOC_RANK_BYTES: [staging parity 0][staging parity 1][counter block].
+// In host code this name is only a handle for cudaGetSymbolAddress, never an address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[TCCL_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kNoAllocMaxDevices = 64;
+void* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+}  // namespace
+
+extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ranks, int32_t dtype,
+                                          uint64_t count, uint64_t stream) {
+  TCCL_CHECK_ARG(buffers != nullptr, "buffers is null");
+  TCCL_CHECK_ARG(n_ranks >= 1 && n_ranks <= TCCL_NOALLOC_MAX_RANKS,
+                 "n_ranks must be 1.." << TCCL_NOALLOC_MAX_RANKS << ", got " << n_ranks);
+  TCCL_CHECK_ARG(dtype == kF16 || dtype == kBF16 || dtype == kF32,
+                 "dtype must be 0 (fp16), 1 (bf16) or 2 (fp32)");
+  const uint64_t elem = dtype == kF32 ? 4 : 2;
+  const uint64_t bytes = count * elem;
+  TCCL_CHECK_ARG(count > 0, "count must be positive");
+  TCCL_CHECK_ARG(bytes <= TCCL_NOALLOC_MAX_BYTES,
+                 "message of " << bytes << " bytes exceeds the built-in scratch ("
+                               << TCCL_NOALLOC_MAX_BYTES << " bytes per buffer); use the heap-based "
+                               << "all-reduce for larger messages");
+  for (int r = 0; r < n_ranks; ++r)
+    TCCL_CHECK_ARG(buffers[r] != 0 && buffers[r] % 16 == 0,
+                   "buffer " << r << " must be a non-null, 16-byte aligned device address");
+  int dev = 0;
+  TCCL_CHECK_CUDA(cudaGetDevice(&dev));
+  TCCL_CHECK_ARG(dev >= 0 && dev < kNoAllocMaxDevices, "device ordinal out of range");
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    // Once per device, with that device current: the device address of the array.
+    void* ptr = nullptr;
+    TCCL_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    TCCL_CHECK_ARG(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  const uint64_t scratch = reinterpret_cast<uint64_t>(g_noalloc_scratch_ptr[dev]);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // The counters keep the previous call's values: they must start at zero.
+  for (int r = 0; r < n_ranks; ++r)
+    TCCL_CHECK_CUDA(cudaMemsetAsync(
+        reinterpret_cast<void*>(scratch + r * uint64_t(TCCL_NOALLOC_RANK_BYTES) +
+                                2 * uint64_t(TCCL_NOALLOC_MAX_BYTES)),
+        0, 256, s));
+  int grid = static_cast<int>((bytes / 16 + 1023) / 1024);
+  grid = grid < 1 ? 1 : (grid > 32 ? 32 : grid);
+  // phase 1 for every rank (publish a snapshot), then phase 2 for every rank (sum):
+  // kernels of one GPU never wait on one another.
+  for (int phase = 1; phase <= 2; ++phase) {
+    for (int r = 0; r < n_ranks; ++r) {
+      CollParams p;
+      p.op = kAllReduceOneShot; p.dtype = dtype; p.rank = r; p.world_size = n_ranks; p.root = 0;
+      p.use_multimem = 0; p.phase_mask = phase; p.elem_size = static_cast<int32_t>(elem);
+      p.epoch = 1;
+      p.src = buffers[r]; p.dst = buffers[r];
+      p.staging = scratch + r * uint64_t(TCCL_NOALLOC_RANK_BYTES);
+      p.counters = p.staging + 2 * uint64_t(TCCL_NOALLOC_MAX_BYTES);
+      p.mc_base = 0; p.heap_base = 0;
+      p.heap_stride = TCCL_NOALLOC_RANK_BYTES;
+      p.bytes = bytes; p.status = 0; p.budget_ns = 2000000000ull;
+      allreduce_oneshot_kernel<<<grid, 512, 0, s>>>(p);
+      TCCL_CHECK_CUDA(cudaGetLastError());
+    }
+  }
+  return kOk;
+}

@@ -98,6 +98,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   volatile uint32_t* tmem_slot_g =
       reinterpret_cast<volatile uint32_t*>(ctl_generic + (tmem_slot - smem_ctl));
   volatile uint32_t* abort_flag = tmem_slot_g + 1;
+  // Slabs (one per epilogue warp and tile) whose local bulk stores have completed; the
+  // communication warps poll it to learn which tiles of C they may forward.
+  const uint32_t done_count = tmem_slot + 8;
+  volatile uint32_t* done_count_g = tmem_slot_g + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -114,6 +118,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     }
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
+    *done_count_g = 0;
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -130,6 +135,88 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 
   const int first = p.tile_begin + static_cast<int>(blockIdx.x);
   const int step = static_cast<int>(gridDim.x);
+  // Finished tiles of C are forwarded to the peers by warps 2 and 3 (16-byte stores or
+  // multimem stores read back from this rank's copy of C) rather than by the epilogue.
+  const bool comm_push = p.world_size > 1 && p.push_mode != kPushTma &&
+                         (p.mode == kModePushAll || p.mode == kModeAllScatter);
+
+  // ------------------------- communication warps (2, 3) -------------------------
+  // Warp 2 forwards rows [0, 64) of every finished tile, warp 3 rows [64, 128): one
+  // warp-wide 16-byte load per tile row from this rank's C (still in L2), one store per
+  // peer (or one multimem store), eight rows in flight.  The fence + counter update
+  // that publishes the half tile stalls only this warp, never the epilogue.
+  auto comm_role = [&](int half) {
+    const int tile_cols = p.epi_op == kEpiSiluGate ? kBN / 2 : kBN;
+    const int vpr = tile_cols / 8;   // 16-byte vectors per tile row
+    const int rpi = 32 / vpr;        // tile rows covered by one warp-wide access
+    const int lrow = lane / vpr, lvec = lane % vpr;
+    uint32_t n_tiles = 0;
+    for (int t = first; t < p.tile_end; t += step) {
+      ++n_tiles;
+      const uint32_t want = n_tiles * kEpiWarps;
+      bool got = true;
+      uint32_t seen = 0;
+      for (uint32_t it = 0;; ++it) {
+        asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(seen) : "r"(done_count) : "memory");
+        if (seen >= want) break;
+        if (wb.expired(it)) { got = false; break; }
+        if (it > 8) __nanosleep(64);
+      }
+      got = __all_sync(0xffffffffu, got);
+      if (!got) {
+        if (lane == 0 && !wb.aborted())
+          report_status(status, kStatusTimeoutMbarrier, 60 + half, want, seen, p.rank, t);
+        break;
+      }
+      fence_proxy_async_all();
+      const TileCoord c = decode_tile(p, t);
+      int lo = c.out_x, hi = c.out_x + tile_cols;
+      if (hi > p.out_cols) hi = p.out_cols;
+      if (p.mode == kModeAllScatter) {
+        if (lo < p.scatter_col_begin) lo = p.scatter_col_begin;
+        if (hi > p.scatter_col_end) hi = p.scatter_col_end;
+      }
+      if (hi > lo) {
+        const int col = c.out_x + lvec * 8;
+        const bool col_ok = col >= lo && col < hi;
+        const int y0 = c.out_y + half * (kBM / 2) + lrow;
+        const int64_t col_off = static_cast<int64_t>(col) * 2;
+        const char* src = reinterpret_cast<const char*>(p.out_ptr[p.rank]);
+        for (int r0 = 0; r0 < kBM / 2; r0 += 8 * rpi) {
+          uint4 v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int row = y0 + r0 + j * rpi;
+            if (col_ok && row < p.out_rows)
+              v[j] = ld_remote_v4(src + static_cast<int64_t>(row) * p.out_ld_bytes + col_off);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int row = y0 + r0 + j * rpi;
+            if (!(col_ok && row < p.out_rows)) continue;
+            const int64_t off = static_cast<int64_t>(row) * p.out_ld_bytes + col_off;
+            if (p.push_mode == kPushMultimem) {
+              multimem_st_v4(reinterpret_cast<char*>(p.out_mc_ptr) + off, v[j]);
+            } else {
+              for (int d = 1; d < p.world_size; ++d)
+                st_remote_v4(reinterpret_cast<char*>(p.out_ptr[(p.rank + d) % p.world_size]) + off,
+                             v[j]);
+            }
+          }
+        }
+      }
+      if (p.sig_local != 0) {
+        fence_acq_rel_sys();   // every lane's peer stores are performed before the signal
+        __syncwarp();
+        if (lane == 0) {
+          const int group = c.lm / p.group_m_tiles;
+          for (int d = 1; d < p.world_size; ++d)
+            red_release_sys_add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, group),
+                                static_cast<uint32_t>(kEpiWarps / 2));
+        }
+      }
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -227,6 +314,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         for (int it = 0; it < 1000000 && !mbar_try_wait(bar_drain, 0); ++it) {}
       }
     }
+  } else if (warp == 2) {
+    if (comm_push) comm_role(0);
   } else if (warp == 3) {
     // ------------------- all-gather push of the A operand ---------------------
     if (p.ag_bytes != 0 && p.do_ag_push && p.world_size > 1) {
@@ -267,6 +356,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         }
       }
     }
+    if (comm_push) comm_role(1);
     // ---------------------- incoming TileGroup waiter -------------------------
     if (p.mode == kModePushAll && p.wait_incoming && p.world_size > 1) {
       const int groups = (p.m_tiles_local + p.group_m_tiles - 1) / p.group_m_tiles;
@@ -296,6 +386,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     bool ok = true;
     // lane 0: the last two tiles whose signals have not been sent yet ([0] = older)
     bool pend_valid[2] = {false, false};
+    bool slab_pending = false;   // lane 0: a slab whose completion the comm warps still await
     int pend_owner[2] = {0, 0}, pend_group[2] = {0, 0};
     // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
     auto send_signal = [&](int owner, int g) {
@@ -339,6 +430,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         break;
       }
       tcgen05_fence_after();
+      if (p.trace != 0 && lane == 0)
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3] = globaltimer_ns();
       const uint32_t t_acc = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 
       for (int ch = 0; ch < n_chunks; ++ch) {
@@ -435,42 +528,36 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           // Local destination (plain GEMM, own all-gather rows, reduced tile).
           const int local_slot = p.mode == kModeGemm ? 0 : p.rank;
           if (lane == 0) tma_store_3d(&p.tma_out[local_slot], col0, y, 0, sbuf);
-          if (push_all && p.world_size > 1) {
-            if (p.push_mode == kPushTma) {
-              if (lane == 0)
-                for (int d = 1; d < p.world_size; ++d)
-                  tma_store_3d(&p.tma_out[(p.rank + d) % p.world_size], col0, y, 0, sbuf);
-            } else {
-              const uint8_t* sg = my_epi_g + buf * kEpiBufBytes;
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const int idx = lane + 32 * i, r = idx >> 3, j = idx & 7;
-                if (y + r < p.out_rows && col0 + j * 8 < p.out_cols) {
-                  const uint4 w =
-                      *reinterpret_cast<const uint4*>(sg + r * 128 + ((j ^ (r & 7)) << 4));
-                  const int64_t off = static_cast<int64_t>(y + r) * p.out_ld_bytes +
-                                      static_cast<int64_t>(col0 + j * 8) * 2;
-                  if (p.push_mode == kPushMultimem) {
-                    multimem_st_v4(reinterpret_cast<char*>(p.out_mc_ptr) + off, w);
-                  } else {
-                    for (int d = 1; d < p.world_size; ++d)
-                      st_remote_v4(
-                          reinterpret_cast<char*>(p.out_ptr[(p.rank + d) % p.world_size]) + off, w);
-                  }
-                }
-              }
-            }
+          // Peer copies: one bulk store per destination here, or (other push modes) left
+          // to the communication warps, which forward the tile once it is complete.
+          if (push_all && p.world_size > 1 && p.push_mode == kPushTma) {
+            if (lane == 0)
+              for (int d = 1; d < p.world_size; ++d)
+                tma_store_3d(&p.tma_out[(p.rank + d) % p.world_size], col0, y, 0, sbuf);
           }
         }
         if (lane == 0) tma_store_commit();
         buf ^= 1u;
       }
 
+      if (p.trace != 0 && lane == 0)
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3 + 1] = globaltimer_ns();
       // ---- TileGroup signalling: this slab of this tile is now on its way ----
       const bool signals = p.world_size > 1 && p.sig_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
                             (p.mode == kModeReduceScatter && !reduce_here));
-      if (p.push_mode == kPushTma) {
+      if (comm_push) {
+        // Tell the communication warps that the previous tile's slab is in global memory
+        // (its bulk groups have completed; this tile's may still be in flight).
+        if (lane == 0) {
+          if (slab_pending) {
+            if (n_chunks == 4) tma_store_wait_all<4>(); else tma_store_wait_all<2>();
+            fence_proxy_async_all();
+            asm volatile("red.release.cta.shared.add.u32 [%0], 1;" ::"r"(done_count) : "memory");
+          }
+          slab_pending = true;
+        }
+      } else if (p.push_mode == kPushTma) {
         // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent two
         // tiles late: by then its bulk groups have completed (data has reached the peer)
         // while the groups of the two most recent tiles are still in flight, so neither
@@ -505,14 +592,16 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         if (lane == 0)
           red_release_sys_add(reinterpret_cast<uint32_t*>(p.sig_local) + group, 1u);
       }
-      if (p.trace != 0 && q == 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[t] = globaltimer_ns();
+      if (p.trace != 0 && lane == 0)
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3 + 2] = globaltimer_ns();
 
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) {
       tma_store_wait_all<0>();
       fence_proxy_async_all();
+      if (slab_pending)
+        asm volatile("red.release.cta.shared.add.u32 [%0], 1;" ::"r"(done_count) : "memory");
       for (int i = 0; i < 2; ++i)
         if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i]);
     }

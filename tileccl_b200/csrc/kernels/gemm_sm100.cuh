@@ -92,7 +92,8 @@ struct alignas(64) FusedGemmParams {
   // diagnostics
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;
-  uint64_t trace;                     // optional uint64[3 * tiles]: start / ready / done timestamps
+  // optional uint64[tiles][4 epilogue warps][3]: accumulator ready / stores issued / signalled
+  uint64_t trace;
 };
 
 }  // namespace tileccl

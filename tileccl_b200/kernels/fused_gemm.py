@@ -168,6 +168,7 @@ class FusedGemmPlan:
         self.grid = info.grid
         self.tiles_total = info.tiles_total
         self.tiles_per_owner = info.tiles_per_owner
+        self.owners = max(1, info.tiles_total // max(1, info.tiles_per_owner))
         self.m_tiles_local = info.m_tiles_local
         self.n_tiles_local = info.n_tiles_local
         self.groups = info.groups

@@ -275,16 +275,19 @@ class GemmAllGatherPlan:
         if got != self.contract:
             raise ValueError("tensors no longer match this GemmAllGatherPlan; build a new plan")
 
-    def execute(self, A, B, C, *, validate: bool = True, wait: bool = True):
+    def execute(self, A, B, C, *, validate: bool = True, wait: bool = True, a_host=None):
+        """``a_host``: pinned host tensor shaped like ``A``; when given, ``A`` is filled
+        from it on a side stream, run of tile rows by run, while the kernel computes."""
         if validate:
             self.validate_tensors(A, B, C)
         c, ctx = self.contract, self.ctx
         if c.layout == "columns":
             _fused.push_all(ctx, "gemm_allgather_cols", A, B, C, region_row0=0,
-                            region_col0=c.rank * c.shard_cols, b_is_nk=self.b_is_nk, wait=wait)
+                            region_col0=c.rank * c.shard_cols, b_is_nk=self.b_is_nk, wait=wait,
+                            a_host=a_host)
         else:
             _fused.push_all(ctx, "gemm_allgather_rows", A, B, C, region_row0=c.rank * A.shape[0],
-                            region_col0=0, b_is_nk=self.b_is_nk, wait=wait)
+                            region_col0=0, b_is_nk=self.b_is_nk, wait=wait, a_host=a_host)
         return C
 
     def to_dict(self) -> dict:
@@ -337,11 +340,16 @@ def gemm_allgather(A, B_shard, C, *, ctx=None, storage_kind="symmetric"):
         A, B_shard, C, validate=False)
 
 
-def gemm_allgather_rows(A_local, B, C, *, ctx=None, b_is_nk=False, wait=True):
+def gemm_allgather_rows(A_local, B, C, *, ctx=None, b_is_nk=False, wait=True, a_host=None):
     """Row-sharded form: ``A_local (M/ws, K)``, ``B (K, N)``, ``C (M, N)`` on the heap;
-    rows ``[r*M/ws, (r+1)*M/ws)`` of ``C`` on every rank come from rank ``r``."""
+    rows ``[r*M/ws, (r+1)*M/ws)`` of ``C`` on every rank come from rank ``r``.
+
+    ``a_host`` (pinned host tensor shaped like ``A_local``): the activations are
+    streamed from the host into ``A_local`` while the kernel runs, tile rows in
+    the order the kernel consumes them, so only the last run's math is exposed
+    after the PCIe copy."""
     plan = build_gemm_allgather_plan(A_local, B, C, ctx=ctx, layout="rows", b_is_nk=b_is_nk)
-    return plan.execute(A_local, B, C, validate=False, wait=wait)
+    return plan.execute(A_local, B, C, validate=False, wait=wait, a_host=a_host)
 
 
 # ==========================================================================
@@ -377,12 +385,13 @@ class GemmReduceScatterPlan:
         if got != self.contract:
             raise ValueError("tensors no longer match this GemmReduceScatterPlan; build a new plan")
 
-    def execute(self, A, B, C, *, validate: bool = True):
+    def execute(self, A, B, C, *, validate: bool = True, a_host=None):
+        """``a_host``: pinned host tensor shaped like ``A`` to stream the operand from."""
         if validate:
             self.validate_tensors(A, B, C)
         axis = 1 if self.contract.layout == "columns" else 0
         _fused.reduce_scatter(self.ctx, f"gemm_reducescatter_{self.contract.layout}", A, B, C,
-                              split_axis=axis, b_is_nk=self.b_is_nk)
+                              split_axis=axis, b_is_nk=self.b_is_nk, a_host=a_host)
         return C
 
     def to_dict(self) -> dict:
@@ -450,11 +459,12 @@ def gemm_reducescatter(A, B, C, *, ctx=None, implementation="auto", storage_kind
                                          storage_kind=storage_kind).execute(A, B, C, validate=False)
 
 
-def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False):
+def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False, a_host=None):
     """Row-sharded form: ``A (M, K/ws)``, ``B (K/ws, N)``, ``C_local (M/ws, N)``:
-    ``C_local_r = sum_i (A_i @ B_i)[r*M/ws:(r+1)*M/ws, :]``."""
+    ``C_local_r = sum_i (A_i @ B_i)[r*M/ws:(r+1)*M/ws, :]``.  ``a_host`` streams ``A``
+    from pinned host memory as in :func:`gemm_allgather_rows`."""
     plan = build_gemm_reducescatter_plan(A, B, C_local, ctx=ctx, layout="rows", b_is_nk=b_is_nk)
-    return plan.execute(A, B, C_local, validate=False)
+    return plan.execute(A, B, C_local, validate=False, a_host=a_host)
 
 
 # ==========================================================================

@@ -157,18 +157,101 @@ def _b_dims(B: torch.Tensor, b_is_nk: bool) -> tuple:
 
 
 # --------------------------------------------------------------------------
+# A operand streamed from pinned host memory while the kernel runs
+# --------------------------------------------------------------------------
+def _tile_row_chunks(plan, min_tiles: int = 2 * 148, max_chunks: int = 8) -> list:
+    """Split the rank's tile order into runs of whole tile rows.
+
+    Returns ``[(tile_begin, tile_end, [(row0, row1), ...]), ...]`` where the row
+    ranges are the rows of A the run reads.  Runs follow the kernel's visiting
+    order (owner-major for reduce-scatter, see csrc/plan/tile_order.h), so the
+    host copy of run i only has to stay ahead of the launch of run i.
+    """
+    n_t = plan.n_tiles_local
+    rows_total = plan.m_tiles_local * plan.owners           # tile rows in visiting order
+    per_chunk = max(1, -(-min_tiles // n_t))
+    n_chunks = max(1, min(max_chunks, rows_total // per_chunk))
+    bounds = [round(i * rows_total / n_chunks) for i in range(n_chunks + 1)]
+    spec = plan.spec
+    chunks = []
+    for i in range(n_chunks):
+        r0, r1 = bounds[i], bounds[i + 1]
+        if r1 <= r0:
+            continue
+        ranges = []
+        tr = r0
+        while tr < r1:
+            oi, lm = divmod(tr, plan.m_tiles_local)
+            lm_end = min(plan.m_tiles_local, lm + (r1 - tr))
+            base = 0
+            if plan.owners > 1 and spec.split_axis == 0:
+                owner = (spec.rank + 1 + oi) % spec.world_size
+                base = owner * spec.sub_m
+            lo = base + lm * fg.BLOCK_M
+            hi = base + min(spec.sub_m if plan.owners > 1 else spec.a_rows, lm_end * fg.BLOCK_M)
+            ranges.append((lo, min(hi, spec.a_rows)))
+            tr += lm_end - lm
+        chunks.append((r0 * n_t, r1 * n_t, ranges))
+    return chunks
+
+
+def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, **launch_kw) -> None:
+    """Run ``plan`` while its A operand is still arriving from pinned host memory.
+
+    The rows of ``a_host`` are copied to ``A`` on a side stream in the order the
+    kernel consumes them; every run of tile rows is launched as soon as its rows
+    are on the device, so all but the last run's math hides under the PCIe copy.
+    Everything is stream-ordered: the host never blocks.
+    """
+    if a_host.shape != A.shape or a_host.dtype != A.dtype:
+        raise ValueError(f"a_host must match A: {tuple(a_host.shape)} {a_host.dtype} vs "
+                         f"{tuple(A.shape)} {A.dtype}")
+    if not a_host.is_pinned():
+        raise ValueError("a_host must be pinned host memory (tensor.pin_memory())")
+    if (plan.owners > 1 and plan.spec.split_axis != 0) or plan.spec.rot_m_tiles != 0:
+        # column-split reduce-scatter reads every row of A for every owner
+        A.copy_(a_host, non_blocking=True)
+        plan.launch(**launch_kw)
+        return
+    st = op_state(ctx, ("h2d_stream",))
+    if "stream" not in st:
+        st["stream"] = torch.cuda.Stream(device=ctx.torch_device)
+        st["events"] = [torch.cuda.Event() for _ in range(16)]
+        st["next"] = 0
+    side, cur = st["stream"], torch.cuda.current_stream()
+    chunks = getattr(plan, "_row_chunks", None)
+    if chunks is None:
+        chunks = plan._row_chunks = _tile_row_chunks(plan)
+    side.wait_stream(cur)                       # earlier readers of A are done
+    wait_incoming = launch_kw.pop("wait_incoming", False)
+    ag_push = launch_kw.pop("ag_push", False)
+    for i, (t0, t1, ranges) in enumerate(chunks):
+        ev = st["events"][st["next"] % 16]
+        st["next"] += 1
+        with torch.cuda.stream(side):
+            for lo, hi in ranges:
+                A[lo:hi].copy_(a_host[lo:hi], non_blocking=True)
+            ev.record(side)
+        cur.wait_event(ev)
+        last = i == len(chunks) - 1
+        plan.launch(tile_begin=t0, tile_end=t1, wait_incoming=wait_incoming and last,
+                    ag_push=ag_push and i == 0, **launch_kw)
+
+
+# --------------------------------------------------------------------------
 # push-all: C_d[region of this rank] = A @ B for every rank d
 # --------------------------------------------------------------------------
 def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
              region_row0: int, region_col0: int, b_is_nk: bool = False,
              group_m_tiles: Optional[int] = None, push_mode: Optional[int] = None,
-             wait: bool = True) -> None:
+             wait: bool = True, a_host: Optional[torch.Tensor] = None) -> None:
     """Product of the local operands, written into the same region of ``C`` on every rank.
 
     ``C`` must live on the symmetric heap.  ``region_*`` is where this rank's
     ``[A.rows, N_b]`` block goes inside ``C``.  With ``wait`` the call also
     makes sure (on the stream) that every peer's block has arrived in the local
-    ``C``.
+    ``C``.  ``a_host`` (pinned, same shape as ``A``): the operand is first brought
+    to ``A`` from the host, overlapped with the kernel (see ``launch_streamed``).
     """
     _require_2d("A", A, ctx)
     _require_2d("B", B, ctx)
@@ -216,10 +299,19 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
     sigst["epoch"] += 1
     epoch = sigst["epoch"]
     if ws == 1:
-        plan.launch()
+        if a_host is not None:
+            launch_streamed(ctx, plan, A, a_host)
+        else:
+            plan.launch()
         return
     fused_wait = wait and _in_kernel_waits_ok(ctx) and not ctx.is_single_process
-    phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, wait_incoming=fused_wait))]
+    if a_host is not None and not ctx.is_single_process:
+        phases = [_on_device(ctx, lambda: launch_streamed(ctx, plan, A, a_host, epoch=epoch,
+                                                          wait_incoming=fused_wait))]
+    else:
+        if a_host is not None:
+            A.copy_(a_host, non_blocking=True)
+        phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, wait_incoming=fused_wait))]
     if wait and not fused_wait:
         phases.append(_on_device(ctx, lambda: wait_groups(ctx, st["sig"], plan.groups,
                                                           st["per_epoch"], epoch)))
@@ -239,7 +331,7 @@ def wait_groups(ctx, sig: torch.Tensor, n_groups: int, per_epoch: torch.Tensor, 
 # --------------------------------------------------------------------------
 def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
                    split_axis: int, b_is_nk: bool = False, group_m_tiles: Optional[int] = None,
-                   push_mode: Optional[int] = None) -> None:
+                   push_mode: Optional[int] = None, a_host: Optional[torch.Tensor] = None) -> None:
     """Every rank multiplies its operands; block ``r`` of the summed product lands on rank ``r``.
 
     ``split_axis=0``: ``A`` is ``[ws * Mloc, K]``, ``C`` is ``[Mloc, N]`` (row blocks).
@@ -303,9 +395,15 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     plan = st["plan"]
     sigst["epoch"] += 1
     epoch = sigst["epoch"]
-    if ws == 1 or _in_kernel_waits_ok(ctx):
+    if a_host is not None and (ws == 1 or (_in_kernel_waits_ok(ctx) and not ctx.is_single_process)):
+        phases = [_on_device(ctx, lambda: launch_streamed(ctx, plan, A, a_host, epoch=epoch))]
+    elif ws == 1 or _in_kernel_waits_ok(ctx):
+        if a_host is not None:
+            A.copy_(a_host, non_blocking=True)
         phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch))]
     else:
+        if a_host is not None:
+            A.copy_(a_host, non_blocking=True)
         # Emulated ranks: peers' tiles for everybody first, then each owner's own (reducing) tiles.
         n_remote = plan.tiles_per_owner * (ws - 1)
         phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, tile_begin=0, tile_end=n_remote)),

@@ -270,7 +270,7 @@ def run_ours(args):
                        "parallelism": f"tp{world} row-sharded",
                        "l2": "256 MiB flush write before every problem, outside the timed events",
                        "timing": "CUDA events per problem, max over ranks, mean over steps",
-                       "push_mode": os.environ.get("TILECCL_PUSH_MODE", "stores"),
+                       "push_mode": os.environ.get("TILECCL_PUSH_MODE", "tma"),
                        "nvls_bound": bool(ctx.heap.has_multicast),
                        "roofline_peaks": peaks},
             "shapes": shapes, "clocks": clocks, "gpu_launches": launches,

@@ -110,6 +110,8 @@ class GemmDesc(C.Structure):
         ("status", C.c_uint64),
         ("trace", C.c_uint64),
         ("wait_budget_ns", C.c_uint64),
+        ("tuning", C.c_int32),
+        ("reserved0", C.c_int32),
     ]
 
 

@@ -110,8 +110,10 @@ typedef struct TcclGemmDesc {
   int32_t scatter_col_begin, scatter_col_end;
   int32_t grid;                  // 0 = one CTA per SM
   uint64_t status;               // uint32[8] in device memory, may be 0
-  uint64_t trace;                // uint64[tiles * 12] in device memory (3 stamps per epilogue warp), may be 0
+  uint64_t trace;                // uint64[tiles * 16] in device memory (4 stamps per epilogue warp), may be 0
   uint64_t wait_budget_ns;       // 0 = default (2 s)
+  int32_t tuning;                // bit 0: TileGroup signals after a completed bulk store are relaxed adds
+  int32_t reserved0;
 } TcclGemmDesc;
 
 typedef struct TcclGemmPlanInfo {

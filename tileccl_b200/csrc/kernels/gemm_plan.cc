@@ -154,6 +154,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   p.scatter_col_end = d.scatter_col_end;
   p.status = d.status;
   p.trace = d.trace;
+  p.tuning = d.tuning;
   p.wait_budget_ns = d.wait_budget_ns ? d.wait_budget_ns : 2000000000ull;
 
   const int groups = (p.m_tiles_local + p.group_m_tiles - 1) / p.group_m_tiles;

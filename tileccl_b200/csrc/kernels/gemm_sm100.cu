@@ -389,12 +389,19 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     bool slab_pending = false;   // lane 0: a slab whose completion the comm warps still await
     int pend_owner[2] = {0, 0}, pend_group[2] = {0, 0};
     // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
-    auto send_signal = [&](int owner, int g) {
+    auto send_signal = [&](int owner, int g, bool after_bulk) {
+      const bool relaxed = after_bulk && (p.tuning & kTuneRelaxedSignalAfterBulk) != 0;
+      auto add = [&](uint32_t* ctr) {
+        if (relaxed)
+          asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
+        else
+          red_release_sys_add(ctr, 1u);
+      };
       if (p.mode == kModeReduceScatter) {
-        red_release_sys_add(peer_counter(p, owner, 0, g), 1u);
+        add(peer_counter(p, owner, 0, g));
       } else {
         for (int d = 1; d < p.world_size; ++d)
-          red_release_sys_add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, g), 1u);
+          add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, g));
       }
     };
     for (int t = first; ok && t < p.tile_end; t += step) {
@@ -431,7 +438,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
       tcgen05_fence_after();
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3] = globaltimer_ns();
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4] = globaltimer_ns();
       const uint32_t t_acc = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 
       for (int ch = 0; ch < n_chunks; ++ch) {
@@ -541,7 +548,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
 
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3 + 1] = globaltimer_ns();
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 1] = globaltimer_ns();
       // ---- TileGroup signalling: this slab of this tile is now on its way ----
       const bool signals = p.world_size > 1 && p.sig_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
@@ -566,7 +573,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           if (pend_valid[0]) {
             if (n_chunks == 4) tma_store_wait_all<8>(); else tma_store_wait_all<4>();
             fence_proxy_async_all();
-            send_signal(pend_owner[0], pend_group[0]);
+            if (p.trace != 0)
+              reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 2] =
+                  globaltimer_ns();
+            send_signal(pend_owner[0], pend_group[0], true);
           }
           pend_valid[0] = pend_valid[1];
           pend_owner[0] = pend_owner[1];
@@ -580,7 +590,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         fence_proxy_async_all();
         fence_acq_rel_sys();                      // every lane's peer stores are ordered first
         __syncwarp();
-        if (lane == 0) send_signal(c.owner, group);
+        if (lane == 0) send_signal(c.owner, group, false);
       }
       // Plain GEMM feeding a consumer kernel on the same GPU (producer / consumer
       // pattern): publish the slab on this rank's own TileGroup counter.
@@ -593,7 +603,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           red_release_sys_add(reinterpret_cast<uint32_t*>(p.sig_local) + group, 1u);
       }
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 3 + 2] = globaltimer_ns();
+        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 3] = globaltimer_ns();
 
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
@@ -603,7 +613,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       if (slab_pending)
         asm volatile("red.release.cta.shared.add.u32 [%0], 1;" ::"r"(done_count) : "memory");
       for (int i = 0; i < 2; ++i)
-        if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i]);
+        if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
     }
   }
 

@@ -41,6 +41,14 @@ enum PushMode : int {
   kPushTma = 1,     // peer copies with one TMA store per destination
   kPushMultimem = 2,  // one multimem.st per 16 bytes reaches every rank (needs NVLS)
 };
+enum TuningBits : int {
+  // A TileGroup signal that follows a *completed* bulk store is sent as a relaxed add
+  // instead of a release add.  Completion of a bulk group means the destination has
+  // acknowledged the data, so an add issued afterwards cannot overtake it; a release add
+  // would additionally wait for the younger bulk stores still in flight (measured: about
+  // 6 us per tile and warp on NVLink 5 under load).
+  kTuneRelaxedSignalAfterBulk = 1,
+};
 enum EpilogueOp : int {
   kEpiNone = 0,
   kEpiSiluGate = 1,  // out[:, j] = silu(acc[:, j]) * acc[:, 128 + j] per 256-column tile
@@ -92,8 +100,10 @@ struct alignas(64) FusedGemmParams {
   // diagnostics
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;
-  // optional uint64[tiles][4 epilogue warps][3]: accumulator ready / stores issued / signalled
+  // optional uint64[tiles][4 epilogue warps][4]:
+  // accumulator ready / stores issued / older stores complete / signalled
   uint64_t trace;
+  int32_t tuning;                     // TuningBits
 };
 
 }  // namespace tileccl

@@ -9,6 +9,7 @@ dozen driver calls; launching it costs one kernel launch, so callers keep plans
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -123,6 +124,7 @@ class FusedGemmSpec:
     grid: int = 0
     status_ptr: int = 0
     trace_ptr: int = 0
+    tuning: int = -1            # -1: TILECCL_TUNING from the environment (default 1)
     wait_budget_ns: int = 0
 
 
@@ -159,6 +161,7 @@ class FusedGemmPlan:
         d.grid = spec.grid
         d.status = spec.status_ptr
         d.trace = spec.trace_ptr
+        d.tuning = spec.tuning if spec.tuning >= 0 else int(os.environ.get("TILECCL_TUNING", "1"))
         d.wait_budget_ns = spec.wait_budget_ns
         handle = C.c_void_p()
         _native.call("tccl_gemm_plan_create", C.byref(d), C.byref(handle))

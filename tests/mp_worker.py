@@ -73,6 +73,32 @@ def main() -> int:
             check(f"gemm_reducescatter push{push} {dtype}", C2, full[rank * mloc:(rank + 1) * mloc], tol)
             dist.barrier()
 
+    # Many more tiles than CTAs: every CTA goes from remote tiles to its own (reducing)
+    # tiles while signals of its last remote tiles are still held back.
+    M, N, K = 8192, 2048, 256 * ws
+    mloc = M // ws
+    A3 = ctx.randn(M, K // ws, dtype=torch.float16)
+    A3.mul_(K ** -0.5)
+    B3 = ctx.randn(K // ws, N, dtype=torch.float16)
+    C3 = torch.zeros(mloc, N, dtype=torch.float16, device=dev)
+    for _ in range(3):
+        _fused.reduce_scatter(ctx, "t_rs_large", A3, B3, C3, split_axis=0)
+    ops.check_status(ctx)
+    A3s, B3s = gather(A3), gather(B3)
+    full = sum(A3s[r].float() @ B3s[r].float() for r in range(ws))
+    check("gemm_reducescatter large", C3, full[rank * mloc:(rank + 1) * mloc], 5e-3)
+    C4 = ctx.zeros(M, N, dtype=torch.float16)
+    A4 = ctx.randn(mloc, K, dtype=torch.float16)
+    A4.mul_(K ** -0.5)
+    B4 = ctx.randn(K, N, dtype=torch.float16)
+    for _ in range(3):
+        _fused.push_all(ctx, "t_ag_large", A4, B4, C4, region_row0=rank * mloc, region_col0=0)
+    ops.check_status(ctx)
+    A4s, B4s = gather(A4), gather(B4)
+    check("gemm_allgather large", C4,
+          torch.cat([A4s[r].float() @ B4s[r].float() for r in range(ws)]), 5e-3)
+    dist.barrier()
+
     for nvls_off in ("1", "0"):
         os.environ["TILECCL_DISABLE_NVLS"] = nvls_off
         for dtype, tol in ((torch.float16, 2e-2), (torch.float32, 1e-5)):

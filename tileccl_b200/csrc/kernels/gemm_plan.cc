@@ -112,6 +112,12 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     if (rc) return rc;
     p.out_ptr[i] = d.out_ptr[i];
   }
+  if (d.mode == kModeReduceScatter && d.world_size > 1) {
+    TCCL_CHECK_ARG(d.stage_local != 0, "reduce-scatter needs this rank's staging area");
+    rc = encode_map(&p.tma_stage, bf16, d.stage_local, d.out_cols, d.out_rows, d.ldo * 2, kChunkN,
+                    kSlabM, slots, slot_bytes, "staging");
+    if (rc) return rc;
+  }
   p.out_mc_ptr = d.out_mc_ptr;
   p.out_ld_bytes = d.ldo * 2;
   p.out_slot_bytes = static_cast<int64_t>(slot_bytes);

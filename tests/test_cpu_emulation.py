@@ -87,7 +87,32 @@ def test_late_rank_within_budget_is_fine():
 def test_tile_order_own_tiles_last():
     order = em.tile_order(2, 2, owners=4, rank=1, world_size=4)
     owners = [o for o, _, _ in order]
-    assert owners == [2] * 4 + [3] * 4 + [0] * 4 + [1] * 4       # rank+1 first, self last
-    assert [(lm, ln) for _, lm, ln in order[:4]] == [(0, 0), (0, 1), (1, 0), (1, 1)]
+    # rounds over the peers (rank+1, rank+2, rank+3 per tile row), own rows last
+    assert owners == [2, 2, 3, 3, 0, 0] * 2 + [1] * 4
+    assert [(lm, ln) for _, lm, ln in order[:6]] == [(0, 0), (0, 1)] * 3
+    assert [(lm, ln) for _, lm, ln in order[-4:]] == [(0, 0), (0, 1), (1, 0), (1, 1)]
     rot = em.tile_order(4, 1, rot_m_tiles=2)
     assert [lm for _, lm, _ in rot] == [2, 3, 0, 1]
+
+
+@pytest.mark.parametrize("m,n,ws,lag", [(8, 2, 2, 3), (5, 3, 4, 1), (6, 1, 8, 2), (4, 2, 3, 4),
+                                         (4, 2, 3, 9)])
+def test_tile_order_with_trailing_own_rows(m, n, ws, lag):
+    for rank in range(ws):
+        order = em.tile_order(m, n, owners=ws, rank=rank, world_size=ws, own_lag=lag)
+        # a permutation of all (owner, row, column) triples
+        assert sorted(order) == sorted((o, lm, ln) for o in range(ws) for lm in range(m)
+                                       for ln in range(n))
+        pos = {tile: i for i, tile in enumerate(order)}
+        eff = lag if lag <= m else m
+        for j in range(m):
+            # own row j comes after every remote row j + eff - 1 (clipped to the last round) ...
+            r = min(j + eff, m) - 1
+            for o in range(ws):
+                if o != rank:
+                    assert pos[(rank, j, 0)] > pos[(o, r, n - 1)]
+        # ... and at every instant all ranks address the same distance d = owner - rank
+        for t in range(len(order)):
+            o, lm, _ = order[t]
+            o0, lm0, _ = em.tile_order(m, n, owners=ws, rank=0, world_size=ws, own_lag=lag)[t]
+            assert (o - rank) % ws == o0 % ws and lm == lm0

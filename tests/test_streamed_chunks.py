@@ -9,7 +9,7 @@ from tileccl_b200.ops._fused import _tile_row_chunks
 def _plan(m_tiles, n_tiles, owners, rank, sub_m, a_rows):
     return NS(n_tiles_local=n_tiles, m_tiles_local=m_tiles, owners=owners,
               spec=NS(rank=rank, world_size=max(owners, 1), sub_m=sub_m, a_rows=a_rows,
-                      split_axis=0))
+                      split_axis=0, rs_own_lag=0))
 
 
 @pytest.mark.parametrize("m_tiles,n_tiles,owners,rank,sub_m", [
@@ -31,9 +31,19 @@ def test_chunks_cover_every_tile_and_row_once(m_tiles, n_tiles, owners, rank, su
     assert all(v == 1 for v in seen)
 
 
-def test_chunks_follow_owner_major_order():
-    # rank 1 of 4 visits owner 2's rows first and its own rows last
+def test_chunks_follow_the_round_order():
+    # rank 1 of 4: every round visits owners 2, 3, 0; its own rows come last
     chunks = _tile_row_chunks(_plan(32, 16, 4, 1, 4096, 16384))
-    assert chunks[0][2][0][0] == 2 * 4096
-    assert chunks[-1][2][-1] == (1 * 4096 + 4096 - (chunks[-1][2][-1][1] - chunks[-1][2][-1][0]),
-                                 2 * 4096)
+    first = chunks[0][2]
+    assert first[0][0] == 2 * 4096 and {lo // 4096 for lo, _ in first} == {0, 2, 3}
+    assert chunks[-1][2][-1][1] == 2 * 4096
+
+
+def test_visit_rows_matches_the_native_tile_order():
+    from tileccl_b200 import emulation as em
+    from tileccl_b200.ops._fused import visit_rows
+
+    for (m, ws, lag) in [(8, 2, 3), (5, 4, 1), (6, 8, 2), (4, 3, 0), (4, 3, 9)]:
+        for rank in range(ws):
+            native = em.tile_order(m, 2, owners=ws, rank=rank, world_size=ws, own_lag=lag)
+            assert [(o, lm) for o, lm, ln in native if ln == 0] == visit_rows(m, ws, rank, ws, lag)

@@ -111,7 +111,7 @@ class GemmDesc(C.Structure):
         ("trace", C.c_uint64),
         ("wait_budget_ns", C.c_uint64),
         ("tuning", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("rs_own_lag", C.c_int32),
     ]
 
 
@@ -173,6 +173,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_emul_gemm_reducescatter": [i32, i32, i32, i32, C.c_void_p, C.c_void_p, C.c_void_p, i32,
                                          i32, i32, i32, i32, i32, i32, C.POINTER(i32)],
         "tccl_plan_tile_order": [i32, i32, i32, i32, i32, i32, C.POINTER(i32), i32],
+        "tccl_plan_tile_order_ex": [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32), i32],
         "tccl_bootstrap_allgather": [i32, i32, C.c_char_p, i32, u64, i32, C.POINTER(u64),
                                      C.POINTER(i32)],
     }

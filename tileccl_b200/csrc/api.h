@@ -113,7 +113,7 @@ typedef struct TcclGemmDesc {
   uint64_t trace;                // uint64[tiles * 16] in device memory (4 stamps per epilogue warp), may be 0
   uint64_t wait_budget_ns;       // 0 = default (2 s)
   int32_t tuning;                // bit 0: TileGroup signals after a completed bulk store are relaxed adds
-  int32_t reserved0;
+  int32_t rs_own_lag;            // reduce-scatter: rounds by which the own (reducing) tile rows trail; 0 = all last
 } TcclGemmDesc;
 
 typedef struct TcclGemmPlanInfo {
@@ -201,6 +201,10 @@ int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32_t N, int32
 // (owner, tile row, tile column) of every tile in one rank's visiting order.
 int tccl_plan_tile_order(int32_t m_tiles_local, int32_t n_tiles_local, int32_t owners, int32_t rank,
                          int32_t world_size, int32_t rot_m_tiles, int32_t* out, int32_t capacity);
+// Same, with the reduce-scatter own rows trailing the remote rounds by `own_lag` (0 = all last).
+int tccl_plan_tile_order_ex(int32_t m_tiles_local, int32_t n_tiles_local, int32_t owners,
+                            int32_t rank, int32_t world_size, int32_t rot_m_tiles, int32_t own_lag,
+                            int32_t* out, int32_t capacity);
 
 // --------------------------------------------------------------------------
 // Device-primitive test harness (csrc/kernels/prim_test.cu): one launch acts as

@@ -252,11 +252,26 @@ extern "C" int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32
 }
 
 // Tile order of one rank as (owner, lm, ln) triples, for tests of the schedule.
+extern "C" int tccl_plan_tile_order_ex(int32_t m_tiles_local, int32_t n_tiles_local,
+                                       int32_t owners, int32_t rank, int32_t world_size,
+                                       int32_t rot_m_tiles, int32_t own_lag, int32_t* out,
+                                       int32_t capacity);
+
 extern "C" int tccl_plan_tile_order(int32_t m_tiles_local, int32_t n_tiles_local, int32_t owners,
                                     int32_t rank, int32_t world_size, int32_t rot_m_tiles,
                                     int32_t* out, int32_t capacity) {
+  return tccl_plan_tile_order_ex(m_tiles_local, n_tiles_local, owners, rank, world_size,
+                                 rot_m_tiles, 0, out, capacity);
+}
+
+extern "C" int tccl_plan_tile_order_ex(int32_t m_tiles_local, int32_t n_tiles_local,
+                                       int32_t owners, int32_t rank, int32_t world_size,
+                                       int32_t rot_m_tiles, int32_t own_lag, int32_t* out,
+                                       int32_t capacity) {
   TCCL_CHECK_ARG(m_tiles_local > 0 && n_tiles_local > 0 && owners >= 1 && out != nullptr, "bad argument");
-  const TileOrderShape shape{m_tiles_local, n_tiles_local, owners, rank, world_size, rot_m_tiles};
+  TCCL_CHECK_ARG(own_lag >= 0, "own_lag must be >= 0");
+  const TileOrderShape shape{m_tiles_local, n_tiles_local, owners, rank, world_size, rot_m_tiles,
+                             own_lag};
   const int n = tile_order_count(shape);
   TCCL_CHECK_ARG(capacity >= n, "output too small");
   for (int t = 0; t < n; ++t) {

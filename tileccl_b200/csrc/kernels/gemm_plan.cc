@@ -161,6 +161,8 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   p.status = d.status;
   p.trace = d.trace;
   p.tuning = d.tuning;
+  TCCL_CHECK_ARG(d.rs_own_lag >= 0, "rs_own_lag must be >= 0");
+  p.rs_own_lag = d.mode == kModeReduceScatter ? d.rs_own_lag : 0;
   p.wait_budget_ns = d.wait_budget_ns ? d.wait_budget_ns : 2000000000ull;
 
   const int groups = (p.m_tiles_local + p.group_m_tiles - 1) / p.group_m_tiles;

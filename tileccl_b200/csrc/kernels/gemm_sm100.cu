@@ -40,7 +40,7 @@ struct TileCoord {
 
 __device__ __forceinline__ TileCoord decode_tile(const FusedGemmParams& p, int t) {
   const TileOrderShape shape{p.m_tiles_local, p.n_tiles_local, p.owners, p.rank, p.world_size,
-                             p.rot_m_tiles};
+                             p.rot_m_tiles, p.rs_own_lag};
   const TileOrderEntry e = tile_order_decode(shape, t);
   TileCoord c;
   c.owner = e.owner;
@@ -434,26 +434,31 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       const int row = c.out_y + q * kSlabM + lane;   // destination-local row of this thread
 
       if (reduce_here && p.world_size > 1) {
-        // Signals still held back for earlier (remote) tiles go out before this warp may
-        // block: the peers' owners wait for them just as this rank is about to wait for
-        // theirs, and holding them across the wait closes a cycle around the ranks.
-        if (lane == 0 && (pend_valid[0] || pend_valid[1])) {
-          tma_store_wait_all<0>();
-          fence_proxy_async_all();
-          for (int i = 0; i < 2; ++i) {
-            if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
-            pend_valid[i] = false;
-          }
-        }
         // All peers' partial tiles of this TileGroup must have landed in local staging.
         const uint32_t target =
             p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
                                             p.n_tiles_local * kEpiWarps);
         uint32_t seen = 0;
         bool got = true;
-        if (lane == 0)
-          got = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
-                             &seen);
+        if (lane == 0) {
+          const uint32_t* ctr = reinterpret_cast<const uint32_t*>(p.sig_local) + group;
+          seen = ld_acquire_sys(ctr);
+          if (static_cast<int32_t>(seen - target) < 0) {
+            // This warp is about to block.  Signals it still holds back for earlier
+            // (remote) tiles go out first: the peers' owners wait for them just as this
+            // rank waits for theirs, and holding them across the wait would close a cycle
+            // around the ranks.
+            if (pend_valid[0] || pend_valid[1]) {
+              tma_store_wait_all<0>();
+              fence_proxy_async_all();
+              for (int i = 0; i < 2; ++i) {
+                if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
+                pend_valid[i] = false;
+              }
+            }
+            got = tile_wait_ge(ctr, target, wb, &seen);
+          }
+        }
         got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
         if (!got) {
           if (lane == 0) {
@@ -478,7 +483,9 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       };
       if (red_items > 0 && lane == 0) {
         // The partials are in local memory already: fetch the first ones while the
-        // accumulator is still being produced.
+        // accumulator is still being produced.  (They were written by peers and observed
+        // through the counter: order the bulk reads after that observation.)
+        fence_proxy_async_all();
         for (int i = 0; i < kRedBufs && i < red_items; ++i) red_issue(i);
       }
 
@@ -745,7 +752,7 @@ cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t s
   }
   // A launch that contains reducing (owner) tiles trades one pipeline stage for the ring
   // of prefetched partial tiles.
-  if (p.mode == kModeReduceScatter && p.world_size > 1)
+  if ((p.mode == kModeReduceScatter && p.world_size > 1) || (p.tuning & kTuneForceReduceVariant))
     fused_gemm_sm100_kernel<kStagesReduce><<<grid, kThreads, kSmemTotal, stream>>>(p);
   else
     fused_gemm_sm100_kernel<kStages><<<grid, kThreads, kSmemTotal, stream>>>(p);

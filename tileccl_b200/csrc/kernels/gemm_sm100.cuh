@@ -55,6 +55,9 @@ enum TuningBits : int {
   // would additionally wait for the younger bulk stores still in flight (measured: about
   // 6 us per tile and warp on NVLink 5 under load).
   kTuneRelaxedSignalAfterBulk = 1,
+  // Run every mode on the kernel variant with the shorter operand pipeline (the one
+  // reduce-scatter owners use); only useful to measure what the fourth stage is worth.
+  kTuneForceReduceVariant = 2,
 };
 enum EpilogueOp : int {
   kEpiNone = 0,
@@ -112,6 +115,7 @@ struct alignas(64) FusedGemmParams {
   // accumulator ready / stores issued / older stores complete / signalled
   uint64_t trace;
   int32_t tuning;                     // TuningBits
+  int32_t rs_own_lag;                 // TileOrderShape::own_lag
 };
 
 }  // namespace tileccl

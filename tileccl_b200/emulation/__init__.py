@@ -98,10 +98,13 @@ def gemm_reducescatter(A_list: Sequence[torch.Tensor], B_list: Sequence[torch.Te
 
 
 def tile_order(m_tiles_local: int, n_tiles_local: int, *, owners: int = 1, rank: int = 0,
-               world_size: int = 1, rot_m_tiles: int = 0) -> list:
-    """``(owner, tile_row, tile_col)`` in the order rank ``rank`` visits its tiles."""
+               world_size: int = 1, rot_m_tiles: int = 0, own_lag: int = 0) -> list:
+    """``(owner, tile_row, tile_col)`` in the order rank ``rank`` visits its tiles.
+
+    ``own_lag`` (reduce-scatter): rounds by which the rank's own tile rows trail the
+    remote rows; 0 keeps all own rows for the end."""
     n = m_tiles_local * n_tiles_local * owners
     buf = (C.c_int32 * (3 * n))()
-    _native.call("tccl_plan_tile_order", m_tiles_local, n_tiles_local, owners, rank, world_size,
-                 rot_m_tiles, buf, n)
+    _native.call("tccl_plan_tile_order_ex", m_tiles_local, n_tiles_local, owners, rank, world_size,
+                 rot_m_tiles, own_lag, buf, n)
     return [(buf[3 * i], buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]

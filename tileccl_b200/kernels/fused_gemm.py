@@ -125,6 +125,7 @@ class FusedGemmSpec:
     status_ptr: int = 0
     trace_ptr: int = 0
     tuning: int = -1            # -1: TILECCL_TUNING from the environment (default 1)
+    rs_own_lag: int = 0         # reduce-scatter: rounds the own tile rows trail (0 = all last)
     wait_budget_ns: int = 0
 
 
@@ -161,6 +162,7 @@ class FusedGemmPlan:
         d.grid = spec.grid
         d.status = spec.status_ptr
         d.trace = spec.trace_ptr
+        d.rs_own_lag = spec.rs_own_lag
         d.tuning = spec.tuning if spec.tuning >= 0 else int(os.environ.get("TILECCL_TUNING", "1"))
         d.wait_budget_ns = spec.wait_budget_ns
         handle = C.c_void_p()

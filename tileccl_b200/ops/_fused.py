@@ -77,6 +77,25 @@ def default_push_mode(ctx) -> int:
     return fg.PUSH_TMA
 
 
+def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
+    """Rounds by which a reduce-scatter rank's own tile rows trail its remote rows.
+
+    A round sends one tile row to every peer.  The own row j is reduced once the
+    peers' row j has arrived, so it trails by the time a pushed row needs to land
+    under load (about 40 us with the queues the kernel keeps in flight).  0 means
+    "own rows last" (nothing to overlap, or too few rows).
+    """
+    env = os.environ.get("TILECCL_RS_OWN_LAG")
+    if env is not None:
+        return max(0, int(env))
+    if ws < 2 or m_tiles < 2:
+        return 0
+    round_bytes = (ws - 1) * n_tiles * fg.BLOCK_M * fg.BLOCK_N * 2
+    round_us = round_bytes / 690e3            # measured NVLink 5 push rate, bytes per us
+    lag = int(-(-40.0 // round_us))
+    return lag if 1 <= lag < m_tiles else 0
+
+
 def default_group_m_tiles(m_tiles: int) -> int:
     """Finest TileGroup (one tile row) unless that would need more than MAX_GROUPS counters."""
     return max(1, -(-m_tiles // MAX_GROUPS))
@@ -160,38 +179,52 @@ def _b_dims(B: torch.Tensor, b_is_nk: bool) -> tuple:
 # --------------------------------------------------------------------------
 # A operand streamed from pinned host memory while the kernel runs
 # --------------------------------------------------------------------------
+def visit_rows(m_tiles: int, owners: int, rank: int, world_size: int, own_lag: int = 0) -> list:
+    """``(owner, tile_row)`` of every tile row in the order the kernel visits them
+    (the row-level view of csrc/plan/tile_order.h; rot_m_tiles = 0)."""
+    if owners <= 1:
+        return [(rank, r) for r in range(m_tiles)]
+    lag = m_tiles if own_lag <= 0 or own_lag > m_tiles else own_lag
+    rows = []
+    for r in range(m_tiles):
+        rows += [((rank + d) % world_size, r) for d in range(1, owners)]
+        if r >= lag:
+            rows.append((rank, r - lag))
+    rows += [(rank, j) for j in range(m_tiles - lag, m_tiles)]
+    return rows
+
+
 def _tile_row_chunks(plan, min_tiles: int = 2 * 148, max_chunks: int = 8) -> list:
     """Split the rank's tile order into runs of whole tile rows.
 
     Returns ``[(tile_begin, tile_end, [(row0, row1), ...]), ...]`` where the row
     ranges are the rows of A the run reads.  Runs follow the kernel's visiting
-    order (owner-major for reduce-scatter, see csrc/plan/tile_order.h), so the
-    host copy of run i only has to stay ahead of the launch of run i.
+    order (rounds over the owners for reduce-scatter, see csrc/plan/tile_order.h),
+    so the host copy of run i only has to stay ahead of the launch of run i.
     """
     n_t = plan.n_tiles_local
-    rows_total = plan.m_tiles_local * plan.owners           # tile rows in visiting order
+    spec = plan.spec
+    order = visit_rows(plan.m_tiles_local, plan.owners, spec.rank, spec.world_size,
+                       getattr(spec, "rs_own_lag", 0))
+    rows_total = len(order)
     per_chunk = max(1, -(-min_tiles // n_t))
     n_chunks = max(1, min(max_chunks, rows_total // per_chunk))
     bounds = [round(i * rows_total / n_chunks) for i in range(n_chunks + 1)]
-    spec = plan.spec
     chunks = []
     for i in range(n_chunks):
         r0, r1 = bounds[i], bounds[i + 1]
         if r1 <= r0:
             continue
         ranges = []
-        tr = r0
-        while tr < r1:
-            oi, lm = divmod(tr, plan.m_tiles_local)
-            lm_end = min(plan.m_tiles_local, lm + (r1 - tr))
-            base = 0
-            if plan.owners > 1 and spec.split_axis == 0:
-                owner = (spec.rank + 1 + oi) % spec.world_size
-                base = owner * spec.sub_m
+        for owner, lm in order[r0:r1]:
+            base = owner * spec.sub_m if plan.owners > 1 and spec.split_axis == 0 else 0
+            limit = spec.sub_m if plan.owners > 1 else spec.a_rows
             lo = base + lm * fg.BLOCK_M
-            hi = base + min(spec.sub_m if plan.owners > 1 else spec.a_rows, lm_end * fg.BLOCK_M)
-            ranges.append((lo, min(hi, spec.a_rows)))
-            tr += lm_end - lm
+            hi = min(base + min(limit, (lm + 1) * fg.BLOCK_M), spec.a_rows)
+            if ranges and ranges[-1][1] == lo:
+                ranges[-1] = (ranges[-1][0], hi)       # merge adjacent rows
+            else:
+                ranges.append((lo, hi))
         chunks.append((r0 * n_t, r1 * n_t, ranges))
     return chunks
 
@@ -390,6 +423,8 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             ldb=B.stride(0), k=K, sub_m=sub_m, sub_n=sub_n, out_ptrs=dests, ldo=sub_n,
             out_rows=sub_m, out_cols=sub_n, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank,
             world_size=ws, split_axis=split_axis, out_slot_elems=sub_m * sub_n, out_slots=2 * ws,
+            rs_own_lag=(default_rs_own_lag(ws, m_tiles, -(-sub_n // fg.BLOCK_N))
+                        if ws > 1 and _in_kernel_waits_ok(ctx) else 0),
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
             stage_local=stage_ptr, status_ptr=status_block(ctx).data_ptr(),
             wait_budget_ns=wait_budget_ns()))

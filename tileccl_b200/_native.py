@@ -112,6 +112,7 @@ class GemmDesc(C.Structure):
         ("wait_budget_ns", C.c_uint64),
         ("tuning", C.c_int32),
         ("rs_own_lag", C.c_int32),
+        ("ident_ptr", C.c_uint64),
     ]
 
 

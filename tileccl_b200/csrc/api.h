@@ -114,6 +114,7 @@ typedef struct TcclGemmDesc {
   uint64_t wait_budget_ns;       // 0 = default (2 s)
   int32_t tuning;                // bit 0: TileGroup signals after a completed bulk store are relaxed adds
   int32_t rs_own_lag;            // reduce-scatter: rounds by which the own (reducing) tile rows trail; 0 = all last
+  uint64_t ident_ptr;            // reduce-scatter: 128 x 128 identity matrix of the operand dtype (row-major)
 } TcclGemmDesc;
 
 typedef struct TcclGemmPlanInfo {

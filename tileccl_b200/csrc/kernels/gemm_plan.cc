@@ -114,8 +114,11 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   }
   if (d.mode == kModeReduceScatter && d.world_size > 1) {
     TCCL_CHECK_ARG(d.stage_local != 0, "reduce-scatter needs this rank's staging area");
-    rc = encode_map(&p.tma_stage, bf16, d.stage_local, d.out_cols, d.out_rows, d.ldo * 2, kChunkN,
-                    kSlabM, slots, slot_bytes, "staging");
+    TCCL_CHECK_ARG(d.ident_ptr != 0, "reduce-scatter needs the 128 x 128 identity operand");
+    rc = encode_map(&p.tma_stage, bf16, d.stage_local, d.out_cols, d.out_rows, d.ldo * 2, 64, kBK,
+                    slots, slot_bytes, "staging");
+    if (rc) return rc;
+    rc = encode_map(&p.tma_ident, bf16, d.ident_ptr, kBM, kBM, kBM * 2, kBK, kBM, 0, 0, "identity");
     if (rc) return rc;
   }
   p.out_mc_ptr = d.out_mc_ptr;

@@ -89,15 +89,12 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
 
 }  // namespace
 
-template <int kStagesT>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  constexpr bool kReduceRing = kStagesT == kStagesReduce;
-  const uint32_t smem_epi = smem_base + kStagesT * kStageBytes;
-  const uint32_t smem_red = smem_epi + kSmemEpi;          // only with kReduceRing
+  const uint32_t smem_epi = smem_base + kSmemPipe;
   const uint32_t smem_ctl = smem_base + kSmemPipe + kSmemEpi;
   uint8_t* ctl_generic = smem_raw + (smem_ctl - smem_u32(smem_raw));
 
@@ -114,17 +111,14 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // communication warps poll it to learn which tiles of C they may forward.
   const uint32_t done_count = tmem_slot + 8;
   volatile uint32_t* done_count_g = tmem_slot_g + 2;
-  // "partial tile landed in the ring" barriers: kEpiWarps x kRedBufs x 8 B
-  const uint32_t bar_red = tmem_slot + 16;
-  static_assert(8 * (2 * kStages + 2 * kAccBufs + 1) + 16 + 8 * kEpiWarps * kRedBufs <= kSmemCtl,
-                "control block overflow");
+  static_assert(8 * (2 * kStages + 2 * kAccBufs + 1) + 16 <= kSmemCtl, "control block overflow");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStagesT; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
@@ -133,8 +127,6 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       mbar_init(bar_acc_empty + 8 * a, kEpiWarps);
     }
     mbar_init(bar_drain, 1);
-    if (kReduceRing)
-      for (int i = 0; i < kEpiWarps * kRedBufs; ++i) mbar_init(bar_red + 8 * i, 1);
     *abort_flag = 0;
     *done_count_g = 0;
     mbar_fence_init();
@@ -277,12 +269,50 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             for (int i = 0; i < kBN / 64; ++i)
               tma_load_2d(sb + i * (64 * kBK * 2), &p.tma_b, c.b_col0 + i * 64, kb * kBK, bar);
           }
-          if (++stage == kStagesT) { stage = 0; phase ^= 1u; }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok && p.mode == kModeReduceScatter && p.world_size > 1 && c.owner == p.rank) {
+          // Own tile: after its K blocks, the peers' staged partial tiles go through the
+          // same pipeline (two 64-row halves each, in rank order) next to the identity.
+          const int group = c.lm / p.group_m_tiles;
+          const uint32_t target =
+              p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
+                                              p.n_tiles_local * kEpiWarps);
+          uint32_t seen = 0;
+          if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
+                            &seen)) {
+            report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();   // bulk reads of the partials come after that observation
+          for (int src = 0; ok && src < p.world_size; ++src) {
+            if (src == p.rank) continue;
+            const int z = p.stage_parity * p.world_size + src;
+            for (int hb = 0; hb < kBM / kBK; ++hb) {
+              if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wb)) {
+                report_status(status, kStatusTimeoutMbarrier, 12, 0, 0, p.rank, t);
+                ok = false;
+                break;
+              }
+              const uint32_t sa = smem_base + stage * kStageBytes;
+              const uint32_t sb = sa + kStageABytes;
+              const uint32_t bar = bar_full + 8 * stage;
+              mbar_expect_tx(bar, kStageBytes);
+              tma_load_2d(sa, &p.tma_ident, hb * kBK, 0, bar);
+#pragma unroll
+              for (int i = 0; i < kBN / 64; ++i)
+                tma_load_3d(sb + i * (64 * kBK * 2), &p.tma_stage, c.out_x + i * 64,
+                            c.out_y + hb * kBK, z, bar);
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            }
+          }
         }
       }
       if (!ok) {
         // Let loads that are still in flight land before the CTA retires.
-        for (int s = 0; s < kStagesT; ++s)
+        for (int s = 0; s < kStages; ++s)
           for (int it = 0; it < 100000 && !mbar_try_wait(bar_full + 8 * s, 0) &&
                            !mbar_try_wait(bar_full + 8 * s, 1); ++it) {}
       }
@@ -291,6 +321,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     // ------------------------------- MMA issuer -------------------------------
     if (elect_one_sync()) {
       const uint32_t idesc = umma_idesc_f16(p.is_bf16, 0, p.b_kmajor ? 0 : 1, kBM, kBN);
+      const uint32_t idesc_red = umma_idesc_f16(p.is_bf16, 0, 1, kBM, kBN);
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
@@ -302,7 +333,11 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        // Own reduce-scatter tiles continue with the peers' partial tiles (see the producer).
+        const bool reduce_tile = p.mode == kModeReduceScatter && p.world_size > 1 &&
+                                 decode_tile(p, t).owner == p.rank;
+        const int kb_total = p.k_blocks + (reduce_tile ? (kBM / kBK) * (p.world_size - 1) : 0);
+        for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, wb)) {
             report_status(status, kStatusTimeoutMbarrier, 21, 0, 0, p.rank, t);
             ok = false;
@@ -314,13 +349,16 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
             const uint64_t da = umma_smem_desc_sw128(sa + k * (kUmmaK * 2), 16, 1024);
+            // A staged partial tile is always an MN-major ([K', N] row-major) B operand.
+            const bool b_k = p.b_kmajor && kb < p.k_blocks;
             const uint64_t db =
-                p.b_kmajor ? umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024)
-                           : umma_smem_desc_sw128(sb + k * (kUmmaK * 128), 64 * kBK * 2, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                b_k ? umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024)
+                    : umma_smem_desc_sw128(sb + k * (kUmmaK * 128), 64 * kBK * 2, 1024);
+            umma_f16(d_tmem, da, db, b_k == (p.b_kmajor != 0) ? idesc : idesc_red,
+                     (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
-          if (++stage == kStagesT) { stage = 0; phase ^= 1u; }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         umma_commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
@@ -405,11 +443,6 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     // lane 0: the last two tiles whose signals have not been sent yet ([0] = older)
     bool pend_valid[2] = {false, false};
     bool slab_pending = false;   // lane 0: a slab whose completion the comm warps still await
-    // Ring of staged partial tiles (reduce-scatter owner): items are (chunk, source rank)
-    // pairs in consumption order; red_base counts the items of earlier tiles.
-    uint32_t red_base = 0;
-    const uint32_t my_red = smem_red + q * (kRedBufs * kEpiBufBytes);
-    const uint32_t my_red_bar = bar_red + 8 * (q * kRedBufs);
     int pend_owner[2] = {0, 0}, pend_group[2] = {0, 0};
     // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
     auto send_signal = [&](int owner, int g, bool after_bulk) {
@@ -431,62 +464,19 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       const TileCoord c = decode_tile(p, t);
       const int group = c.lm / p.group_m_tiles;
       const bool reduce_here = p.mode == kModeReduceScatter && c.owner == p.rank;
-      const int row = c.out_y + q * kSlabM + lane;   // destination-local row of this thread
 
-      if (reduce_here && p.world_size > 1) {
-        // All peers' partial tiles of this TileGroup must have landed in local staging.
-        const uint32_t target =
-            p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
-                                            p.n_tiles_local * kEpiWarps);
-        uint32_t seen = 0;
-        bool got = true;
-        if (lane == 0) {
-          const uint32_t* ctr = reinterpret_cast<const uint32_t*>(p.sig_local) + group;
-          seen = ld_acquire_sys(ctr);
-          if (static_cast<int32_t>(seen - target) < 0) {
-            // This warp is about to block.  Signals it still holds back for earlier
-            // (remote) tiles go out first: the peers' owners wait for them just as this
-            // rank waits for theirs, and holding them across the wait would close a cycle
-            // around the ranks.
-            if (pend_valid[0] || pend_valid[1]) {
-              tma_store_wait_all<0>();
-              fence_proxy_async_all();
-              for (int i = 0; i < 2; ++i) {
-                if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
-                pend_valid[i] = false;
-              }
-            }
-            got = tile_wait_ge(ctr, target, wb, &seen);
-          }
-        }
-        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
-        if (!got) {
-          if (lane == 0) {
-            report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
-            *abort_flag = 1;
-          }
-          ok = false;
-          break;
-        }
-      }
-
-      const int red_items = (kReduceRing && reduce_here) ? n_chunks * (p.world_size - 1) : 0;
-      // lane 0: start the TMA load of item i of this tile into its ring slot
-      auto red_issue = [&](int i) {
-        const int ch = i / (p.world_size - 1), pi = i - ch * (p.world_size - 1);
-        const int src = pi < p.rank ? pi : pi + 1;
-        const uint32_t slot = (red_base + static_cast<uint32_t>(i)) % kRedBufs;
-        mbar_expect_tx(my_red_bar + 8 * slot, kEpiBufBytes);
-        tma_load_3d(my_red + slot * kEpiBufBytes, &p.tma_stage, c.out_x + ch * kChunkN,
-                    c.out_y + q * kSlabM, p.stage_parity * p.world_size + src,
-                    my_red_bar + 8 * slot);
-      };
-      if (red_items > 0 && lane == 0) {
-        // The partials are in local memory already: fetch the first ones while the
-        // accumulator is still being produced.  (They were written by peers and observed
-        // through the counter: order the bulk reads after that observation.)
+      if (reduce_here && p.world_size > 1 && lane == 0 && (pend_valid[0] || pend_valid[1]) &&
+          !mbar_try_wait(bar_acc_full + 8 * acc, acc_phase)) {
+        // The accumulator of an own tile may be held up until the peers' partial tiles have
+        // arrived (the producer warp waits for them).  Signals this warp still holds back
+        // for earlier remote tiles go out before it blocks: the peers' owners wait for them
+        // just as this rank waits for theirs, and holding them would close a cycle.
+        tma_store_wait_all<0>();
         fence_proxy_async_all();
-        for (int i = 0; i < kRedBufs && i < red_items; ++i) red_issue(i);
+        for (int i = 0; i < 2; ++i) {
+          if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
+          pend_valid[i] = false;
+        }
       }
 
       if (!mbar_wait(bar_acc_full + 8 * acc, acc_phase, wb)) {
@@ -531,50 +521,6 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         }
 
         const int col0 = c.out_x + ch * kChunkN;     // destination-local column of v[0]
-        if (kReduceRing && red_items > 0) {
-          // Add the other ranks' partials (16-bit) from the prefetch ring, in rank order.
-          for (int pi = 0; ok && pi < p.world_size - 1; ++pi) {
-            const int i = ch * (p.world_size - 1) + pi;
-            const uint32_t g = red_base + static_cast<uint32_t>(i);
-            const uint32_t slot = g % kRedBufs;
-            if (!mbar_wait(my_red_bar + 8 * slot, (g / kRedBufs) & 1u, wb)) {
-              if (lane == 0) report_status(status, kStatusTimeoutMbarrier, 42, 0, 0, p.rank, t);
-              ok = false;
-              break;
-            }
-            const uint32_t sred = my_red + slot * kEpiBufBytes + lane * 128;
-#pragma unroll
-            for (int j = 0; j < kChunkN / 8; ++j) {
-              uint4 w;
-              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                           : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
-                           : "r"(sred + ((j ^ (lane & 7)) << 4))
-                           : "memory");
-              tile_accumulate_16x8(bf16, &v[j * 8], w);
-            }
-            __syncwarp();
-            if (lane == 0 && i + kRedBufs < red_items) red_issue(i + kRedBufs);
-          }
-          if (!ok) break;
-        } else if (reduce_here && p.world_size > 1 && row < p.out_rows) {
-          // Add the other ranks' partials (16-bit, written into this rank's staging).
-          for (int src = 0; src < p.world_size; ++src) {
-            if (src == p.rank) continue;
-            const char* base = reinterpret_cast<const char*>(p.stage_local) +
-                               static_cast<int64_t>(p.stage_parity * p.world_size + src) *
-                                   p.out_slot_bytes +
-                               static_cast<int64_t>(row) * p.out_cols * 2 +
-                               static_cast<int64_t>(col0) * 2;
-#pragma unroll
-            for (int j = 0; j < kChunkN / 8; ++j) {
-              if (col0 + j * 8 < p.out_cols) {
-                uint4 w = ld_remote_v4(base + j * 16);
-                tile_accumulate_16x8(bf16, &v[j * 8], w);
-              }
-            }
-          }
-        }
-
         // Staging buffer `buf` was last read by the stores committed two chunks ago.
         if (lane == 0) tma_store_wait_read<kEpiBufs - 1>();
         __syncwarp();
@@ -689,7 +635,6 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       if (p.trace != 0 && lane == 0)
         reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 3] = globaltimer_ns();
 
-      red_base += static_cast<uint32_t>(red_items);
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
     if (lane == 0) {
@@ -742,20 +687,12 @@ cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t s
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_set[dev]) {
-    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<kStages>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<kStagesReduce>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kSmemTotal);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  // A launch that contains reducing (owner) tiles trades one pipeline stage for the ring
-  // of prefetched partial tiles.
-  if ((p.mode == kModeReduceScatter && p.world_size > 1) || (p.tuning & kTuneForceReduceVariant))
-    fused_gemm_sm100_kernel<kStagesReduce><<<grid, kThreads, kSmemTotal, stream>>>(p);
-  else
-    fused_gemm_sm100_kernel<kStages><<<grid, kThreads, kSmemTotal, stream>>>(p);
+  fused_gemm_sm100_kernel<<<grid, kThreads, kSmemTotal, stream>>>(p);
   return cudaGetLastError();
 }
 

@@ -12,10 +12,6 @@ static constexpr int kBN = 256;       // columns of C per tile (= UMMA N, fp32 T
 static constexpr int kBK = 64;        // K elements per stage (64 x 2 B = one 128-byte swizzle row)
 static constexpr int kUmmaK = 16;     // K per tcgen05.mma for 16-bit inputs
 static constexpr int kStages = 4;     // TMA -> MMA ring depth
-// Reduce-scatter owners give one pipeline stage to a ring of staged partial tiles that
-// TMA prefetches for the reducing epilogue (3 x 4 KiB per epilogue warp).
-static constexpr int kStagesReduce = 3;
-static constexpr int kRedBufs = 3;
 static constexpr int kAccBufs = 2;    // TMEM accumulator double buffer (2 x 256 columns)
 static constexpr int kEpiWarps = 4;   // epilogue warps (one per 32-lane TMEM quarter)
 static constexpr int kThreads = 256;  // warp 0 TMA, 1 MMA, 2 TMEM alloc, 3 waiter, 4-7 epilogue
@@ -29,9 +25,6 @@ static constexpr int kEpiBufBytes = kSlabM * kChunkN * 2;  // 4 KiB per (warp, b
 static constexpr int kEpiBufs = 2;
 static constexpr int kSmemPipe = kStages * kStageBytes;
 static constexpr int kSmemEpi = kEpiWarps * kEpiBufs * kEpiBufBytes;
-static constexpr int kSmemRed = kEpiWarps * kRedBufs * kEpiBufBytes;
-static_assert(kStagesReduce * kStageBytes + kSmemRed <= kStages * kStageBytes,
-              "the partial-tile ring must fit in the pipeline stages it replaces");
 static constexpr int kSmemCtl = 256;
 static constexpr int kSmemTotal = kSmemPipe + kSmemEpi + kSmemCtl + 1024;  // + alignment slack
 
@@ -55,9 +48,6 @@ enum TuningBits : int {
   // would additionally wait for the younger bulk stores still in flight (measured: about
   // 6 us per tile and warp on NVLink 5 under load).
   kTuneRelaxedSignalAfterBulk = 1,
-  // Run every mode on the kernel variant with the shorter operand pipeline (the one
-  // reduce-scatter owners use); only useful to measure what the fourth stage is worth.
-  kTuneForceReduceVariant = 2,
 };
 enum EpilogueOp : int {
   kEpiNone = 0,
@@ -68,7 +58,11 @@ struct alignas(64) FusedGemmParams {
   CUtensorMap tma_a;                  // A as [rows, K], box {64, 128}, 128B swizzle
   CUtensorMap tma_b;                  // B as [N, K] box {64, 256} or [K, N] box {64, 64}
   CUtensorMap tma_out[kMaxRanks];     // 3-D {cols, rows, slots}, box {64, 32, 1}
-  CUtensorMap tma_stage;              // this rank's reduce-scatter staging, same geometry (loads)
+  // Reduce-scatter owners sum the peers' partial tiles on the tensor cores: a staged
+  // partial tile P (128 x 256, 16-bit) enters the operand pipeline as a [K'=128, N=256]
+  // B operand next to a 128 x 128 identity as A operand, so acc += I * P = P in fp32.
+  CUtensorMap tma_stage;              // this rank's staging {cols, rows, slots}, box {64, 64, 1}
+  CUtensorMap tma_ident;              // identity [128, 128], box {64, 128}
   // raw views of the same destinations for the non-TMA push modes
   uint64_t out_ptr[kMaxRanks];
   uint64_t out_mc_ptr;                // multicast alias of the destination (push mode 2)

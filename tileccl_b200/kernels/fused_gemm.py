@@ -126,7 +126,22 @@ class FusedGemmSpec:
     trace_ptr: int = 0
     tuning: int = -1            # -1: TILECCL_TUNING from the environment (default 1)
     rs_own_lag: int = 0         # reduce-scatter: rounds the own tile rows trail (0 = all last)
+    ident_ptr: int = 0          # reduce-scatter: 128 x 128 identity of `dtype` (see identity_operand)
     wait_budget_ns: int = 0
+
+
+_IDENTITY = {}
+
+
+def identity_operand(dtype: torch.dtype, device) -> torch.Tensor:
+    """The 128 x 128 identity a reduce-scatter owner multiplies the peers' staged partial
+    tiles with, so that the tensor cores add them to the accumulator (acc += I @ P)."""
+    device = torch.device(device)
+    key = (dtype, device.index if device.index is not None else torch.cuda.current_device())
+    t = _IDENTITY.get(key)
+    if t is None:
+        t = _IDENTITY[key] = torch.eye(BLOCK_M, dtype=dtype, device=device).contiguous()
+    return t
 
 
 class FusedGemmPlan:
@@ -163,6 +178,7 @@ class FusedGemmPlan:
         d.status = spec.status_ptr
         d.trace = spec.trace_ptr
         d.rs_own_lag = spec.rs_own_lag
+        d.ident_ptr = spec.ident_ptr
         d.tuning = spec.tuning if spec.tuning >= 0 else int(os.environ.get("TILECCL_TUNING", "1"))
         d.wait_budget_ns = spec.wait_budget_ns
         handle = C.c_void_p()

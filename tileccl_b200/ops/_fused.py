@@ -423,6 +423,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             ldb=B.stride(0), k=K, sub_m=sub_m, sub_n=sub_n, out_ptrs=dests, ldo=sub_n,
             out_rows=sub_m, out_cols=sub_n, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank,
             world_size=ws, split_axis=split_axis, out_slot_elems=sub_m * sub_n, out_slots=2 * ws,
+            ident_ptr=fg.identity_operand(A.dtype, A.device).data_ptr() if ws > 1 else 0,
             rs_own_lag=(default_rs_own_lag(ws, m_tiles, -(-sub_n // fg.BLOCK_N))
                         if ws > 1 and _in_kernel_waits_ok(ctx) else 0),
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,

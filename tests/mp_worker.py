@@ -101,6 +101,7 @@ def main() -> int:
 
     for nvls_off in ("1", "0"):
         os.environ["TILECCL_DISABLE_NVLS"] = nvls_off
+        os.environ["TILECCL_FORCE_NVLS"] = "1"       # also at two ranks
         for dtype, tol in ((torch.float16, 2e-2), (torch.float32, 1e-5)):
             for n in (1024, 8198, 1_000_000):
                 n = n // ws * ws
@@ -127,6 +128,7 @@ def main() -> int:
                 dist.barrier()
     coll.check_status(ctx.heap)
     os.environ["TILECCL_DISABLE_NVLS"] = "0"
+    os.environ["TILECCL_FORCE_NVLS"] = "0"
 
     tokens, hidden, ffn = 128 * ws * 2, 512, 256 * ws
     mlp = TPMLP(ctx, tokens=tokens, hidden=hidden, ffn=ffn, dtype=torch.bfloat16, seed=3)

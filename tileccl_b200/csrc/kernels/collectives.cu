@@ -117,10 +117,20 @@ __device__ __forceinline__ bool vec_ok(const void* a, const void* b, uint64_t by
 }
 __device__ __forceinline__ void copy_vec(char* dst, const char* src, uint64_t bytes, int es) {
   if (vec_ok(dst, src, bytes)) {
+    // Eight 16-byte loads in flight per thread before the first store: the copy is bound by
+    // the link, not by one load latency per store.
+    constexpr int U = 8;
     const uint64_t n = bytes >> 4;
     const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-         i += stride)
+    uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    for (; i + (U - 1) * stride < n; i += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) v[j] = *reinterpret_cast<const uint4*>(src + ((i + j * stride) << 4));
+#pragma unroll
+      for (int j = 0; j < U; ++j) st_remote_v4(dst + ((i + j * stride) << 4), v[j]);
+    }
+    for (; i < n; i += stride)
       st_remote_v4(dst + (i << 4), *reinterpret_cast<const uint4*>(src + (i << 4)));
   } else if (es == 8) {
     copy_elems<uint64_t>(dst, src, bytes);
@@ -133,9 +143,18 @@ __device__ __forceinline__ void copy_vec(char* dst, const char* src, uint64_t by
   }
 }
 __device__ __forceinline__ void copy_vec_mc(char* mc_dst, const char* src, uint64_t bytes) {
+  constexpr int U = 8;
   const uint64_t n = bytes >> 4;
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-  for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+  uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + (U - 1) * stride < n; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) v[j] = *reinterpret_cast<const uint4*>(src + ((i + j * stride) << 4));
+#pragma unroll
+    for (int j = 0; j < U; ++j) multimem_st_v4(mc_dst + ((i + j * stride) << 4), v[j]);
+  }
+  for (; i < n; i += stride)
     multimem_st_v4(mc_dst + (i << 4), *reinterpret_cast<const uint4*>(src + (i << 4)));
 }
 
@@ -244,7 +263,58 @@ __global__ void __launch_bounds__(512) collective_kernel(const CollParams p) {
         // multiple of 16 bytes: then everything goes through the scalar loop below.
         const bool aligned = ((chunk_off | reinterpret_cast<uint64_t>(dst)) & 15u) == 0;
         const uint64_t n = aligned ? (my_bytes >> 4) : 0;
-        for (uint64_t i = gtid; i < n; i += gstride) {
+        uint64_t i = gtid;
+        if (p.use_multimem) {
+          // In-switch reduction: several multimem.ld_reduce in flight per thread, then the
+          // stores (one multimem.st reaches every rank).
+          constexpr int U = 4;
+          for (; i + (U - 1) * gstride < n; i += U * gstride) {
+            uint4 o[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+              o[j] = mc_reduce(p.dtype, mcast<char>(p, p.src) + chunk_off + ((i + j * gstride) << 4));
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+              const uint64_t ii = i + j * gstride;
+              if (p.op == kReduceScatter) *reinterpret_cast<uint4*>(dst + (ii << 4)) = o[j];
+              else multimem_st_v4(mcast<char>(p, p.dst) + chunk_off + (ii << 4), o[j]);
+            }
+          }
+        }
+        if (!p.use_multimem) {
+          // Peer loads of two items in flight per thread before the first accumulate.
+          for (; i + gstride < n; i += 2 * gstride) {
+            uint4 v0[kMaxRanks], v1[kMaxRanks];
+            const uint64_t off0 = chunk_off + (i << 4), off1 = chunk_off + ((i + gstride) << 4);
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < ws) {
+                v0[r] = ld_remote_v4(peer<char>(p, p.src, r) + off0);
+                v1[r] = ld_remote_v4(peer<char>(p, p.src, r) + off1);
+              }
+            float a0[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            float a1[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+              if (r < ws) {
+                accumulate(p.dtype, a0, v0[r]);
+                accumulate(p.dtype, a1, v1[r]);
+              }
+            const uint4 o0 = finish(p.dtype, a0), o1 = finish(p.dtype, a1);
+            if (p.op == kReduceScatter) {
+              *reinterpret_cast<uint4*>(dst + (i << 4)) = o0;
+              *reinterpret_cast<uint4*>(dst + ((i + gstride) << 4)) = o1;
+            } else {
+#pragma unroll
+              for (int r = 0; r < kMaxRanks; ++r)
+                if (r < ws) {
+                  st_remote_v4(peer<char>(p, p.dst, r) + off0, o0);
+                  st_remote_v4(peer<char>(p, p.dst, r) + off1, o1);
+                }
+            }
+          }
+        }
+        for (; i < n; i += gstride) {
           uint4 out;
           const uint64_t off = chunk_off + (i << 4);
           if (p.use_multimem) {

@@ -55,6 +55,18 @@ def _ctx_or_current(ctx):
     return current_context()
 
 
+def _cached_plan(ctx, key, build):
+    """Plans of the one-call collectives, kept per context: a repeated call on the same
+    buffer skips contract resolution (the small-message latency is host time)."""
+    cache = ctx.__dict__.setdefault("_collective_plans", {})
+    plan = cache.get(key)
+    if plan is None:
+        if len(cache) >= 512:
+            cache.clear()
+        plan = cache[key] = build()
+    return plan
+
+
 def _check_storage(storage_kind: str) -> None:
     if storage_kind not in _STORAGE_KINDS:
         raise ValueError(f"storage_kind must be one of {_STORAGE_KINDS}, got {storage_kind!r}")
@@ -599,8 +611,10 @@ def build_allgather_plan(src, output, *, ctx=None, storage_kind="symmetric") -> 
 
 def allgather(src, output, *, ctx=None, storage_kind="symmetric"):
     """Rank-major concatenation of every rank's ``src`` into ``output`` on every rank."""
-    return build_allgather_plan(src, output, ctx=ctx, storage_kind=storage_kind).execute(
-        src, output, validate=False)
+    ctx = _ctx_or_current(ctx)
+    key = ("allgather", src.data_ptr(), output.data_ptr(), src.numel(), src.dtype, storage_kind)
+    return _cached_plan(ctx, key, lambda: build_allgather_plan(
+        src, output, ctx=ctx, storage_kind=storage_kind)).execute(src, output, validate=False)
 
 
 @dataclass(frozen=True)
@@ -656,8 +670,10 @@ def build_allreduce_plan(tensor, *, ctx=None, op="sum", storage_kind="symmetric"
 
 def allreduce(tensor, *, ctx=None, op="sum", storage_kind="symmetric"):
     """In-place sum over ranks."""
-    return build_allreduce_plan(tensor, ctx=ctx, op=op, storage_kind=storage_kind).execute(
-        tensor, validate=False)
+    ctx = _ctx_or_current(ctx)
+    key = ("allreduce", tensor.data_ptr(), tensor.numel(), tensor.dtype, op, storage_kind)
+    return _cached_plan(ctx, key, lambda: build_allreduce_plan(
+        tensor, ctx=ctx, op=op, storage_kind=storage_kind)).execute(tensor, validate=False)
 
 
 @dataclass(frozen=True)
@@ -703,8 +719,12 @@ def build_reduce_scatter_plan(src, output, *, ctx=None, implementation="auto",
 
 def reduce_scatter(src, output, *, ctx=None, implementation="auto", storage_kind="symmetric"):
     """``output = sum over ranks of src[rank * n:(rank + 1) * n]`` (rank-major chunks)."""
-    return build_reduce_scatter_plan(src, output, ctx=ctx, implementation=implementation,
-                                     storage_kind=storage_kind).execute(src, output, validate=False)
+    ctx = _ctx_or_current(ctx)
+    key = ("reduce_scatter", src.data_ptr(), output.data_ptr(), src.numel(), src.dtype,
+           implementation, storage_kind)
+    return _cached_plan(ctx, key, lambda: build_reduce_scatter_plan(
+        src, output, ctx=ctx, implementation=implementation,
+        storage_kind=storage_kind)).execute(src, output, validate=False)
 
 
 def broadcast(tensor, *, ctx=None, root: int = 0):

@@ -112,9 +112,17 @@ def _grid_for(nbytes: int, device: torch.device) -> int:
 
 
 def _use_multimem(heap, nbytes: int) -> bool:
+    """NVLS (multimem) path?  With two ranks a multicast store also loops the data back
+    to the sender through the switch and measures slower than plain peer stores
+    (about 500 vs 700 GB/s), so the default is NVLS only from three ranks on;
+    ``TILECCL_FORCE_NVLS=1`` uses it whenever it is bound, ``TILECCL_DISABLE_NVLS=1`` never."""
     if not heap.has_multicast or os.environ.get("TILECCL_DISABLE_NVLS", "0") not in ("", "0"):
         return False
-    return nbytes % 16 == 0 and nbytes >= 16
+    if nbytes % 16 != 0 or nbytes < 16:
+        return False
+    if os.environ.get("TILECCL_FORCE_NVLS", "0") not in ("", "0"):
+        return True
+    return heap.world_size > 2
 
 
 def _validate(name: str, t: torch.Tensor, heap) -> None:
@@ -157,8 +165,23 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
     st["epoch"] += 1
     epoch = st["epoch"]
     grid = grid or _grid_for(nbytes, heap.device)
-    status = _status(heap).data_ptr()
-    counters = st["counters"].data_ptr()
+    if "status_ptr" not in st:
+        st["status_ptr"] = _status(heap).data_ptr()
+        st["counters_ptr"] = st["counters"].data_ptr()
+        st["budget_ns"] = _budget_ns()
+        st["fn"] = getattr(_native.load(), "tccl_collective_launch")
+    status, counters = st["status_ptr"], st["counters_ptr"]
+    if not heap.emulated and heap.local_group is None:
+        # One process per GPU: a single launch with all three phases, on the current stream
+        # of the current device (the heap's device).  This is the latency path: no closures,
+        # no device switch.
+        rc = st["fn"](op, dtype_code, heap.rank, heap.world_size, root, 1 if use_multimem else 0,
+                      7, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, counters,
+                      heap.multicast_base, heap.local_base, heap.stride, nbytes, grid, status,
+                      st["budget_ns"], torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            _native.check("tccl_collective_launch", rc)
+        return
 
     def make(mask: int):
         def go():

@@ -26,8 +26,28 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def _summary(label, plan, trace, tiles, ms, rank):
+def _write_timeline(path, label, plan, t, rank, max_ctas=16):
+    """Device-clock timeline (one lane per CTA, epilogue warp 0): a span per tile from
+    "accumulator ready" to "signalled", written with planning.runtime.TimelineRecorder."""
+    from tileccl_b200.planning.runtime.timeline import TimelineRecorder
+
+    rec = TimelineRecorder(benchmark="trace_fused_gemm", path_name=label,
+                           metadata={"clock": "%globaltimer", "rank": rank, "grid": plan.grid})
+    t0 = t[:, :, 0][t[:, :, 0] > 0].min()
+    for b in range(min(plan.grid, max_ctas)):
+        for i in range(b, t.shape[0], plan.grid):
+            a, s3 = t[i, 0, 0], t[i, 0, 3]
+            if a > 0 and s3 > 0:
+                rec.record_span(name=f"tile{i}", lane=f"cta{b}", start_ms=(a - t0) / 1e6,
+                                end_ms=(s3 - t0) / 1e6, category="epilogue", rank=rank,
+                                source="device_globaltimer", tile_range={"tile": i})
+    rec.write_json(path)
+
+
+def _summary(label, plan, trace, tiles, ms, rank, timeline=None):
     t = trace.cpu().numpy().astype(np.int64).reshape(tiles, 4, 4)
+    if timeline and rank == 0:
+        _write_timeline(timeline, label, plan, t, rank)
     t0 = t[:, :, 0][t[:, :, 0] > 0].min()
     rel = (t - t0) / 1e3
     grid = plan.grid
@@ -64,6 +84,8 @@ def main() -> None:
     ap.add_argument("--ag", default="16384,4096,1024", help="M,N,K of the GEMM + all-gather")
     ap.add_argument("--rs", default="16384,4096,2048", help="M,N,K of the GEMM -> reduce-scatter")
     ap.add_argument("--iters", type=int, default=4)
+    ap.add_argument("--timeline", default=None,
+                    help="write rank 0's per-CTA timeline of the all-gather run to this JSON file")
     args = ap.parse_args()
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
@@ -115,7 +137,7 @@ def main() -> None:
         heap_stride=ctx.heap.stride, sig_stride=_fused.MAX_GROUPS, trace_ptr=trace.data_ptr(),
         status_ptr=status))
     ms = timed(plan, trace, wait_incoming=True)
-    _summary(f"GEMM+AG {M}x{N}x{K} ws={ws}", plan, trace, tiles, ms, rank)
+    _summary(f"GEMM+AG {M}x{N}x{K} ws={ws}", plan, trace, tiles, ms, rank, args.timeline)
     dist.barrier()
 
     M, N, K = (int(x) for x in args.rs.split(","))

@@ -186,6 +186,7 @@ def run_ours(args):
     events = []
     sync_all()
     t_wall0 = time.perf_counter()
+    host_s = 0.0
     for _ in range(args.steps):
         row = []
         for p in probs:
@@ -193,7 +194,9 @@ def run_ours(args):
             s = torch.cuda.Event(enable_timing=True)
             e = torch.cuda.Event(enable_timing=True)
             s.record()
+            h0 = time.perf_counter()
             run_one(p)
+            host_s += time.perf_counter() - h0
             e.record()
             row.append((s, e))
         events.append(row)
@@ -274,6 +277,7 @@ def run_ours(args):
                        "nvls_bound": bool(ctx.heap.has_multicast),
                        "roofline_peaks": peaks},
             "shapes": shapes, "clocks": clocks, "gpu_launches": launches,
+            "host_us_per_op": round(host_s / (args.steps * len(probs)) * 1e6, 1),
             "wall_ms_per_step_incl_flush": round(t_wall * 1e3 / args.steps, 4),
             "baseline_published": {"what": "reference S2, 2x H100 NVLink", "ms": PUBLISHED_S2_MS},
         }

@@ -184,6 +184,7 @@ class FusedGemmPlan:
         handle = C.c_void_p()
         _native.call("tccl_gemm_plan_create", C.byref(d), C.byref(handle))
         self._handle = handle
+        self._launch_fn = getattr(_native.load(), "tccl_gemm_plan_launch")
         info = _native.GemmPlanInfo()
         _native.call("tccl_gemm_plan_info", self._handle, C.byref(info))
         self.grid = info.grid
@@ -203,10 +204,11 @@ class FusedGemmPlan:
         global LAUNCH_COUNT
         s = stream if stream is not None else torch.cuda.current_stream()
         LAUNCH_COUNT += 1
-        _native.call("tccl_gemm_plan_launch", self._handle, epoch & 0xFFFFFFFF,
-                     a_gate_target & 0xFFFFFFFF, tile_begin, tile_end,
-                     (1 if wait_incoming else 0) | (2 if ag_push else 0),
-                     s.cuda_stream)
+        rc = self._launch_fn(self._handle, epoch & 0xFFFFFFFF, a_gate_target & 0xFFFFFFFF,
+                             tile_begin, tile_end,
+                             (1 if wait_incoming else 0) | (2 if ag_push else 0), s.cuda_stream)
+        if rc != 0:
+            _native.check("tccl_gemm_plan_launch", rc)
 
     def group_m_count(self, g: int) -> int:
         left = self.m_tiles_local - g * self.spec.group_m_tiles

@@ -55,6 +55,11 @@ def _ctx_or_current(ctx):
     return current_context()
 
 
+def _mm_key(kind, A, B, C, *extra):
+    return (kind, A.data_ptr(), B.data_ptr(), C.data_ptr(), tuple(A.shape), tuple(B.shape),
+            tuple(C.shape), A.stride(0), B.stride(0), C.stride(0), A.dtype) + extra
+
+
 def _cached_plan(ctx, key, build):
     """Plans of the one-call collectives, kept per context: a repeated call on the same
     buffer skips contract resolution (the small-message latency is host time)."""
@@ -348,7 +353,10 @@ def gemm_allgather(A, B_shard, C, *, ctx=None, storage_kind="symmetric"):
     ``A (M, K)`` full, ``B_shard (K, N/ws)``, ``C (M, N)`` on the heap:
     ``C[:, r*N/ws:(r+1)*N/ws] = A_r @ B_shard_r`` for every rank ``r``, on every rank.
     """
-    return build_gemm_allgather_plan(A, B_shard, C, ctx=ctx, storage_kind=storage_kind).execute(
+    ctx = _ctx_or_current(ctx)
+    return _cached_plan(ctx, _mm_key("gemm_allgather", A, B_shard, C, storage_kind),
+                        lambda: build_gemm_allgather_plan(A, B_shard, C, ctx=ctx,
+                                                          storage_kind=storage_kind)).execute(
         A, B_shard, C, validate=False)
 
 
@@ -360,7 +368,10 @@ def gemm_allgather_rows(A_local, B, C, *, ctx=None, b_is_nk=False, wait=True, a_
     streamed from the host into ``A_local`` while the kernel runs, tile rows in
     the order the kernel consumes them, so only the last run's math is exposed
     after the PCIe copy."""
-    plan = build_gemm_allgather_plan(A_local, B, C, ctx=ctx, layout="rows", b_is_nk=b_is_nk)
+    ctx = _ctx_or_current(ctx)
+    plan = _cached_plan(ctx, _mm_key("gemm_allgather_rows", A_local, B, C, b_is_nk),
+                        lambda: build_gemm_allgather_plan(A_local, B, C, ctx=ctx, layout="rows",
+                                                          b_is_nk=b_is_nk))
     return plan.execute(A_local, B, C, validate=False, wait=wait, a_host=a_host)
 
 
@@ -467,15 +478,21 @@ def gemm_reducescatter(A, B, C, *, ctx=None, implementation="auto", storage_kind
     ``A (M, K)`` is this rank's contribution, ``B (K, N)``, ``C (M, N/ws)``:
     ``C_r = sum_i (A_i @ B_i)[:, r*N/ws:(r+1)*N/ws]``.
     """
-    return build_gemm_reducescatter_plan(A, B, C, ctx=ctx, implementation=implementation,
-                                         storage_kind=storage_kind).execute(A, B, C, validate=False)
+    ctx = _ctx_or_current(ctx)
+    return _cached_plan(ctx, _mm_key("gemm_reducescatter", A, B, C, implementation, storage_kind),
+                        lambda: build_gemm_reducescatter_plan(
+                            A, B, C, ctx=ctx, implementation=implementation,
+                            storage_kind=storage_kind)).execute(A, B, C, validate=False)
 
 
 def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False, a_host=None):
     """Row-sharded form: ``A (M, K/ws)``, ``B (K/ws, N)``, ``C_local (M/ws, N)``:
     ``C_local_r = sum_i (A_i @ B_i)[r*M/ws:(r+1)*M/ws, :]``.  ``a_host`` streams ``A``
     from pinned host memory as in :func:`gemm_allgather_rows`."""
-    plan = build_gemm_reducescatter_plan(A, B, C_local, ctx=ctx, layout="rows", b_is_nk=b_is_nk)
+    ctx = _ctx_or_current(ctx)
+    plan = _cached_plan(ctx, _mm_key("gemm_reducescatter_rows", A, B, C_local, b_is_nk),
+                        lambda: build_gemm_reducescatter_plan(A, B, C_local, ctx=ctx, layout="rows",
+                                                              b_is_nk=b_is_nk))
     return plan.execute(A, B, C_local, validate=False, a_host=a_host)
 
 

@@ -4,6 +4,7 @@
 // launch and no driver calls.
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 
@@ -13,6 +14,7 @@
 
 namespace tileccl {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_gemm2sm(const FusedGemmParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
                                const uint32_t* per_epoch, uint32_t epoch, int skip_src,
                                uint32_t* status, uint64_t budget_ns, int rank,
@@ -23,6 +25,8 @@ namespace {
 struct GemmPlan {
   FusedGemmParams params;
   TcclGemmPlanInfo info;
+  bool pair_kernel = false;   // whole-problem launches run on CTA pairs (gemm2sm_sm100.cu)
+  int pair_grid = 0;
 };
 
 // 16-bit row-major matrix [rows, cols] (+ optional slot dimension) -> tensor map
@@ -112,6 +116,14 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     if (rc) return rc;
     p.out_ptr[i] = d.out_ptr[i];
   }
+  // B for the CTA-pair kernel: each CTA of a pair loads 128 of the tile's 256 columns.
+  if (d.b_kmajor)
+    rc = encode_map(&p.tma_b_half, bf16, d.b_ptr, d.k, d.b_cols, d.ldb * 2, kBK, kBN / 2, 0, 0,
+                    "B[N,K] half");
+  else
+    rc = encode_map(&p.tma_b_half, bf16, d.b_ptr, d.b_cols, d.k, d.ldb * 2, 64, kBK, 0, 0,
+                    "B[K,N] half");
+  if (rc) return rc;
   if (d.mode == kModeReduceScatter && d.world_size > 1) {
     TCCL_CHECK_ARG(d.stage_local != 0, "reduce-scatter needs this rank's staging area");
     TCCL_CHECK_ARG(d.ident_ptr != 0, "reduce-scatter needs the 128 x 128 identity operand");
@@ -196,6 +208,19 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   info.groups = groups;
   info.k_blocks = p.k_blocks;
   info.smem_bytes = kSmemTotal;
+
+  // Plain whole-problem GEMMs run on CTA pairs (256 x 256 per pair).  Everything that
+  // signals, gates, reduces or traces stays on the one-CTA kernel.
+  const char* env = std::getenv("TILECCL_GEMM_2SM");
+  const bool allowed = env == nullptr || env[0] != '0';
+  plan->pair_kernel = allowed && d.mode == kModeGemm && d.epi_op == kEpiNone && d.sig_local == 0 &&
+                      d.a_gate == 0 && d.ag_bytes == 0 && d.rot_m_tiles == 0 && d.trace == 0 &&
+                      d.grid <= 0 && grid >= 2;
+  if (plan->pair_kernel) {
+    const int pair_tiles = ((p.m_tiles_local + 1) / 2) * p.n_tiles_local;
+    const int pairs = grid / 2 < pair_tiles ? grid / 2 : pair_tiles;
+    plan->pair_grid = 2 * pairs;
+  }
   return kOk;
 }
 
@@ -245,6 +270,10 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   } else
   if (grid > tile_end - tile_begin) grid = tile_end - tile_begin;
   if (grid < 1) grid = 1;
+  if (plan->pair_kernel && tile_begin == 0 && tile_end == total && !ag_push) {
+    TCCL_CHECK_CUDA(launch_gemm2sm(p, plan->pair_grid, reinterpret_cast<cudaStream_t>(stream)));
+    return kOk;
+  }
   TCCL_CHECK_CUDA(launch_fused_gemm(p, grid, reinterpret_cast<cudaStream_t>(stream)));
   return kOk;
 }

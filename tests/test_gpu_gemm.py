@@ -69,3 +69,31 @@ def test_argument_errors():
         gemm(a, torch.randn(64, 128, device="cuda").bfloat16())
     with pytest.raises(_native.NativeError):             # K not a multiple of 8 elements
         gemm(torch.randn(128, 60, device="cuda").half(), torch.randn(60, 128, device="cuda").half())
+
+
+@pytest.mark.parametrize("b_is_nk", [False, True])
+def test_one_cta_and_cta_pair_kernels_agree(monkeypatch, b_is_nk):
+    """The plain GEMM runs on CTA pairs by default; TILECCL_GEMM_2SM=0 keeps the one-CTA
+    kernel.  Same inputs, same fp32 accumulation order inside a tile: identical output."""
+    from tileccl_b200.kernels import fused_gemm as fg
+
+    M, N, K = 896, 768, 448          # 7 tile rows: the last pair has one real half
+    torch.manual_seed(5)
+    a = (torch.randn(M, K, device="cuda") / K ** 0.5).half()
+    b = torch.randn(K, N, device="cuda").half()
+    bb = b.t().contiguous() if b_is_nk else b
+    outs = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("TILECCL_GEMM_2SM", flag)
+        c = torch.zeros(M, N, device="cuda", dtype=torch.float16)
+        spec = fg.FusedGemmSpec(
+            mode=fg.MODE_GEMM, dtype=torch.float16, a_ptr=a.data_ptr(), a_rows=M, lda=K,
+            b_ptr=bb.data_ptr(), b_cols=N, ldb=bb.stride(0), k=K, sub_m=M, sub_n=N,
+            out_ptrs=[c.data_ptr()], ldo=N, out_rows=M, out_cols=N, b_kmajor=b_is_nk)
+        plan = fg.FusedGemmPlan(spec)
+        plan.launch()
+        torch.cuda.synchronize()
+        plan.close()
+        outs.append(c)
+    assert _rel_err(outs[0], a.float() @ b.float()) < 4e-3
+    assert torch.equal(outs[0], outs[1])

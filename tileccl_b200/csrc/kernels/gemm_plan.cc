@@ -14,7 +14,7 @@
 
 namespace tileccl {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_gemm2sm(const FusedGemmParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
                                const uint32_t* per_epoch, uint32_t epoch, int skip_src,
                                uint32_t* status, uint64_t budget_ns, int rank,
@@ -25,8 +25,8 @@ namespace {
 struct GemmPlan {
   FusedGemmParams params;
   TcclGemmPlanInfo info;
-  bool pair_kernel = false;   // whole-problem launches run on CTA pairs (gemm2sm_sm100.cu)
-  int pair_grid = 0;
+  bool pair_kernel = false;   // whole-order launches run on CTA pairs
+  int pair_grid = 0, pair_push_grid = 0;
 };
 
 // 16-bit row-major matrix [rows, cols] (+ optional slot dimension) -> tensor map
@@ -209,17 +209,18 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   info.k_blocks = p.k_blocks;
   info.smem_bytes = kSmemTotal;
 
-  // Plain whole-problem GEMMs run on CTA pairs (256 x 256 per pair).  Everything that
-  // signals, gates, reduces or traces stays on the one-CTA kernel.
+  // Launches that run the rank's whole tile order use CTA pairs (256 x 256 per pair, see
+  // gemm_sm100.cu); tile-range launches (emulated ranks, host-streamed operand), traced
+  // launches and explicit grids stay on the one-CTA form.
   const char* env = std::getenv("TILECCL_GEMM_2SM");
   const bool allowed = env == nullptr || env[0] != '0';
-  plan->pair_kernel = allowed && d.mode == kModeGemm && d.epi_op == kEpiNone && d.sig_local == 0 &&
-                      d.a_gate == 0 && d.ag_bytes == 0 && d.rot_m_tiles == 0 && d.trace == 0 &&
-                      d.grid <= 0 && grid >= 2;
+  plan->pair_kernel = allowed && d.rot_m_tiles % 2 == 0 && d.trace == 0 && d.grid <= 0 && grid >= 2 &&
+                      grid % 2 == 0;
   if (plan->pair_kernel) {
-    const int pair_tiles = ((p.m_tiles_local + 1) / 2) * p.n_tiles_local;
+    const int pair_tiles = ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
     const int pairs = grid / 2 < pair_tiles ? grid / 2 : pair_tiles;
     plan->pair_grid = 2 * pairs;
+    plan->pair_push_grid = grid & ~1;
   }
   return kOk;
 }
@@ -270,8 +271,10 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   } else
   if (grid > tile_end - tile_begin) grid = tile_end - tile_begin;
   if (grid < 1) grid = 1;
-  if (plan->pair_kernel && tile_begin == 0 && tile_end == total && !ag_push) {
-    TCCL_CHECK_CUDA(launch_gemm2sm(p, plan->pair_grid, reinterpret_cast<cudaStream_t>(stream)));
+  if (plan->pair_kernel && tile_begin == 0 && tile_end == total) {
+    // (an all-gather-pushing launch has a fixed grid: the consumers count its CTAs)
+    TCCL_CHECK_CUDA(launch_fused_gemm_pair(p, ag_push ? plan->pair_push_grid : plan->pair_grid,
+                                           reinterpret_cast<cudaStream_t>(stream)));
     return kOk;
   }
   TCCL_CHECK_CUDA(launch_fused_gemm(p, grid, reinterpret_cast<cudaStream_t>(stream)));

@@ -36,13 +36,23 @@ struct TileCoord {
   int out_x, out_y;     // destination-local coordinates (elements)
   int owner;            // reduce-scatter: rank that owns the tile; else this rank
   int lm;               // tile row inside the owner's sub-problem (TileGroup = lm / group_m_tiles)
+  bool valid;           // false: padding half of the last pair-tile row
 };
 
-__device__ __forceinline__ TileCoord decode_tile(const FusedGemmParams& p, int t) {
-  const TileOrderShape shape{p.m_tiles_local, p.n_tiles_local, p.owners, p.rank, p.world_size,
-                             p.rot_m_tiles, p.rs_own_lag};
-  const TileOrderEntry e = tile_order_decode(shape, t);
+// One-CTA kernel: `t` indexes the rank's 128-row tiles.  CTA-pair kernel: `t` indexes
+// 256-row pair-tiles (same visiting order over half as many tile rows) and CTA `cta` of
+// the pair owns tile row 2 * (pair row) + cta, which may lie past the last real tile row
+// (`valid` = false: the CTA still takes part in the MMA but stores and signals nothing).
+template <bool kPair>
+__device__ __forceinline__ TileCoord decode_tile(const FusedGemmParams& p, int t, int cta = 0) {
+  const int m_rows = kPair ? (p.m_tiles_local + 1) / 2 : p.m_tiles_local;
+  const TileOrderShape shape{m_rows, p.n_tiles_local, p.owners, p.rank, p.world_size,
+                             kPair ? p.rot_m_tiles / 2 : p.rot_m_tiles,
+                             kPair ? (p.rs_own_lag + 1) / 2 : p.rs_own_lag};
+  TileOrderEntry e = tile_order_decode(shape, t);
+  if (kPair) e.lm = e.lm * 2 + cta;
   TileCoord c;
+  c.valid = e.lm < p.m_tiles_local;
   c.owner = e.owner;
   c.lm = e.lm;
   c.a_row0 = e.lm * kBM;
@@ -87,10 +97,34 @@ __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap
       : "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* m, int x,
+                                                 int y, int z, uint32_t cluster_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile"
+      ".mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(cluster_bar)
+      : "memory");
+}
+
+// Shared-memory geometry of the two kernel forms.  One CTA: 128 x 256 tile, 48 KB per K
+// block, four stages.  CTA pair (tcgen05 cta_group::2): 256 x 256 per pair, every CTA stages
+// its own 128 rows of A and 128 of the 256 columns of B (32 KB), six stages.
+template <bool kPair>
+struct Geo {
+  static constexpr int kNumStages = kPair ? 6 : kStages;
+  static constexpr int kBBytes = kPair ? kStageBBytes / 2 : kStageBBytes;
+  static constexpr int kBytes = kStageABytes + kBBytes;
+  static constexpr int kBBoxes = kPair ? kBN / 2 / 64 : kBN / 64;   // 64-column boxes of an MN-major B
+  static_assert(kNumStages * kBytes <= kSmemPipe, "operand ring exceeds its shared-memory budget");
+};
+
 }  // namespace
 
+template <bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
+  using G = Geo<kPair>;
+  constexpr int kNS = G::kNumStages;
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -98,9 +132,12 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   const uint32_t smem_ctl = smem_base + kSmemPipe + kSmemEpi;
   uint8_t* ctl_generic = smem_raw + (smem_ctl - smem_u32(smem_raw));
 
-  const uint32_t bar_full = smem_ctl;                         // kStages x 8 B
-  const uint32_t bar_empty = bar_full + 8 * kStages;          // kStages x 8 B
-  const uint32_t bar_acc_full = bar_empty + 8 * kStages;      // kAccBufs x 8 B
+  // In the pair form every CTA has all barriers; the leader's "full" and "accumulator
+  // empty" barriers are the ones in use (both CTAs report to them), "empty" and
+  // "accumulator full" are signalled in both CTAs by multicast commits.
+  const uint32_t bar_full = smem_ctl;                         // kNS x 8 B
+  const uint32_t bar_empty = bar_full + 8 * kNS;              // kNS x 8 B
+  const uint32_t bar_acc_full = bar_empty + 8 * kNS;          // kAccBufs x 8 B
   const uint32_t bar_acc_empty = bar_acc_full + 8 * kAccBufs; // kAccBufs x 8 B
   const uint32_t bar_drain = bar_acc_empty + 8 * kAccBufs;    // 8 B
   const uint32_t tmem_slot = bar_drain + 8;                   // 4 B
@@ -111,20 +148,22 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // communication warps poll it to learn which tiles of C they may forward.
   const uint32_t done_count = tmem_slot + 8;
   volatile uint32_t* done_count_g = tmem_slot_g + 2;
-  static_assert(8 * (2 * kStages + 2 * kAccBufs + 1) + 16 <= kSmemCtl, "control block overflow");
+  static_assert(8 * (2 * kNS + 2 * kAccBufs + 1) + 16 <= kSmemCtl, "control block overflow");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int cta = kPair ? static_cast<int>(cluster_ctarank()) : 0;   // 0 = leader of the pair
+  const bool leader = cta == 0;
   uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kNS; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < kAccBufs; ++a) {
       mbar_init(bar_acc_full + 8 * a, 1);
-      mbar_init(bar_acc_empty + 8 * a, kEpiWarps);
+      mbar_init(bar_acc_empty + 8 * a, kPair ? 2 * kEpiWarps : kEpiWarps);
     }
     mbar_init(bar_drain, 1);
     *abort_flag = 0;
@@ -132,19 +171,30 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     mbar_fence_init();
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, kAccBufs * kBN);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(tmem_slot, kAccBufs * kBN);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, kAccBufs * kBN);
+      tmem_relinquish();
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // barriers and TMEM of both CTAs exist
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot_g;
 
   WaitBudget wb;
   wb.start(p.wait_budget_ns, abort_flag);
 
-  const int first = p.tile_begin + static_cast<int>(blockIdx.x);
-  const int step = static_cast<int>(gridDim.x);
+  // Tile iteration: 128-row tiles per CTA, or 256-row pair-tiles per CTA pair (the pair
+  // form always runs the rank's whole tile order).
+  const int first = kPair ? static_cast<int>(blockIdx.x >> 1)
+                          : p.tile_begin + static_cast<int>(blockIdx.x);
+  const int step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int tile_end =
+      kPair ? ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners : p.tile_end;
   // Finished tiles of C are forwarded to the peers by warps 2 and 3 (16-byte stores or
   // multimem stores read back from this rank's copy of C) rather than by the epilogue.
   const bool comm_push = p.world_size > 1 && p.push_mode != kPushTma &&
@@ -161,7 +211,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     const int rpi = 32 / vpr;        // tile rows covered by one warp-wide access
     const int lrow = lane / vpr, lvec = lane % vpr;
     uint32_t n_tiles = 0;
-    for (int t = first; t < p.tile_end; t += step) {
+    for (int t = first; t < tile_end; t += step) {
       ++n_tiles;
       const uint32_t want = n_tiles * kEpiWarps;
       bool got = true;
@@ -179,7 +229,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         break;
       }
       fence_proxy_async_all();
-      const TileCoord c = decode_tile(p, t);
+      const TileCoord c = decode_tile<kPair>(p, t, cta);
+      if (!c.valid) continue;
       int lo = c.out_x, hi = c.out_x + tile_cols;
       if (hi > p.out_cols) hi = p.out_cols;
       if (p.mode == kModeAllScatter) {
@@ -235,9 +286,9 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       tma_prefetch_desc(&p.tma_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = first; ok && t < p.tile_end; t += step) {
-        const TileCoord c = decode_tile(p, t);
-        if (p.a_gate != 0) {
+      for (int t = first; ok && t < tile_end; t += step) {
+        const TileCoord c = decode_tile<kPair>(p, t, cta);
+        if (p.a_gate != 0 && c.valid) {
           // Rows of A written by a peer: wait for that peer's arrival counter.
           int src = c.a_row0 / p.a_gate_rows_per_rank;
           if (src != p.rank) {
@@ -257,75 +308,121 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             ok = false;
             break;
           }
-          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sa = smem_base + stage * G::kBytes;
           const uint32_t sb = sa + kStageABytes;
-          const uint32_t bar = bar_full + 8 * stage;
-          mbar_expect_tx(bar, kStageBytes);
-          tma_load_2d(sa, &p.tma_a, kb * kBK, c.a_row0, bar);
-          if (p.b_kmajor) {
-            tma_load_2d(sb, &p.tma_b, kb * kBK, c.b_col0, bar);
-          } else {
+          if (kPair) {
+            // Own halves; the bytes of both CTAs are counted on the leader's barrier.
+            if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * G::kBytes);
+            const uint32_t bar = mapa_shared(bar_full + 8 * stage, 0);
+            const int b_col = c.b_col0 + cta * (kBN / 2);
+            tma_load_2d_pair(sa, &p.tma_a, kb * kBK, c.a_row0, bar);
+            if (p.b_kmajor) {
+              tma_load_2d_pair(sb, &p.tma_b_half, kb * kBK, b_col, bar);
+            } else {
 #pragma unroll
-            for (int i = 0; i < kBN / 64; ++i)
-              tma_load_2d(sb + i * (64 * kBK * 2), &p.tma_b, c.b_col0 + i * 64, kb * kBK, bar);
+              for (int i = 0; i < G::kBBoxes; ++i)
+                tma_load_2d_pair(sb + i * (64 * kBK * 2), &p.tma_b_half, b_col + i * 64, kb * kBK,
+                                 bar);
+            }
+          } else {
+            const uint32_t bar = bar_full + 8 * stage;
+            mbar_expect_tx(bar, G::kBytes);
+            tma_load_2d(sa, &p.tma_a, kb * kBK, c.a_row0, bar);
+            if (p.b_kmajor) {
+              tma_load_2d(sb, &p.tma_b, kb * kBK, c.b_col0, bar);
+            } else {
+#pragma unroll
+              for (int i = 0; i < G::kBBoxes; ++i)
+                tma_load_2d(sb + i * (64 * kBK * 2), &p.tma_b, c.b_col0 + i * 64, kb * kBK, bar);
+            }
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++stage == kNS) { stage = 0; phase ^= 1u; }
         }
         if (ok && p.mode == kModeReduceScatter && p.world_size > 1 && c.owner == p.rank) {
           // Own tile: after its K blocks, the peers' staged partial tiles go through the
-          // same pipeline (two 64-row halves each, in rank order) next to the identity.
-          const int group = c.lm / p.group_m_tiles;
-          const uint32_t target =
-              p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
-                                              p.n_tiles_local * kEpiWarps);
-          uint32_t seen = 0;
-          if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
-                            &seen)) {
-            report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
-            *abort_flag = 1;
-            ok = false;
-            break;
+          // same pipeline, in rank order, next to the identity.  One CTA: two 64-row
+          // halves of the tile.  CTA pair: the 256 x 256 identity times the two stacked
+          // tiles of the pair, K' = 256 in four blocks; this CTA's rows of the identity are
+          // zero outside its own two blocks (loaded as out-of-range boxes), and it stages
+          // its 128 columns of both tiles.
+          const int lm_first = kPair ? c.lm - cta : c.lm;
+          const int n_rows = kPair ? 2 : 1;
+          for (int i = 0; ok && i < n_rows; ++i) {
+            const int lm = lm_first + i;
+            if (lm >= p.m_tiles_local) continue;
+            const int group = lm / p.group_m_tiles;
+            const uint32_t target =
+                p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
+                                                p.n_tiles_local * kEpiWarps);
+            uint32_t seen = 0;
+            if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
+                              &seen)) {
+              report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
+              *abort_flag = 1;
+              ok = false;
+            }
           }
+          if (!ok) break;
           fence_proxy_async_all();   // bulk reads of the partials come after that observation
+          constexpr int kRedBlocks = (kPair ? 2 : 1) * (kBM / kBK);
           for (int src = 0; ok && src < p.world_size; ++src) {
             if (src == p.rank) continue;
             const int z = p.stage_parity * p.world_size + src;
-            for (int hb = 0; hb < kBM / kBK; ++hb) {
+            for (int hb = 0; hb < kRedBlocks; ++hb) {
               if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, wb)) {
                 report_status(status, kStatusTimeoutMbarrier, 12, 0, 0, p.rank, t);
                 ok = false;
                 break;
               }
-              const uint32_t sa = smem_base + stage * kStageBytes;
+              const uint32_t sa = smem_base + stage * G::kBytes;
               const uint32_t sb = sa + kStageABytes;
-              const uint32_t bar = bar_full + 8 * stage;
-              mbar_expect_tx(bar, kStageBytes);
-              tma_load_2d(sa, &p.tma_ident, hb * kBK, 0, bar);
+              if (kPair) {
+                if (leader) mbar_expect_tx(bar_full + 8 * stage, 2 * G::kBytes);
+                const uint32_t bar = mapa_shared(bar_full + 8 * stage, 0);
+                tma_load_2d_pair(sa, &p.tma_ident, (hb - 2 * cta) * kBK, 0, bar);
+                const int y = lm_first * kBM + hb * kBK;     // row of the stacked pair of tiles
 #pragma unroll
-              for (int i = 0; i < kBN / 64; ++i)
-                tma_load_3d(sb + i * (64 * kBK * 2), &p.tma_stage, c.out_x + i * 64,
-                            c.out_y + hb * kBK, z, bar);
-              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                for (int i = 0; i < G::kBBoxes; ++i)
+                  tma_load_3d_pair(sb + i * (64 * kBK * 2), &p.tma_stage,
+                                   c.out_x + cta * (kBN / 2) + i * 64, y, z, bar);
+              } else {
+                const uint32_t bar = bar_full + 8 * stage;
+                mbar_expect_tx(bar, G::kBytes);
+                tma_load_2d(sa, &p.tma_ident, hb * kBK, 0, bar);
+#pragma unroll
+                for (int i = 0; i < G::kBBoxes; ++i)
+                  tma_load_3d(sb + i * (64 * kBK * 2), &p.tma_stage, c.out_x + i * 64,
+                              c.out_y + hb * kBK, z, bar);
+              }
+              if (++stage == kNS) { stage = 0; phase ^= 1u; }
             }
           }
         }
       }
       if (!ok) {
         // Let loads that are still in flight land before the CTA retires.
-        for (int s = 0; s < kStages; ++s)
+        for (int s = 0; s < kNS; ++s)
           for (int it = 0; it < 100000 && !mbar_try_wait(bar_full + 8 * s, 0) &&
                            !mbar_try_wait(bar_full + 8 * s, 1); ++it) {}
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
+  } else if (warp == 1 && leader) {
+    // ------------------- MMA issuer (in a pair: the leader CTA only) -------------------
     if (elect_one_sync()) {
-      const uint32_t idesc = umma_idesc_f16(p.is_bf16, 0, p.b_kmajor ? 0 : 1, kBM, kBN);
-      const uint32_t idesc_red = umma_idesc_f16(p.is_bf16, 0, 1, kBM, kBN);
+      constexpr int kM = kPair ? 2 * kBM : kBM;
+      const uint32_t idesc = umma_idesc_f16(p.is_bf16, 0, p.b_kmajor ? 0 : 1, kM, kBN);
+      const uint32_t idesc_red = umma_idesc_f16(p.is_bf16, 0, 1, kM, kBN);
+      auto mma = [&](uint32_t d, uint64_t da, uint64_t db, uint32_t id, uint32_t accum) {
+        if (kPair) umma_f16_pair(d, da, db, id, accum); else umma_f16(d, da, db, id, accum);
+      };
+      // One arrival on `bar` (in both CTAs of a pair) once the MMAs issued so far are done.
+      auto commit = [&](uint32_t bar) {
+        if (kPair) umma_commit_pair(bar, 3); else umma_commit(bar);
+      };
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int t = first; ok && t < p.tile_end; t += step) {
+      for (int t = first; ok && t < tile_end; t += step) {
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, wb)) {
           report_status(status, kStatusTimeoutMbarrier, 20, 0, 0, p.rank, t);
           ok = false;
@@ -335,8 +432,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         const uint32_t d_tmem = tmem_base + acc * kBN;
         // Own reduce-scatter tiles continue with the peers' partial tiles (see the producer).
         const bool reduce_tile = p.mode == kModeReduceScatter && p.world_size > 1 &&
-                                 decode_tile(p, t).owner == p.rank;
-        const int kb_total = p.k_blocks + (reduce_tile ? (kBM / kBK) * (p.world_size - 1) : 0);
+                                 decode_tile<kPair>(p, t, cta).owner == p.rank;
+        const int kb_total =
+            p.k_blocks +
+            (reduce_tile ? (kPair ? 2 : 1) * (kBM / kBK) * (p.world_size - 1) : 0);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, wb)) {
             report_status(status, kStatusTimeoutMbarrier, 21, 0, 0, p.rank, t);
@@ -344,7 +443,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             break;
           }
           tcgen05_fence_after();
-          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sa = smem_base + stage * G::kBytes;
           const uint32_t sb = sa + kStageABytes;
 #pragma unroll
           for (int k = 0; k < kBK / kUmmaK; ++k) {
@@ -354,19 +453,19 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             const uint64_t db =
                 b_k ? umma_smem_desc_sw128(sb + k * (kUmmaK * 2), 16, 1024)
                     : umma_smem_desc_sw128(sb + k * (kUmmaK * 128), 64 * kBK * 2, 1024);
-            umma_f16(d_tmem, da, db, b_k == (p.b_kmajor != 0) ? idesc : idesc_red,
-                     (kb | k) != 0 ? 1u : 0u);
+            mma(d_tmem, da, db, b_k == (p.b_kmajor != 0) ? idesc : idesc_red,
+                (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+          if (++stage == kNS) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
+        commit(bar_acc_full + 8 * acc);   // accumulator complete -> epilogue
         if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
       }
       if (!ok) {
         // Outstanding MMAs must finish before TMEM is released.
-        umma_commit(bar_drain);
+        if (kPair) umma_commit_pair(bar_drain, 1); else umma_commit(bar_drain);
         for (int it = 0; it < 1000000 && !mbar_try_wait(bar_drain, 0); ++it) {}
       }
     }
@@ -460,8 +559,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, g));
       }
     };
-    for (int t = first; ok && t < p.tile_end; t += step) {
-      const TileCoord c = decode_tile(p, t);
+    for (int t = first; ok && t < tile_end; t += step) {
+      const TileCoord c = decode_tile<kPair>(p, t, cta);
       const int group = c.lm / p.group_m_tiles;
       const bool reduce_here = p.mode == kModeReduceScatter && c.owner == p.rank;
 
@@ -517,7 +616,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           // Every TMEM read of this accumulator is done: hand it back to the MMA warp.
           tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+          if (lane == 0) {
+            if (kPair) mbar_arrive_cluster(mapa_shared(bar_acc_empty + 8 * acc, 0));
+            else mbar_arrive(bar_acc_empty + 8 * acc);
+          }
         }
 
         const int col0 = c.out_x + ch * kChunkN;     // destination-local column of v[0]
@@ -580,7 +682,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       if (p.trace != 0 && lane == 0)
         reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 1] = globaltimer_ns();
       // ---- TileGroup signalling: this slab of this tile is now on its way ----
-      const bool signals = p.world_size > 1 && p.sig_local != 0 &&
+      const bool signals = c.valid && p.world_size > 1 && p.sig_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
                             (p.mode == kModeReduceScatter && !reduce_here));
       if (comm_push) {
@@ -624,7 +726,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
       // Plain GEMM feeding a consumer kernel on the same GPU (producer / consumer
       // pattern): publish the slab on this rank's own TileGroup counter.
-      if (p.mode == kModeGemm && p.sig_local != 0) {
+      if (p.mode == kModeGemm && p.sig_local != 0 && c.valid) {
         if (lane == 0) tma_store_wait_all<0>();
         fence_proxy_async_all();
         __threadfence();
@@ -647,11 +749,15 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     }
   }
 
+  // In a pair neither CTA may retire while its partner can still read its operands or
+  // touch its barriers; TMEM goes back only after every MMA and TMEM read is done.
   tcgen05_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();
   if (warp == 2) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kAccBufs * kBN);
+    if (kPair) tmem_dealloc_pair(tmem_base, kAccBufs * kBN);
+    else tmem_dealloc(tmem_base, kAccBufs * kBN);
   }
 }
 
@@ -681,19 +787,47 @@ __global__ void wait_groups_kernel(const uint32_t* sig, int sig_stride, int n_sr
   }
 }
 
-cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream) {
+static cudaError_t launch_fused_gemm_attrs_once() {
   static bool attr_set[64] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_set[dev]) {
-    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kSmemTotal);
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<true>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  fused_gemm_sm100_kernel<<<grid, kThreads, kSmemTotal, stream>>>(p);
+  return cudaSuccess;
+}
+
+cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream) {
+  cudaError_t e = launch_fused_gemm_attrs_once();
+  if (e != cudaSuccess) return e;
+  fused_gemm_sm100_kernel<false><<<grid, kThreads, kSmemTotal, stream>>>(p);
   return cudaGetLastError();
+}
+
+// The CTA-pair form: clusters of two CTAs, `grid` even, always the rank's whole tile order.
+cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream) {
+  cudaError_t e = launch_fused_gemm_attrs_once();
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid & ~1), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, fused_gemm_sm100_kernel<true>, p);
 }
 
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,

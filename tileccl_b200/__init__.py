@@ -30,6 +30,31 @@ _LAZY_SUBMODULES = ("ops", "patterns", "planning", "primitives", "sync", "memory
                     "models", "parallel", "kernels", "backends", "support", "cli", "emulation")
 
 
+_PRELOADED = set()
+
+
+def _preload_kernels(device) -> None:
+    """Load every kernel of the native library onto ``device`` once.
+
+    CUDA loads kernels lazily, and the first launch of a kernel may wait for kernels
+    already running on the device.  When one host thread drives several ranks, a rank's
+    kernel that spins on a peer could otherwise sit in front of that peer's first launch.
+    """
+    import torch
+
+    dev = torch.device(device)
+    if dev.type != "cuda" or not torch.cuda.is_available():
+        return
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx in _PRELOADED:
+        return
+    from . import _native
+
+    with torch.cuda.device(idx):
+        _native.call("tccl_preload_kernels")
+    _PRELOADED.add(idx)
+
+
 @dataclass
 class TileCCLContext:
     rank: int
@@ -69,6 +94,7 @@ class TileCCLContext:
             self.local_group = heap.local_group
         self._workspace_cache.clear()
         self._state.clear()
+        _preload_kernels(heap.device)
         return self
 
     @property

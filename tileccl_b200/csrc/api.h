@@ -13,6 +13,9 @@ extern "C" {
 
 const char* tccl_last_error(void);
 const char* tccl_version(void);
+// Loads every kernel of the library onto the current device (call once per device, before
+// kernels that wait on other ranks are in flight).
+int tccl_preload_kernels(void);
 
 // --------------------------------------------------------------------------
 // Device / topology query (csrc/runtime/device.cc)

@@ -573,3 +573,12 @@ extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ran
   }
   return kOk;
 }
+
+namespace tileccl {
+cudaError_t preload_collective_kernels() {
+  cudaFuncAttributes a;
+  cudaError_t e = cudaFuncGetAttributes(&a, collective_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, allreduce_oneshot_kernel);
+  return e;
+}
+}  // namespace tileccl

@@ -15,6 +15,10 @@
 namespace tileccl {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream);
+cudaError_t preload_gemm_kernels();
+cudaError_t preload_collective_kernels();
+cudaError_t preload_push_kernels();
+cudaError_t preload_prim_kernels();
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,
                                const uint32_t* per_epoch, uint32_t epoch, int skip_src,
                                uint32_t* status, uint64_t budget_ns, int rank,
@@ -297,5 +301,19 @@ extern "C" int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src,
                                      reinterpret_cast<uint32_t*>(status),
                                      budget_ns ? budget_ns : 2000000000ull, rank,
                                      reinterpret_cast<cudaStream_t>(stream)));
+  return kOk;
+}
+
+// Loads every kernel of the library onto the current device.  With CUDA's lazy module
+// loading the first launch of a kernel may have to wait for kernels already running on
+// the device; a kernel that spins on a peer whose launch sits behind such a first launch
+// (several ranks driven by one host thread) would then run into its wait budget.  Called
+// once per device when a context is created.
+extern "C" int tccl_preload_kernels(void) {
+  using namespace tileccl;
+  TCCL_CHECK_CUDA(preload_gemm_kernels());
+  TCCL_CHECK_CUDA(preload_collective_kernels());
+  TCCL_CHECK_CUDA(preload_push_kernels());
+  TCCL_CHECK_CUDA(preload_prim_kernels());
   return kOk;
 }

@@ -438,7 +438,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             (reduce_tile ? (kPair ? 2 : 1) * (kBM / kBK) * (p.world_size - 1) : 0);
         for (int kb = 0; kb < kb_total; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, wb)) {
-            report_status(status, kStatusTimeoutMbarrier, 21, 0, 0, p.rank, t);
+            report_status(status, kStatusTimeoutMbarrier, 21, kb_total, kb, p.rank, t);
             ok = false;
             break;
           }
@@ -828,6 +828,16 @@ cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStrea
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, fused_gemm_sm100_kernel<true>, p);
+}
+
+// Forces the module that holds these kernels onto the current device (see tccl_preload_kernels).
+cudaError_t preload_gemm_kernels() {
+  cudaFuncAttributes a;
+  cudaError_t e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<false>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<true>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, wait_groups_kernel);
+  if (e == cudaSuccess) e = launch_fused_gemm_attrs_once();
+  return e;
 }
 
 cudaError_t launch_wait_groups(const uint32_t* sig, int sig_stride, int n_src, int n_groups,

@@ -138,3 +138,10 @@ extern "C" int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t 
   TCCL_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
+
+namespace tileccl {
+cudaError_t preload_prim_kernels() {
+  cudaFuncAttributes a;
+  return cudaFuncGetAttributes(&a, prim_test_kernel);
+}
+}  // namespace tileccl

@@ -155,3 +155,10 @@ extern "C" int tccl_push_region(uint64_t region, uint64_t mc_region, int64_t ld_
   TCCL_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
+
+namespace tileccl {
+cudaError_t preload_push_kernels() {
+  cudaFuncAttributes a;
+  return cudaFuncGetAttributes(&a, push_region_kernel);
+}
+}  // namespace tileccl

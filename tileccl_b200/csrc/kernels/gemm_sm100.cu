@@ -279,6 +279,52 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     }
   };
 
+  // ------------------- all-gather push of the A operand (warps 2, 3) -------------------
+  // This rank's shard goes to the same place in every peer's heap: 16-byte stores, or one
+  // multimem store per 16 bytes when a multicast mapping is given.  A warp sustains well
+  // under 1 GB/s of remote stores, so both spare warps of every CTA share the work; each
+  // adds one arrival to the peers' gate counter when its part has been performed.
+  auto ag_push_role = [&](int part) {
+    if (p.ag_bytes == 0 || !p.do_ag_push || p.world_size <= 1) return;
+    constexpr int U = 8;
+    const char* src = reinterpret_cast<const char*>(p.ag_src);
+    const uint64_t nvec = p.ag_bytes >> 4;
+    const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 2 * 32;
+    uint64_t i = (static_cast<uint64_t>(blockIdx.x) * 2 + part) * 32 + lane;
+    for (; i < nvec; i += U * stride) {
+      uint4 v[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j)
+        if (i + j * stride < nvec) v[j] = ld_stream_v4(src + ((i + j * stride) << 4));
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        if (i + j * stride >= nvec) continue;
+        const uint64_t off = (i + j * stride) << 4;
+        if (p.ag_mc_dst != 0) {
+          multimem_st_v4(reinterpret_cast<char*>(p.ag_mc_dst) + off, v[j]);
+        } else {
+          for (int d = 1; d < p.world_size; ++d) {
+            const int r = (p.rank + d) % p.world_size;
+            st_remote_v4(reinterpret_cast<char*>(static_cast<int64_t>(p.ag_dst) +
+                                                 static_cast<int64_t>(r - p.rank) * p.heap_stride) +
+                             off, v[j]);
+          }
+        }
+      }
+    }
+    fence_acq_rel_sys();
+    __syncwarp();
+    if (lane == 0) {
+      for (int d = 1; d < p.world_size; ++d) {
+        const int r = (p.rank + d) % p.world_size;
+        red_release_sys_add(
+            reinterpret_cast<uint32_t*>(static_cast<int64_t>(p.a_gate) +
+                                        static_cast<int64_t>(r - p.rank) * p.heap_stride) + p.rank,
+            1u);
+      }
+    }
+  };
+
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (elect_one_sync()) {
@@ -470,47 +516,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
     }
   } else if (warp == 2) {
+    ag_push_role(0);
     if (comm_push) comm_role(0);
   } else if (warp == 3) {
-    // ------------------- all-gather push of the A operand ---------------------
-    if (p.ag_bytes != 0 && p.do_ag_push && p.world_size > 1) {
-      const char* src = reinterpret_cast<const char*>(p.ag_src);
-      const uint64_t nvec = p.ag_bytes >> 4;
-      const uint64_t stride = static_cast<uint64_t>(gridDim.x) * 32 * 4;
-      for (uint64_t base = (static_cast<uint64_t>(blockIdx.x) * 32 + lane) * 4; base < nvec;
-           base += stride) {
-        uint4 v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (base + j < nvec) v[j] = ld_stream_v4(src + ((base + j) << 4));
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (base + j >= nvec) continue;
-          const uint64_t off = (base + j) << 4;
-          if (p.ag_mc_dst != 0) {
-            multimem_st_v4(reinterpret_cast<char*>(p.ag_mc_dst) + off, v[j]);
-          } else {
-            for (int d = 1; d < p.world_size; ++d) {
-              const int r = (p.rank + d) % p.world_size;
-              st_remote_v4(reinterpret_cast<char*>(static_cast<int64_t>(p.ag_dst) +
-                                                   static_cast<int64_t>(r - p.rank) * p.heap_stride) +
-                               off, v[j]);
-            }
-          }
-        }
-      }
-      fence_acq_rel_sys();
-      __syncwarp();
-      if (lane == 0) {
-        for (int d = 1; d < p.world_size; ++d) {
-          const int r = (p.rank + d) % p.world_size;
-          red_release_sys_add(
-              reinterpret_cast<uint32_t*>(static_cast<int64_t>(p.a_gate) +
-                                          static_cast<int64_t>(r - p.rank) * p.heap_stride) + p.rank,
-              1u);
-        }
-      }
-    }
+    ag_push_role(1);
     if (comm_push) comm_role(1);
     // ---------------------- incoming TileGroup waiter -------------------------
     if (p.mode == kModePushAll && p.wait_incoming && p.world_size > 1) {

@@ -22,6 +22,7 @@ MODE_PUSH_ALL = 1
 MODE_REDUCE_SCATTER = 2
 MODE_ALL_SCATTER = 3
 
+AG_PUSH_WARPS = 2          # warps per CTA that push the A operand (one gate arrival each)
 PUSH_STORES = 0
 PUSH_TMA = 1
 PUSH_MULTIMEM = 2

@@ -60,7 +60,15 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
         raise ValueError(f"rows per rank ({mloc}) must be a multiple of {fg.BLOCK_M} so that no "
                          "tile mixes rows of two ranks")
     if use_multimem is None:
-        use_multimem = ws > 1 and ctx.heap.has_multicast and _fused.default_push_mode(ctx) == fg.PUSH_MULTIMEM
+        # One multimem store reaches every peer: from three ranks on the shard leaves this
+        # GPU once instead of ws - 1 times (the spare warps that push it are store-rate
+        # bound).  With two ranks a multicast store also loops back to the sender.
+        import os
+
+        use_multimem = (ws > 2 and ctx.heap.has_multicast
+                        and os.environ.get("TILECCL_DISABLE_NVLS", "0") in ("", "0")) or (
+            ws > 1 and ctx.heap.has_multicast
+            and _fused.default_push_mode(ctx) == fg.PUSH_MULTIMEM)
     key = ("ag_gemm", name, x_full.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, x_full.dtype,
            epi, b_is_nk, use_multimem)
     st = _fused.op_state(ctx, key)
@@ -89,7 +97,7 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
         plan.launch()
         return out
     gate["epoch"] += 1
-    target = gate["epoch"] * plan.push_grid
+    target = gate["epoch"] * plan.push_grid * fg.AG_PUSH_WARPS
     if ctx.emulated:
         phases = [_fused._on_device(ctx, lambda: plan.launch(a_gate_target=target, tile_begin=0,
                                                              tile_end=0, ag_push=True)),

@@ -116,6 +116,21 @@ class GemmDesc(C.Structure):
     ]
 
 
+STREAM_MAX_RANGES = 4
+
+
+class StreamChunk(C.Structure):
+    _fields_ = [
+        ("tile_begin", C.c_int32),
+        ("tile_end", C.c_int32),
+        ("n_ranges", C.c_int32),
+        ("reserved", C.c_int32),
+        ("dst", C.c_uint64 * STREAM_MAX_RANGES),
+        ("src", C.c_uint64 * STREAM_MAX_RANGES),
+        ("bytes", C.c_uint64 * STREAM_MAX_RANGES),
+    ]
+
+
 class GemmPlanInfo(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),
@@ -146,6 +161,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_gemm_plan_create": [C.POINTER(GemmDesc), C.POINTER(vp)],
         "tccl_gemm_plan_info": [vp, C.POINTER(GemmPlanInfo)],
         "tccl_gemm_plan_launch": [vp, u32, u32, i32, i32, i32, u64],
+        "tccl_gemm_plan_launch_streamed": [vp, u32, u32, i32, C.POINTER(StreamChunk), i32, u64, u64],
         "tccl_gemm_plan_destroy": [vp],
         "tccl_wait_groups": [u64, i32, i32, i32, u64, u32, i32, u64, u64, i32, u64],
         "tccl_device_count": [C.POINTER(i32)],

@@ -139,6 +139,23 @@ int tccl_gemm_plan_info(void* plan, TcclGemmPlanInfo* out);
 // of the A operand (an empty tile range is then allowed: push only).
 int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, int32_t tile_begin,
                           int32_t tile_end, int32_t flags, uint64_t stream);
+// The same launch while the A operand is still arriving from pinned host memory: for each
+// run of tiles, the listed byte ranges are copied host -> device on `copy_stream`
+// (one cudaMemcpyAsync per range), and the run is launched on `stream` as soon as its
+// copies are done.  The copies start after everything queued on `stream` so far (earlier
+// readers of A).  flags as above; bit 0 applies to the last run, bit 1 to the first.
+#define TCCL_STREAM_MAX_RANGES 4
+typedef struct TcclStreamChunk {
+  int32_t tile_begin, tile_end;
+  int32_t n_ranges;
+  int32_t reserved;
+  uint64_t dst[TCCL_STREAM_MAX_RANGES];     // device addresses
+  uint64_t src[TCCL_STREAM_MAX_RANGES];     // pinned host addresses
+  uint64_t bytes[TCCL_STREAM_MAX_RANGES];
+} TcclStreamChunk;
+int tccl_gemm_plan_launch_streamed(void* plan, uint32_t epoch, uint32_t a_gate_target,
+                                   int32_t flags, const TcclStreamChunk* chunks, int32_t n_chunks,
+                                   uint64_t copy_stream, uint64_t stream);
 int tccl_gemm_plan_destroy(void* plan);
 
 // Consumer side of the TileGroup protocol as its own launch: waits until

@@ -7,6 +7,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <vector>
 
 #include "../api.h"
 #include "../runtime/errors.h"
@@ -31,6 +32,10 @@ struct GemmPlan {
   TcclGemmPlanInfo info;
   bool pair_kernel = false;   // whole-order launches run on CTA pairs
   int pair_grid = 0, pair_push_grid = 0;
+  std::vector<cudaEvent_t> events;   // streamed launches: one per run of tiles, + 1
+  ~GemmPlan() {
+    for (cudaEvent_t e : events) cudaEventDestroy(e);
+  }
 };
 
 // 16-bit row-major matrix [rows, cols] (+ optional slot dimension) -> tensor map
@@ -282,6 +287,42 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
     return kOk;
   }
   TCCL_CHECK_CUDA(launch_fused_gemm(p, grid, reinterpret_cast<cudaStream_t>(stream)));
+  return kOk;
+}
+
+extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint32_t a_gate_target,
+                                              int32_t flags, const TcclStreamChunk* chunks,
+                                              int32_t n_chunks, uint64_t copy_stream_,
+                                              uint64_t stream_) {
+  TCCL_CHECK_ARG(plan_ != nullptr && chunks != nullptr && n_chunks >= 1, "bad argument");
+  GemmPlan* plan = static_cast<GemmPlan*>(plan_);
+  cudaStream_t copy_stream = reinterpret_cast<cudaStream_t>(copy_stream_);
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  TCCL_CHECK_ARG(copy_stream != stream, "the copy stream must differ from the launch stream");
+  while (static_cast<int>(plan->events.size()) < n_chunks + 1) {
+    cudaEvent_t e;
+    TCCL_CHECK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    plan->events.push_back(e);
+  }
+  // Earlier work on `stream` may still read A: the copies wait for it.
+  TCCL_CHECK_CUDA(cudaEventRecord(plan->events[n_chunks], stream));
+  TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->events[n_chunks], 0));
+  for (int i = 0; i < n_chunks; ++i) {
+    const TcclStreamChunk& c = chunks[i];
+    TCCL_CHECK_ARG(c.n_ranges >= 0 && c.n_ranges <= TCCL_STREAM_MAX_RANGES, "too many ranges");
+    for (int r = 0; r < c.n_ranges; ++r)
+      TCCL_CHECK_CUDA(cudaMemcpyAsync(reinterpret_cast<void*>(c.dst[r]),
+                                      reinterpret_cast<const void*>(c.src[r]), c.bytes[r],
+                                      cudaMemcpyHostToDevice, copy_stream));
+    TCCL_CHECK_CUDA(cudaEventRecord(plan->events[i], copy_stream));
+    TCCL_CHECK_CUDA(cudaStreamWaitEvent(stream, plan->events[i], 0));
+    int f = 0;
+    if (i == n_chunks - 1) f |= flags & 1;
+    if (i == 0) f |= flags & 2;
+    int rc = tccl_gemm_plan_launch(plan_, epoch, a_gate_target, c.tile_begin, c.tile_end, f,
+                                   stream_);
+    if (rc != kOk) return rc;
+  }
   return kOk;
 }
 

@@ -1,15 +1,28 @@
 // Persistent warp-specialised tcgen05 GEMM for sm_100a, with the collective
 // that follows it fused into the epilogue.
 //
-// One CTA per SM.  Roles:
-//   warp 0      TMA producer: A / B tiles -> 4-stage shared-memory ring (local memory only)
-//   warp 1      MMA issuer:   tcgen05.mma (128 x 256 x 16, fp32 accumulators in TMEM)
-//   warp 2      TMEM allocator / deallocator
-//   warp 3      incoming-TileGroup waiter (push-all mode)
-//   warps 4..7  epilogue: tcgen05.ld -> (reduce | SiLU-gate) -> cast -> swizzled staging in
-//               shared memory -> TMA store to the local destination and, per mode, stores
-//               to peer GPUs' memory, followed by a release-add on the peers' TileGroup
-//               counters.
+// Two forms of one kernel (template parameter kPair):
+//   one CTA per tile   128 x 256 tile, tcgen05.mma.cta_group::1, four-stage operand ring.
+//                      Used for tile-range launches (emulated ranks, host-streamed operand)
+//                      and traced launches.
+//   CTA pair per tile  a cluster of two CTAs on a 256 x 256 tile, tcgen05.mma.cta_group::2:
+//                      every CTA stages its own 128 rows of A and 128 of the 256 columns of
+//                      B (32 KB instead of 48 KB per K block and SM), six stages; the
+//                      leader CTA issues the MMAs, commits are multicast to both CTAs'
+//                      barriers, each CTA owns the accumulator and the epilogue of its 128
+//                      rows.  Used whenever a launch runs the rank's whole tile order.
+//
+// Roles per CTA (256 threads):
+//   warp 0      TMA producer: A / B tiles -> shared-memory ring (local memory only, no
+//               multicast); for the own tiles of a reduce-scatter also the peers' staged
+//               partial tiles, which the tensor cores add to the accumulator (identity x
+//               tile)
+//   warp 1      MMA issuer (fp32 accumulators in TMEM, two 256-column buffers)
+//   warp 2, 3   TMEM allocation; all-gather push of the A operand; communication warps of
+//               the `stores` / `multimem` push modes; incoming-TileGroup waiter
+//   warps 4..7  epilogue: tcgen05.ld -> (SiLU-gate) -> cast -> swizzled staging in shared
+//               memory -> TMA store to the local destination and, per mode, TMA stores into
+//               the peers' memory, followed by an add on the peers' TileGroup counters.
 //
 // What replaces what in the reference: the plain mode is its persistent GEMM
 // (tileccl/kernels/gemm.py:52-167); push-all is the GEMM-output all-gather
@@ -18,7 +31,7 @@
 // pattern (tileccl/patterns/wg_specialized.py:210-352) with the communication role
 // played by the epilogue warps instead of dedicated SMs.
 //
-// Peer traffic is stores only (plain st.global, TMA store, or multimem.st);
+// Peer traffic is stores only (TMA store, plain st.global, or multimem.st);
 // operands are always TMA-loaded from this GPU's own memory, without multicast.
 #include "gemm_sm100.cuh"
 

@@ -131,6 +131,12 @@ class FusedGemmSpec:
     wait_budget_ns: int = 0
 
 
+def count_launches(n: int) -> None:
+    """Launches issued by the native runtime on behalf of a plan (LAUNCH_COUNT bookkeeping)."""
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += n
+
+
 _IDENTITY = {}
 
 

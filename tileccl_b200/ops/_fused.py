@@ -250,18 +250,41 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, **launch_k
     st = op_state(ctx, ("h2d_stream",))
     if "stream" not in st:
         st["stream"] = torch.cuda.Stream(device=ctx.torch_device)
-        st["events"] = [torch.cuda.Event() for _ in range(16)]
-        st["next"] = 0
     side, cur = st["stream"], torch.cuda.current_stream()
-    chunks = getattr(plan, "_row_chunks", None)
-    if chunks is None:
-        chunks = plan._row_chunks = _tile_row_chunks(plan)
-    side.wait_stream(cur)                       # earlier readers of A are done
+    key = (A.data_ptr(), a_host.data_ptr(), A.stride(0))
+    prepared = getattr(plan, "_stream_chunks", None)
+    if prepared is None or prepared[0] != key:
+        chunks = _tile_row_chunks(plan)
+        if not A.is_contiguous() or any(len(r) > _native.STREAM_MAX_RANGES for _, _, r in chunks):
+            prepared = (key, None, chunks)
+        else:
+            row_bytes = A.shape[1] * A.element_size()
+            arr = (_native.StreamChunk * len(chunks))()
+            for c, (t0, t1, ranges) in zip(arr, chunks):
+                c.tile_begin, c.tile_end, c.n_ranges = t0, t1, len(ranges)
+                for i, (lo, hi) in enumerate(ranges):
+                    c.dst[i] = A.data_ptr() + lo * row_bytes
+                    c.src[i] = a_host.data_ptr() + lo * row_bytes
+                    c.bytes[i] = (hi - lo) * row_bytes
+            prepared = (key, arr, chunks)
+        plan._stream_chunks = prepared
+    _, arr, chunks = prepared
     wait_incoming = launch_kw.pop("wait_incoming", False)
     ag_push = launch_kw.pop("ag_push", False)
+    if arr is not None:
+        # Copies, events and launches are issued by the native runtime: a few microseconds
+        # of host time per run instead of a Python round trip each.
+        fg.count_launches(len(chunks))
+        _native.call("tccl_gemm_plan_launch_streamed", plan._handle,
+                     launch_kw.get("epoch", 1) & 0xFFFFFFFF,
+                     launch_kw.get("a_gate_target", 0) & 0xFFFFFFFF,
+                     (1 if wait_incoming else 0) | (2 if ag_push else 0), arr, len(chunks),
+                     side.cuda_stream, cur.cuda_stream)
+        return
+    side.wait_stream(cur)                       # earlier readers of A are done
+    events = st.setdefault("events", [torch.cuda.Event() for _ in range(16)])
     for i, (t0, t1, ranges) in enumerate(chunks):
-        ev = st["events"][st["next"] % 16]
-        st["next"] += 1
+        ev = events[i % 16]
         with torch.cuda.stream(side):
             for lo, hi in ranges:
                 A[lo:hi].copy_(a_host[lo:hi], non_blocking=True)

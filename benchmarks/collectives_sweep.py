@@ -4,7 +4,7 @@ scatter on symmetric-heap buffers, 4 KiB .. 1 GiB, fp16 and fp32, values U(-1, 1
 rank, against NCCL on the same buffers.  One process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        benchmarks/collectives_sweep.py [--max-bytes 1073741824] [--out gpurun_out/sweep.json]
+        benchmarks/collectives_sweep.py [--max-bytes 1073741824] [--out sweep.json]
 
 Device time (CUDA events), max over ranks; bus GB/s uses the usual factors
 (allreduce 2(n-1)/n, allgather / reduce_scatter / scatter (n-1)/n, broadcast 1).

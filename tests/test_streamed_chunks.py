@@ -47,3 +47,38 @@ def test_visit_rows_matches_the_native_tile_order():
         for rank in range(ws):
             native = em.tile_order(m, 2, owners=ws, rank=rank, world_size=ws, own_lag=lag)
             assert [(o, lm) for o, lm, ln in native if ln == 0] == visit_rows(m, ws, rank, ws, lag)
+
+
+def test_default_rs_own_lag_policy(monkeypatch):
+    from tileccl_b200.ops._fused import default_rs_own_lag
+
+    monkeypatch.delenv("TILECCL_RS_OWN_LAG", raising=False)
+    # two ranks, 64 tile rows of 16 tiles: a round is 2 MiB = ~3 us of link -> about 13 rounds
+    lag = default_rs_own_lag(2, 64, 16)
+    assert 8 <= lag <= 32
+    # eight ranks: a round is 14.7 MiB -> a few rounds
+    assert 1 <= default_rs_own_lag(8, 16, 16) <= 4
+    # nothing to overlap with a single tile row, or when the lag would cover every row
+    assert default_rs_own_lag(2, 1, 16) == 0
+    assert default_rs_own_lag(2, 4, 1) == 0
+    monkeypatch.setenv("TILECCL_RS_OWN_LAG", "5")
+    assert default_rs_own_lag(2, 64, 16) == 5
+
+
+def test_nvls_policy_for_collectives(monkeypatch):
+    from types import SimpleNamespace
+    from tileccl_b200.primitives.collectives import _use_multimem
+
+    for var in ("TILECCL_DISABLE_NVLS", "TILECCL_FORCE_NVLS"):
+        monkeypatch.delenv(var, raising=False)
+    two = SimpleNamespace(has_multicast=True, world_size=2)
+    eight = SimpleNamespace(has_multicast=True, world_size=8)
+    none = SimpleNamespace(has_multicast=False, world_size=8)
+    assert not _use_multimem(two, 1 << 20)        # a multicast store loops back at two ranks
+    assert _use_multimem(eight, 1 << 20)
+    assert not _use_multimem(eight, 24 + 4)       # not a multiple of 16 bytes
+    assert not _use_multimem(none, 1 << 20)
+    monkeypatch.setenv("TILECCL_FORCE_NVLS", "1")
+    assert _use_multimem(two, 1 << 20)
+    monkeypatch.setenv("TILECCL_DISABLE_NVLS", "1")
+    assert not _use_multimem(eight, 1 << 20)

@@ -63,3 +63,24 @@ def test_rejects_pageable_or_mismatched_host_tensor(ctx):
     with pytest.raises(ValueError):
         ops.gemm_allgather_rows(a, b, c, ctx=ctx,
                                 a_host=torch.zeros(128, 64, dtype=torch.float16).pin_memory())
+
+
+def test_plan_ordered_copies_pipeline_two_problems(ctx):
+    """``a_host_order="plan"``: the copy of one problem may overlap the kernels of the other;
+    repeated calls on the same buffers still see each call's own data."""
+    from tileccl_b200 import ops
+
+    probs = []
+    for (M, N, K) in ((4096, 2048, 512), (2048, 4096, 1024)):
+        a_host = (torch.randn(M, K) * K ** -0.5).to(torch.float16).pin_memory()
+        probs.append((a_host, ctx.zeros(M, K, dtype=torch.float16),
+                      ctx.randn(K, N, dtype=torch.float16), ctx.zeros(M, N, dtype=torch.float16)))
+    for it in range(3):
+        for a_host, a, b, c in probs:
+            a_host.mul_(-0.5)
+        for a_host, a, b, c in probs:
+            ops.gemm_allgather_rows(a, b, c, ctx=ctx, a_host=a_host, a_host_order="plan")
+        torch.cuda.synchronize()
+        for a_host, a, b, c in probs:
+            assert torch.equal(a.cpu(), a_host)
+            assert _rel(c, a_host.cuda().float() @ b.float()) < 5e-3

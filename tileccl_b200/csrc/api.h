@@ -143,7 +143,10 @@ int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, in
 // run of tiles, the listed byte ranges are copied host -> device on `copy_stream`
 // (one cudaMemcpyAsync per range), and the run is launched on `stream` as soon as its
 // copies are done.  The copies start after everything queued on `stream` so far (earlier
-// readers of A).  flags as above; bit 0 applies to the last run, bit 1 to the first.
+// readers of A); with flags bit 2 they only follow this plan's previous streamed call (the
+// caller promises that no other pending work on `stream` touches A), so the copy of one
+// problem overlaps the kernels of the previous one.  Bit 0 applies to the last run, bit 1 to
+// the first.
 #define TCCL_STREAM_MAX_RANGES 4
 typedef struct TcclStreamChunk {
   int32_t tile_begin, tile_end;

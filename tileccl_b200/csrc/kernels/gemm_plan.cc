@@ -33,8 +33,11 @@ struct GemmPlan {
   bool pair_kernel = false;   // whole-order launches run on CTA pairs
   int pair_grid = 0, pair_push_grid = 0;
   std::vector<cudaEvent_t> events;   // streamed launches: one per run of tiles, + 1
+  cudaEvent_t done_event = nullptr;  // end of the last streamed call on its launch stream
+  bool streamed_before = false;
   ~GemmPlan() {
     for (cudaEvent_t e : events) cudaEventDestroy(e);
+    if (done_event != nullptr) cudaEventDestroy(done_event);
   }
 };
 
@@ -304,9 +307,15 @@ extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint3
     TCCL_CHECK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     plan->events.push_back(e);
   }
-  // Earlier work on `stream` may still read A: the copies wait for it.
-  TCCL_CHECK_CUDA(cudaEventRecord(plan->events[n_chunks], stream));
-  TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->events[n_chunks], 0));
+  if ((flags & 4) != 0 && plan->streamed_before) {
+    // The caller promises that nothing else pending on `stream` touches A: the copies only
+    // have to follow this plan's own previous streamed call (its last launch read A).
+    TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->done_event, 0));
+  } else {
+    // Earlier work on `stream` may still read A: the copies wait for all of it.
+    TCCL_CHECK_CUDA(cudaEventRecord(plan->events[n_chunks], stream));
+    TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->events[n_chunks], 0));
+  }
   for (int i = 0; i < n_chunks; ++i) {
     const TcclStreamChunk& c = chunks[i];
     TCCL_CHECK_ARG(c.n_ranges >= 0 && c.n_ranges <= TCCL_STREAM_MAX_RANGES, "too many ranges");
@@ -323,6 +332,10 @@ extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint3
                                    stream_);
     if (rc != kOk) return rc;
   }
+  if (plan->done_event == nullptr)
+    TCCL_CHECK_CUDA(cudaEventCreateWithFlags(&plan->done_event, cudaEventDisableTiming));
+  TCCL_CHECK_CUDA(cudaEventRecord(plan->done_event, stream));
+  plan->streamed_before = true;
   return kOk;
 }
 

@@ -292,7 +292,8 @@ class GemmAllGatherPlan:
         if got != self.contract:
             raise ValueError("tensors no longer match this GemmAllGatherPlan; build a new plan")
 
-    def execute(self, A, B, C, *, validate: bool = True, wait: bool = True, a_host=None):
+    def execute(self, A, B, C, *, validate: bool = True, wait: bool = True, a_host=None,
+                a_host_order: str = "stream"):
         """``a_host``: pinned host tensor shaped like ``A``; when given, ``A`` is filled
         from it on a side stream, run of tile rows by run, while the kernel computes."""
         if validate:
@@ -301,10 +302,11 @@ class GemmAllGatherPlan:
         if c.layout == "columns":
             _fused.push_all(ctx, "gemm_allgather_cols", A, B, C, region_row0=0,
                             region_col0=c.rank * c.shard_cols, b_is_nk=self.b_is_nk, wait=wait,
-                            a_host=a_host)
+                            a_host=a_host, a_host_order=a_host_order)
         else:
             _fused.push_all(ctx, "gemm_allgather_rows", A, B, C, region_row0=c.rank * A.shape[0],
-                            region_col0=0, b_is_nk=self.b_is_nk, wait=wait, a_host=a_host)
+                            region_col0=0, b_is_nk=self.b_is_nk, wait=wait, a_host=a_host,
+                            a_host_order=a_host_order)
         return C
 
     def to_dict(self) -> dict:
@@ -360,19 +362,23 @@ def gemm_allgather(A, B_shard, C, *, ctx=None, storage_kind="symmetric"):
         A, B_shard, C, validate=False)
 
 
-def gemm_allgather_rows(A_local, B, C, *, ctx=None, b_is_nk=False, wait=True, a_host=None):
+def gemm_allgather_rows(A_local, B, C, *, ctx=None, b_is_nk=False, wait=True, a_host=None,
+                        a_host_order="stream"):
     """Row-sharded form: ``A_local (M/ws, K)``, ``B (K, N)``, ``C (M, N)`` on the heap;
     rows ``[r*M/ws, (r+1)*M/ws)`` of ``C`` on every rank come from rank ``r``.
 
     ``a_host`` (pinned host tensor shaped like ``A_local``): the activations are
     streamed from the host into ``A_local`` while the kernel runs, tile rows in
     the order the kernel consumes them, so only the last run's math is exposed
-    after the PCIe copy."""
+    after the PCIe copy.  ``a_host_order="plan"``: the caller guarantees that no other
+    pending work on the stream touches ``A_local``; the copy then only follows this
+    operator's previous call on the same buffers and overlaps whatever else is queued."""
     ctx = _ctx_or_current(ctx)
     plan = _cached_plan(ctx, _mm_key("gemm_allgather_rows", A_local, B, C, b_is_nk),
                         lambda: build_gemm_allgather_plan(A_local, B, C, ctx=ctx, layout="rows",
                                                           b_is_nk=b_is_nk))
-    return plan.execute(A_local, B, C, validate=False, wait=wait, a_host=a_host)
+    return plan.execute(A_local, B, C, validate=False, wait=wait, a_host=a_host,
+                        a_host_order=a_host_order)
 
 
 # ==========================================================================
@@ -408,13 +414,15 @@ class GemmReduceScatterPlan:
         if got != self.contract:
             raise ValueError("tensors no longer match this GemmReduceScatterPlan; build a new plan")
 
-    def execute(self, A, B, C, *, validate: bool = True, a_host=None):
+    def execute(self, A, B, C, *, validate: bool = True, a_host=None,
+                a_host_order: str = "stream"):
         """``a_host``: pinned host tensor shaped like ``A`` to stream the operand from."""
         if validate:
             self.validate_tensors(A, B, C)
         axis = 1 if self.contract.layout == "columns" else 0
         _fused.reduce_scatter(self.ctx, f"gemm_reducescatter_{self.contract.layout}", A, B, C,
-                              split_axis=axis, b_is_nk=self.b_is_nk, a_host=a_host)
+                              split_axis=axis, b_is_nk=self.b_is_nk, a_host=a_host,
+                              a_host_order=a_host_order)
         return C
 
     def to_dict(self) -> dict:
@@ -485,7 +493,8 @@ def gemm_reducescatter(A, B, C, *, ctx=None, implementation="auto", storage_kind
                             storage_kind=storage_kind)).execute(A, B, C, validate=False)
 
 
-def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False, a_host=None):
+def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False, a_host=None,
+                            a_host_order="stream"):
     """Row-sharded form: ``A (M, K/ws)``, ``B (K/ws, N)``, ``C_local (M/ws, N)``:
     ``C_local_r = sum_i (A_i @ B_i)[r*M/ws:(r+1)*M/ws, :]``.  ``a_host`` streams ``A``
     from pinned host memory as in :func:`gemm_allgather_rows`."""
@@ -493,7 +502,7 @@ def gemm_reducescatter_rows(A, B, C_local, *, ctx=None, b_is_nk=False, a_host=No
     plan = _cached_plan(ctx, _mm_key("gemm_reducescatter_rows", A, B, C_local, b_is_nk),
                         lambda: build_gemm_reducescatter_plan(A, B, C_local, ctx=ctx, layout="rows",
                                                               b_is_nk=b_is_nk))
-    return plan.execute(A, B, C_local, validate=False, a_host=a_host)
+    return plan.execute(A, B, C_local, validate=False, a_host=a_host, a_host_order=a_host_order)
 
 
 # ==========================================================================

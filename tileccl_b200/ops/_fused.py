@@ -229,14 +229,23 @@ def _tile_row_chunks(plan, min_tiles: int = 2 * 148, max_chunks: int = 8) -> lis
     return chunks
 
 
-def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, **launch_kw) -> None:
+def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
+                    order: str = "stream", **launch_kw) -> None:
     """Run ``plan`` while its A operand is still arriving from pinned host memory.
 
     The rows of ``a_host`` are copied to ``A`` on a side stream in the order the
     kernel consumes them; every run of tile rows is launched as soon as its rows
     are on the device, so all but the last run's math hides under the PCIe copy.
     Everything is stream-ordered: the host never blocks.
+
+    ``order="stream"``: the copies start after everything queued on the current
+    stream (anything there may still read ``A``).  ``order="plan"``: the caller
+    guarantees that no other pending work touches ``A``; the copies then only follow
+    this operator's previous call on the same buffers, and the transfer for one
+    problem overlaps the kernels of the one before it.
     """
+    if order not in ("stream", "plan"):
+        raise ValueError("order must be 'stream' or 'plan'")
     if a_host.shape != A.shape or a_host.dtype != A.dtype:
         raise ValueError(f"a_host must match A: {tuple(a_host.shape)} {a_host.dtype} vs "
                          f"{tuple(A.shape)} {A.dtype}")
@@ -278,7 +287,8 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, **launch_k
         _native.call("tccl_gemm_plan_launch_streamed", plan._handle,
                      launch_kw.get("epoch", 1) & 0xFFFFFFFF,
                      launch_kw.get("a_gate_target", 0) & 0xFFFFFFFF,
-                     (1 if wait_incoming else 0) | (2 if ag_push else 0), arr, len(chunks),
+                     (1 if wait_incoming else 0) | (2 if ag_push else 0)
+                     | (4 if order == "plan" else 0), arr, len(chunks),
                      side.cuda_stream, cur.cuda_stream)
         return
     side.wait_stream(cur)                       # earlier readers of A are done
@@ -301,7 +311,8 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, **launch_k
 def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
              region_row0: int, region_col0: int, b_is_nk: bool = False,
              group_m_tiles: Optional[int] = None, push_mode: Optional[int] = None,
-             wait: bool = True, a_host: Optional[torch.Tensor] = None) -> None:
+             wait: bool = True, a_host: Optional[torch.Tensor] = None,
+             a_host_order: str = "stream") -> None:
     """Product of the local operands, written into the same region of ``C`` on every rank.
 
     ``C`` must live on the symmetric heap.  ``region_*`` is where this rank's
@@ -373,13 +384,14 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
     epoch = sigst["epoch"]
     if ws == 1:
         if a_host is not None:
-            launch_streamed(ctx, plan, A, a_host)
+            launch_streamed(ctx, plan, A, a_host, order=a_host_order)
         else:
             plan.launch()
         return
     fused_wait = wait and _in_kernel_waits_ok(ctx) and not ctx.is_single_process
     if a_host is not None and not ctx.is_single_process:
         phases = [_on_device(ctx, lambda: launch_streamed(ctx, plan, A, a_host, epoch=epoch,
+                                                          order=a_host_order,
                                                           wait_incoming=fused_wait))]
     else:
         if a_host is not None:
@@ -404,7 +416,8 @@ def wait_groups(ctx, sig: torch.Tensor, n_groups: int, per_epoch: torch.Tensor, 
 # --------------------------------------------------------------------------
 def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
                    split_axis: int, b_is_nk: bool = False, group_m_tiles: Optional[int] = None,
-                   push_mode: Optional[int] = None, a_host: Optional[torch.Tensor] = None) -> None:
+                   push_mode: Optional[int] = None, a_host: Optional[torch.Tensor] = None,
+                   a_host_order: str = "stream") -> None:
     """Every rank multiplies its operands; block ``r`` of the summed product lands on rank ``r``.
 
     ``split_axis=0``: ``A`` is ``[ws * Mloc, K]``, ``C`` is ``[Mloc, N]`` (row blocks).
@@ -482,7 +495,8 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     sigst["epoch"] += 1
     epoch = sigst["epoch"]
     if a_host is not None and (ws == 1 or (_in_kernel_waits_ok(ctx) and not ctx.is_single_process)):
-        phases = [_on_device(ctx, lambda: launch_streamed(ctx, plan, A, a_host, epoch=epoch))]
+        phases = [_on_device(ctx, lambda: launch_streamed(ctx, plan, A, a_host, epoch=epoch,
+                                                          order=a_host_order))]
     elif ws == 1 or _in_kernel_waits_ok(ctx):
         if a_host is not None:
             A.copy_(a_host, non_blocking=True)

@@ -66,11 +66,14 @@ class HardwareProfile:
         ``peaks_path``: JSON with ``bf16_tflops`` (cuBLAS burst).  ``calibration_path``:
         JSON with ``alpha_us``, ``beta_us_per_byte`` and optionally ``min_comm_us``
         (written by ``benchmarks/phase0_calibrate.py``); the environment variable
-        ``TILECCL_CALIBRATION`` names it by default.
+        ``TILECCL_CALIBRATION`` names it, else the ``calibration/b200.json`` that ships
+        next to the package (measured on an 8 x B200 NVSwitch machine) is used.
         """
         prof = _PRESETS[Interconnect.NVLINK_5]
+        shipped = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
+            os.path.abspath(__file__)))), "calibration", "b200.json")
         for path, apply in ((peaks_path, _apply_peaks),
-                            (calibration_path or os.environ.get("TILECCL_CALIBRATION"),
+                            (calibration_path or os.environ.get("TILECCL_CALIBRATION") or shipped,
                              _apply_calibration)):
             if path and os.path.exists(path):
                 try:

@@ -32,11 +32,13 @@ def test_chunks_cover_every_tile_and_row_once(m_tiles, n_tiles, owners, rank, su
 
 
 def test_chunks_follow_the_round_order():
-    # rank 1 of 4: every round visits owners 2, 3, 0; its own rows come last
+    # rank 1 of 4: every round visits owners 2, 3, 0; its own rows come last.  The rows a
+    # run needs are merged into one contiguous range per owner.
     chunks = _tile_row_chunks(_plan(32, 16, 4, 1, 4096, 16384))
     first = chunks[0][2]
-    assert first[0][0] == 2 * 4096 and {lo // 4096 for lo, _ in first} == {0, 2, 3}
-    assert chunks[-1][2][-1][1] == 2 * 4096
+    assert {lo // 4096 for lo, _ in first} == {0, 2, 3} and len(first) == 3
+    assert all(lo % 4096 == 0 for lo, _ in first)            # each owner's first rows
+    assert chunks[-1][2][-1][1] == 2 * 4096                  # ends with rank 1's own rows
 
 
 def test_visit_rows_matches_the_native_tile_order():

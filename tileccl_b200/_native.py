@@ -116,7 +116,7 @@ class GemmDesc(C.Structure):
     ]
 
 
-STREAM_MAX_RANGES = 4
+STREAM_MAX_RANGES = 64
 
 
 class StreamChunk(C.Structure):

@@ -147,7 +147,7 @@ int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, in
 // caller promises that no other pending work on `stream` touches A), so the copy of one
 // problem overlaps the kernels of the previous one.  Bit 0 applies to the last run, bit 1 to
 // the first.
-#define TCCL_STREAM_MAX_RANGES 4
+#define TCCL_STREAM_MAX_RANGES 64
 typedef struct TcclStreamChunk {
   int32_t tile_begin, tile_end;
   int32_t n_ranges;

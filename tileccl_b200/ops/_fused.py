@@ -221,11 +221,15 @@ def _tile_row_chunks(plan, min_tiles: int = 2 * 148, max_chunks: int = 8) -> lis
             limit = spec.sub_m if plan.owners > 1 else spec.a_rows
             lo = base + lm * fg.BLOCK_M
             hi = min(base + min(limit, (lm + 1) * fg.BLOCK_M), spec.a_rows)
-            if ranges and ranges[-1][1] == lo:
-                ranges[-1] = (ranges[-1][0], hi)       # merge adjacent rows
+            ranges.append((lo, hi))
+        # rows of one owner are contiguous across rounds: sort and merge into few large copies
+        merged = []
+        for lo, hi in sorted(ranges):
+            if merged and merged[-1][1] == lo:
+                merged[-1] = (merged[-1][0], hi)
             else:
-                ranges.append((lo, hi))
-        chunks.append((r0 * n_t, r1 * n_t, ranges))
+                merged.append((lo, hi))
+        chunks.append((r0 * n_t, r1 * n_t, merged))
     return chunks
 
 

@@ -150,7 +150,9 @@ _lib_lock = threading.Lock()
 
 
 def lib_path() -> Path:
-    return _build.LIB_PATH
+    """The shared object to load; ``TILECCL_NATIVE_LIB`` names another build of it."""
+    override = os.environ.get("TILECCL_NATIVE_LIB")
+    return Path(override) if override else _build.LIB_PATH
 
 
 def _declare(lib: C.CDLL) -> None:

@@ -122,13 +122,25 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
 // Shared-memory geometry of the two kernel forms.  One CTA: 128 x 256 tile, 48 KB per K
 // block, four stages.  CTA pair (tcgen05 cta_group::2): 256 x 256 per pair, every CTA stages
 // its own 128 rows of A and 128 of the 256 columns of B (32 KB), six stages.
+#ifndef TCCL_PAIR_STAGES
+#define TCCL_PAIR_STAGES 6
+#endif
+#ifndef TCCL_PAIR_EPI_BUFS
+#define TCCL_PAIR_EPI_BUFS 2
+#endif
+
 template <bool kPair>
 struct Geo {
-  static constexpr int kNumStages = kPair ? 6 : kStages;
+  static constexpr int kNumStages = kPair ? TCCL_PAIR_STAGES : kStages;
+  // staging buffers per epilogue warp: a deeper ring lets the epilogue run further ahead of
+  // bulk stores that the link has not taken yet
+  static constexpr int kEpi = kPair ? TCCL_PAIR_EPI_BUFS : kEpiBufs;
   static constexpr int kBBytes = kPair ? kStageBBytes / 2 : kStageBBytes;
   static constexpr int kBytes = kStageABytes + kBBytes;
   static constexpr int kBBoxes = kPair ? kBN / 2 / 64 : kBN / 64;   // 64-column boxes of an MN-major B
-  static_assert(kNumStages * kBytes <= kSmemPipe, "operand ring exceeds its shared-memory budget");
+  static constexpr int kPipeBytes = kNumStages * kBytes;
+  static_assert(kPipeBytes + kEpiWarps * kEpi * kEpiBufBytes <= kSmemPipe + kSmemEpi,
+                "operand ring + staging exceed their shared-memory budget");
 };
 
 }  // namespace
@@ -141,7 +153,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzled tiles need 1024-byte aligned bases.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t smem_epi = smem_base + kSmemPipe;
+  const uint32_t smem_epi = smem_base + G::kPipeBytes;
   const uint32_t smem_ctl = smem_base + kSmemPipe + kSmemEpi;
   uint8_t* ctl_generic = smem_raw + (smem_ctl - smem_u32(smem_raw));
 
@@ -555,7 +567,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     // -------------------------------- epilogue --------------------------------
     const int q = warp - 4;                       // TMEM lane quarter and 32-row slab
     const bool bf16 = p.is_bf16 != 0;
-    const uint32_t my_epi = smem_epi + q * (kEpiBufs * kEpiBufBytes);
+    const uint32_t my_epi = smem_epi + q * (G::kEpi * kEpiBufBytes);
     uint8_t* my_epi_g = smem_raw + (my_epi - smem_u32(smem_raw));
     const int n_chunks = p.epi_op == kEpiSiluGate ? (kBN / 2) / kChunkN : kBN / kChunkN;
     uint32_t acc = 0, acc_phase = 0;
@@ -646,7 +658,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 
         const int col0 = c.out_x + ch * kChunkN;     // destination-local column of v[0]
         // Staging buffer `buf` was last read by the stores committed two chunks ago.
-        if (lane == 0) tma_store_wait_read<kEpiBufs - 1>();
+        if (lane == 0) tma_store_wait_read<G::kEpi - 1>();
         __syncwarp();
         const uint32_t sbuf = my_epi + buf * kEpiBufBytes;
 #pragma unroll
@@ -697,7 +709,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           }
         }
         if (lane == 0) tma_store_commit();
-        buf ^= 1u;
+        buf = (buf + 1u) % G::kEpi;
       }
       if (!ok) break;
 

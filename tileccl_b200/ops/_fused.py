@@ -82,8 +82,9 @@ def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
 
     A round sends one tile row to every peer.  The own row j is reduced once the
     peers' row j has arrived, so it trails by the time a pushed row needs to land
-    under load (about 40 us with the queues the kernel keeps in flight).  0 means
-    "own rows last" (nothing to overlap, or too few rows).
+    under load.  Measured at two ranks (16384 x 4096 x 2048: lag 0 / 8 / 16 / 32 rounds
+    -> 0.174 / 0.166 / 0.154 / 0.161 ms): about 24 us of link time is the sweet spot.
+    0 means "own rows last" (nothing to overlap, or too few rows).
     """
     env = os.environ.get("TILECCL_RS_OWN_LAG")
     if env is not None:
@@ -92,7 +93,7 @@ def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
         return 0
     round_bytes = (ws - 1) * n_tiles * fg.BLOCK_M * fg.BLOCK_N * 2
     round_us = round_bytes / 690e3            # measured NVLink 5 push rate, bytes per us
-    lag = int(-(-40.0 // round_us))
+    lag = int(-(-24.0 // round_us))
     return lag if 1 <= lag < m_tiles else 0
 
 

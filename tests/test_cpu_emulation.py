@@ -116,3 +116,29 @@ def test_tile_order_with_trailing_own_rows(m, n, ws, lag):
             o, lm, _ = order[t]
             o0, lm0, _ = em.tile_order(m, n, owners=ws, rank=0, world_size=ws, own_lag=lag)[t]
             assert (o - rank) % ws == o0 % ws and lm == lm0
+
+
+@pytest.mark.parametrize("ws,m_tiles,lag", [(2, 6, 1), (2, 6, 3), (4, 4, 2), (8, 3, 1), (3, 5, 5),
+                                            (4, 2, 7)])
+def test_reducescatter_with_trailing_own_rows_is_correct_and_deadlock_free(ws, m_tiles, lag):
+    """Every rank is a thread that walks the round order and blocks at its own tiles."""
+    torch.manual_seed(ws * 100 + m_tiles * 10 + lag)
+    bm, bn = 16, 32
+    M, N, K = ws * m_tiles * bm - (3 if m_tiles > 2 else 0) * ws, 80, 8 * ws
+    A = [torch.randn(M, K // ws) for _ in range(ws)]
+    B = [torch.randn(K // ws, N) for _ in range(ws)]
+    outs, st = em.gemm_reducescatter(A, B, block_m=bm, block_n=bn, own_lag=lag, timeout_ms=5000)
+    assert st.ok
+    full = sum(a @ b for a, b in zip(A, B))
+    mloc = M // ws
+    for r in range(ws):
+        assert torch.allclose(outs[r], full[r * mloc:(r + 1) * mloc], atol=1e-4, rtol=1e-4)
+
+
+def test_reducescatter_with_lag_reports_a_missing_peer():
+    torch.manual_seed(3)
+    A = [torch.randn(128, 8) for _ in range(2)]
+    B = [torch.randn(8, 64) for _ in range(2)]
+    _, st = em.gemm_reducescatter(A, B, block_m=16, block_n=32, own_lag=2, fault_rank=1,
+                                  fault="absent", timeout_ms=200, raise_on_timeout=False)
+    assert st.timed_out and st.rank == 0

@@ -169,6 +169,14 @@ extern "C" int tccl_emul_gemm_allgather(int32_t world_size, int32_t M, int32_t N
   return kOk;
 }
 
+extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, int32_t N,
+                                               int32_t K_total, const float* A_all,
+                                               const float* B_all, float* C_all, int32_t block_m,
+                                               int32_t block_n, int32_t group_m_tiles,
+                                               int32_t own_lag, int32_t fault_rank,
+                                               int32_t fault_kind, int32_t fault_delay_ms,
+                                               int32_t timeout_ms, int32_t* status_out);
+
 // A_all: [ws][M][K/ws], B_all: [ws][K/ws][N], C_all: [ws][M/ws][N]
 extern "C" int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32_t N,
                                             int32_t K_total, const float* A_all,
@@ -177,6 +185,22 @@ extern "C" int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32
                                             int32_t fault_rank, int32_t fault_kind,
                                             int32_t fault_delay_ms, int32_t timeout_ms,
                                             int32_t* status_out) {
+  return tccl_emul_gemm_reducescatter_ex(world_size, M, N, K_total, A_all, B_all, C_all, block_m,
+                                         block_n, group_m_tiles, 0, fault_rank, fault_kind,
+                                         fault_delay_ms, timeout_ms, status_out);
+}
+
+// Same with the ranks' own tile rows trailing the remote rounds by `own_lag` rounds
+// (plan/tile_order.h): every rank is one thread that walks its tile order and blocks at its
+// own tiles, so this also exercises the schedule's freedom from deadlock.
+extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, int32_t N,
+                                               int32_t K_total, const float* A_all,
+                                               const float* B_all, float* C_all, int32_t block_m,
+                                               int32_t block_n, int32_t group_m_tiles,
+                                               int32_t own_lag, int32_t fault_rank,
+                                               int32_t fault_kind, int32_t fault_delay_ms,
+                                               int32_t timeout_ms, int32_t* status_out) {
+  TCCL_CHECK_ARG(own_lag >= 0, "own_lag must be >= 0");
   TCCL_CHECK_ARG(world_size >= 1 && world_size <= 64, "world_size must be 1..64");
   TCCL_CHECK_ARG(M > 0 && N > 0 && K_total > 0 && M % world_size == 0 && K_total % world_size == 0,
                  "bad problem shape");
@@ -199,7 +223,7 @@ extern "C" int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32
     const float* A = A_all + static_cast<int64_t>(rank) * M * kloc;
     const float* B = B_all + static_cast<int64_t>(rank) * kloc * N;
     float* C = C_all + static_cast<int64_t>(rank) * mloc * N;
-    const TileOrderShape shape{m_tiles, n_tiles, ws, rank, ws, 0};
+    const TileOrderShape shape{m_tiles, n_tiles, ws, rank, ws, 0, own_lag};
     std::vector<float> tile(static_cast<size_t>(block_m) * block_n);
     for (int t = 0; t < tile_order_count(shape); ++t) {
       const TileOrderEntry e = tile_order_decode(shape, t);

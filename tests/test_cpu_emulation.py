@@ -142,3 +142,33 @@ def test_reducescatter_with_lag_reports_a_missing_peer():
     _, st = em.gemm_reducescatter(A, B, block_m=16, block_n=32, own_lag=2, fault_rank=1,
                                   fault="absent", timeout_ms=200, raise_on_timeout=False)
     assert st.timed_out and st.rank == 0
+
+
+@pytest.mark.parametrize("ws,m_tiles,lag,delay", [(2, 1, 0, 2), (4, 2, 0, 3), (4, 4, 1, 2),
+                                                  (8, 2, 1, 4), (2, 6, 2, 2)])
+def test_late_signalling_needs_the_flush_before_an_owner_wait(ws, m_tiles, lag, delay):
+    """Signals held back while their data is in flight: with the flush before a blocking owner
+    wait the schedule completes; the smallest case shows that without it the ranks stop each
+    other (each holds exactly the signals its peer is waiting for)."""
+    torch.manual_seed(11)
+    bm, bn = 16, 32
+    M, N, K = ws * m_tiles * bm, 64, 4 * ws
+    A = [torch.randn(M, K // ws) for _ in range(ws)]
+    B = [torch.randn(K // ws, N) for _ in range(ws)]
+    outs, st = em.gemm_reducescatter(A, B, block_m=bm, block_n=bn, own_lag=lag,
+                                     signal_delay_tiles=delay, timeout_ms=5000)
+    assert st.ok
+    full = sum(a @ b for a, b in zip(A, B))
+    mloc = M // ws
+    for r in range(ws):
+        assert torch.allclose(outs[r], full[r * mloc:(r + 1) * mloc], atol=1e-4, rtol=1e-4)
+
+
+def test_late_signalling_without_the_flush_deadlocks():
+    torch.manual_seed(12)
+    A = [torch.randn(32, 4) for _ in range(2)]       # one tile row of two tiles per owner
+    B = [torch.randn(4, 64) for _ in range(2)]
+    _, st = em.gemm_reducescatter(A, B, block_m=16, block_n=32, signal_delay_tiles=2,
+                                  flush_before_wait=False, timeout_ms=300,
+                                  raise_on_timeout=False)
+    assert st.timed_out

@@ -192,7 +192,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_emul_gemm_reducescatter": [i32, i32, i32, i32, C.c_void_p, C.c_void_p, C.c_void_p, i32,
                                          i32, i32, i32, i32, i32, i32, C.POINTER(i32)],
         "tccl_emul_gemm_reducescatter_ex": [i32, i32, i32, i32, C.c_void_p, C.c_void_p, C.c_void_p, i32,
-                                            i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)],
+                                            i32, i32, i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32)],
         "tccl_preload_kernels": [],
         "tccl_plan_tile_order": [i32, i32, i32, i32, i32, i32, C.POINTER(i32), i32],
         "tccl_plan_tile_order_ex": [i32, i32, i32, i32, i32, i32, i32, C.POINTER(i32), i32],

@@ -225,8 +225,10 @@ int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32_t N, int32
 int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, int32_t N, int32_t K_total,
                                     const float* A_all, const float* B_all, float* C_all,
                                     int32_t block_m, int32_t block_n, int32_t group_m_tiles,
-                                    int32_t own_lag, int32_t fault_rank, int32_t fault_kind,
-                                    int32_t fault_delay_ms, int32_t timeout_ms, int32_t* status_out);
+                                    int32_t own_lag, int32_t signal_delay_tiles,
+                                    int32_t flush_before_wait, int32_t fault_rank,
+                                    int32_t fault_kind, int32_t fault_delay_ms, int32_t timeout_ms,
+                                    int32_t* status_out);
 // (owner, tile row, tile column) of every tile in one rank's visiting order.
 int tccl_plan_tile_order(int32_t m_tiles_local, int32_t n_tiles_local, int32_t owners, int32_t rank,
                          int32_t world_size, int32_t rot_m_tiles, int32_t* out, int32_t capacity);

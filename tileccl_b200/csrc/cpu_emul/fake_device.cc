@@ -13,8 +13,10 @@
 #include <atomic>
 #include <chrono>
 #include <cstring>
+#include <deque>
 #include <memory>
 #include <thread>
+#include <utility>
 #include <vector>
 
 #include "../api.h"
@@ -173,7 +175,8 @@ extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, in
                                                int32_t K_total, const float* A_all,
                                                const float* B_all, float* C_all, int32_t block_m,
                                                int32_t block_n, int32_t group_m_tiles,
-                                               int32_t own_lag, int32_t fault_rank,
+                                               int32_t own_lag, int32_t signal_delay_tiles,
+                                               int32_t flush_before_wait, int32_t fault_rank,
                                                int32_t fault_kind, int32_t fault_delay_ms,
                                                int32_t timeout_ms, int32_t* status_out);
 
@@ -186,21 +189,27 @@ extern "C" int tccl_emul_gemm_reducescatter(int32_t world_size, int32_t M, int32
                                             int32_t fault_delay_ms, int32_t timeout_ms,
                                             int32_t* status_out) {
   return tccl_emul_gemm_reducescatter_ex(world_size, M, N, K_total, A_all, B_all, C_all, block_m,
-                                         block_n, group_m_tiles, 0, fault_rank, fault_kind,
+                                         block_n, group_m_tiles, 0, 0, 1, fault_rank, fault_kind,
                                          fault_delay_ms, timeout_ms, status_out);
 }
 
 // Same with the ranks' own tile rows trailing the remote rounds by `own_lag` rounds
 // (plan/tile_order.h): every rank is one thread that walks its tile order and blocks at its
 // own tiles, so this also exercises the schedule's freedom from deadlock.
+// `signal_delay_tiles` models the kernel's late signalling: the signal of a tile is sent
+// only when that many later tiles have been finished (the data of a bulk store must have
+// landed first); `flush_before_wait` sends everything still held before a rank blocks at
+// one of its own tiles.  Without the flush, ranks that all hold the signals their peers are
+// waiting for stop each other.
 extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, int32_t N,
                                                int32_t K_total, const float* A_all,
                                                const float* B_all, float* C_all, int32_t block_m,
                                                int32_t block_n, int32_t group_m_tiles,
-                                               int32_t own_lag, int32_t fault_rank,
+                                               int32_t own_lag, int32_t signal_delay_tiles,
+                                               int32_t flush_before_wait, int32_t fault_rank,
                                                int32_t fault_kind, int32_t fault_delay_ms,
                                                int32_t timeout_ms, int32_t* status_out) {
-  TCCL_CHECK_ARG(own_lag >= 0, "own_lag must be >= 0");
+  TCCL_CHECK_ARG(own_lag >= 0 && signal_delay_tiles >= 0, "own_lag and signal_delay_tiles must be >= 0");
   TCCL_CHECK_ARG(world_size >= 1 && world_size <= 64, "world_size must be 1..64");
   TCCL_CHECK_ARG(M > 0 && N > 0 && K_total > 0 && M % world_size == 0 && K_total % world_size == 0,
                  "bad problem shape");
@@ -225,6 +234,15 @@ extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, in
     float* C = C_all + static_cast<int64_t>(rank) * mloc * N;
     const TileOrderShape shape{m_tiles, n_tiles, ws, rank, ws, 0, own_lag};
     std::vector<float> tile(static_cast<size_t>(block_m) * block_n);
+    // signals not sent yet: one entry per finished tile, (owner, group) or owner = -1 for none
+    std::deque<std::pair<int, int>> held;
+    auto release = [&](size_t keep) {
+      while (held.size() > keep) {
+        const auto s = held.front();
+        held.pop_front();
+        if (s.first >= 0) sig.at(s.first, 0, s.second).fetch_add(1, std::memory_order_release);
+      }
+    };
     for (int t = 0; t < tile_order_count(shape); ++t) {
       const TileOrderEntry e = tile_order_decode(shape, t);
       const int r0 = e.lm * block_m, c0 = e.ln * block_n;
@@ -240,12 +258,16 @@ extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, in
         bool signal = true;
         if (rank == fault_rank && fault_kind == kFaultNoSignal) signal = false;
         if (rank == fault_rank && fault_kind == kFaultShortSignal && (t & 1)) signal = false;
-        if (signal) sig.at(e.owner, 0, g).fetch_add(1, std::memory_order_release);
+        held.emplace_back(signal ? e.owner : -1, g);
+        release(static_cast<size_t>(signal_delay_tiles));
       } else {
         // own tile: wait for the peers' partials of this TileGroup, add them in rank order
         const int rows_in_group = imin(group_m_tiles, m_tiles - g * group_m_tiles);
         const uint32_t target = static_cast<uint32_t>((ws - 1) * rows_in_group * n_tiles);
         uint32_t seen = 0;
+        if (ws > 1 && flush_before_wait &&
+            sig.at(rank, 0, g).load(std::memory_order_acquire) < target)
+          release(0);
         if (ws > 1 && !wait_ge(sig.at(rank, 0, g), target, timeout_ms, &seen)) {
           status.report(2, 40, rank, g, target, seen);
           return;
@@ -260,8 +282,11 @@ extern "C" int tccl_emul_gemm_reducescatter_ex(int32_t world_size, int32_t M, in
         for (int i = 0; i < rows; ++i)
           std::memcpy(C + static_cast<int64_t>(r0 + i) * N + c0,
                       tile.data() + static_cast<int64_t>(i) * block_n, sizeof(float) * cols);
+        held.emplace_back(-1, g);
+        release(static_cast<size_t>(signal_delay_tiles));
       }
     }
+    release(0);
   };
   std::vector<std::thread> threads;
   for (int r = 0; r < ws; ++r) threads.emplace_back(body, r);

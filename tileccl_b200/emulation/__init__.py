@@ -84,12 +84,17 @@ def gemm_allgather(A_shards: Sequence[torch.Tensor], B_list: Sequence[torch.Tens
 def gemm_reducescatter(A_list: Sequence[torch.Tensor], B_list: Sequence[torch.Tensor], *,
                        block_m: int = 128, block_n: int = 256, group_m_tiles: int = 1,
                        fault_rank: int = -1, fault: str = "none", fault_delay_ms: int = 0,
-                       timeout_ms: int = 2000, raise_on_timeout: bool = True, own_lag: int = 0):
+                       timeout_ms: int = 2000, raise_on_timeout: bool = True, own_lag: int = 0,
+                       signal_delay_tiles: int = 0, flush_before_wait: bool = True):
     """Rank r holds ``A_list[r] (M, K/ws)`` and ``B_list[r] (K/ws, N)``; returns the list of
     ``C_r (M/ws, N) = sum_i (A_i @ B_i)[r*M/ws:(r+1)*M/ws]`` and the status.
 
     ``own_lag``: rounds by which every rank's own (reducing) tile rows trail its remote
-    rows (0 = own rows last), the schedule of the sm_100a kernel."""
+    rows (0 = own rows last), the schedule of the sm_100a kernel.  ``signal_delay_tiles``
+    holds every tile's signal back until that many later tiles are done (the kernel signals
+    only after a tile's bulk stores have landed); ``flush_before_wait`` sends all held
+    signals before a rank blocks at an own tile, which is what keeps that scheme from
+    deadlocking."""
     ws = len(A_list)
     M, kloc = A_list[0].shape
     N = B_list[0].shape[1]
@@ -97,8 +102,9 @@ def gemm_reducescatter(A_list: Sequence[torch.Tensor], B_list: Sequence[torch.Te
     out = torch.zeros(ws, M // ws, N, dtype=torch.float32)
     st = (C.c_int32 * 6)()
     _native.call("tccl_emul_gemm_reducescatter_ex", ws, M, N, kloc * ws, A.data_ptr(),
-                 B.data_ptr(), out.data_ptr(), block_m, block_n, group_m_tiles, own_lag, fault_rank,
-                 FAULTS[fault], fault_delay_ms, timeout_ms, st)
+                 B.data_ptr(), out.data_ptr(), block_m, block_n, group_m_tiles, own_lag,
+                 signal_delay_tiles, 1 if flush_before_wait else 0, fault_rank, FAULTS[fault],
+                 fault_delay_ms, timeout_ms, st)
     status = EmulationStatus(*[int(x) for x in st])
     if raise_on_timeout and not status.ok:
         raise EmulatedTimeout(status)

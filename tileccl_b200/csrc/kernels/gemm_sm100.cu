@@ -128,6 +128,11 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
 #ifndef TCCL_PAIR_EPI_BUFS
 #define TCCL_PAIR_EPI_BUFS 2
 #endif
+// Tiles by which a TileGroup signal trails the bulk stores it announces.
+#ifndef TCCL_SIGNAL_DELAY_TILES
+#define TCCL_SIGNAL_DELAY_TILES 2
+#endif
+static constexpr int kPend = TCCL_SIGNAL_DELAY_TILES;
 
 template <bool kPair>
 struct Geo {
@@ -573,10 +578,16 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     uint32_t acc = 0, acc_phase = 0;
     uint32_t buf = 0;
     bool ok = true;
-    // lane 0: the last two tiles whose signals have not been sent yet ([0] = older)
-    bool pend_valid[2] = {false, false};
+    // lane 0: the last kPend tiles whose signals have not been sent yet ([0] = oldest)
+    bool pend_valid[kPend] = {};
     bool slab_pending = false;   // lane 0: a slab whose completion the comm warps still await
-    int pend_owner[2] = {0, 0}, pend_group[2] = {0, 0};
+    int pend_owner[kPend] = {}, pend_group[kPend] = {};
+    auto any_pending = [&]() {
+      bool any = false;
+#pragma unroll
+      for (int i = 0; i < kPend; ++i) any = any || pend_valid[i];
+      return any;
+    };
     // One release-add per destination: "one more slab of TileGroup `g` from this rank has landed".
     auto send_signal = [&](int owner, int g, bool after_bulk) {
       const bool relaxed = after_bulk && (p.tuning & kTuneRelaxedSignalAfterBulk) != 0;
@@ -598,7 +609,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       const int group = c.lm / p.group_m_tiles;
       const bool reduce_here = p.mode == kModeReduceScatter && c.owner == p.rank;
 
-      if (reduce_here && p.world_size > 1 && lane == 0 && (pend_valid[0] || pend_valid[1]) &&
+      if (reduce_here && p.world_size > 1 && lane == 0 && any_pending() &&
           !mbar_try_wait(bar_acc_full + 8 * acc, acc_phase)) {
         // The accumulator of an own tile may be held up until the peers' partial tiles have
         // arrived (the producer warp waits for them).  Signals this warp still holds back
@@ -606,7 +617,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         // just as this rank waits for theirs, and holding them would close a cycle.
         tma_store_wait_all<0>();
         fence_proxy_async_all();
-        for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int i = 0; i < kPend; ++i) {
           if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
           pend_valid[i] = false;
         }
@@ -731,25 +743,28 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           slab_pending = true;
         }
       } else if (p.push_mode == kPushTma) {
-        // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent two
-        // tiles late: by then its bulk groups have completed (data has reached the peer)
+        // Peer copies are bulk stores issued by lane 0.  The signal of a tile is sent kPend
+        // (two) tiles late: by then its bulk groups have completed (data has reached the peer)
         // while the groups of the two most recent tiles are still in flight, so neither
         // the NVLink round trip nor the queueing behind other SMs' stores stalls this warp.
         if (lane == 0) {
           if (pend_valid[0]) {
-            if (n_chunks == 4) tma_store_wait_all<8>(); else tma_store_wait_all<4>();
+            if (n_chunks == 4) tma_store_wait_all<4 * kPend>(); else tma_store_wait_all<2 * kPend>();
             fence_proxy_async_all();
             if (p.trace != 0)
               reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 2] =
                   globaltimer_ns();
             send_signal(pend_owner[0], pend_group[0], true);
           }
-          pend_valid[0] = pend_valid[1];
-          pend_owner[0] = pend_owner[1];
-          pend_group[0] = pend_group[1];
-          pend_valid[1] = signals;
-          pend_owner[1] = c.owner;
-          pend_group[1] = group;
+#pragma unroll
+          for (int i = 0; i + 1 < kPend; ++i) {
+            pend_valid[i] = pend_valid[i + 1];
+            pend_owner[i] = pend_owner[i + 1];
+            pend_group[i] = pend_group[i + 1];
+          }
+          pend_valid[kPend - 1] = signals;
+          pend_owner[kPend - 1] = c.owner;
+          pend_group[kPend - 1] = group;
         }
       } else if (signals) {
         if (lane == 0) tma_store_wait_all<0>();   // the local bulk store
@@ -778,7 +793,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       fence_proxy_async_all();
       if (slab_pending)
         asm volatile("red.release.cta.shared.add.u32 [%0], 1;" ::"r"(done_count) : "memory");
-      for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int i = 0; i < kPend; ++i)
         if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
     }
   }

@@ -154,3 +154,25 @@ def test_timeline_schema_roundtrip(tmp_path):
         TimelineEvent("x", "l", 2.0, 1.0)
     with pytest.raises(ValueError):
         TimelineEvent("x", "l", 0.0, 1.0, source="")
+
+
+def test_runtime_config_snapshot_of_the_environment():
+    from tileccl_b200.utils import RuntimeConfig
+
+    cfg = RuntimeConfig.from_env({})
+    assert cfg.push_mode == "tma" and cfg.tuning == 1 and cfg.gemm_cta_pairs
+    assert cfg.rs_own_lag is None and cfg.wait_budget_us is None and not cfg.disable_nvls
+    cfg = RuntimeConfig.from_env({"TILECCL_PUSH_MODE": "Stores", "TILECCL_GEMM_2SM": "0",
+                                  "TILECCL_RS_OWN_LAG": "8", "TILECCL_WAIT_BUDGET_US": "2500",
+                                  "TILECCL_FORCE_NVLS": "1",
+                                  "TileCCL_FORCE_MULTIPROCESS_TRANSPORT": "vmm_fd"})
+    assert cfg.push_mode == "stores" and not cfg.gemm_cta_pairs and cfg.rs_own_lag == 8
+    assert cfg.wait_budget_us == 2500.0 and cfg.force_nvls
+    assert cfg.force_multiprocess_transport == "vmm_fd"
+    assert set(cfg.to_dict()) >= {"push_mode", "tuning", "calibration", "native_lib"}
+    import pytest
+
+    with pytest.raises(ValueError):
+        RuntimeConfig.from_env({"TILECCL_PUSH_MODE": "carrier-pigeon"})
+    with pytest.raises(Exception):
+        cfg.push_mode = "tma"            # frozen

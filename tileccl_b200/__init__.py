@@ -184,7 +184,14 @@ class TileCCLContext:
             "emulated_ranks": self.emulated,
             "heap": self.heap.metadata() if self.heap is not None else None,
             "topology": self.topology.to_dict() if self.topology is not None else None,
+            "config": _runtime_config_dict(),
         }
+
+
+def _runtime_config_dict() -> dict:
+    from .utils.config import RuntimeConfig
+
+    return RuntimeConfig.from_env().to_dict()
 
 
 def _normalize_size(size) -> tuple:

@@ -39,6 +39,13 @@ def _handle_info(args) -> int:
         print(f"native library: {_native.lib_path()} ({_native.version()})")
     except Exception as exc:
         print(f"native library: unavailable ({exc})")
+    try:
+        from tileccl_b200.utils.config import RuntimeConfig
+
+        cfg = RuntimeConfig.from_env().to_dict()
+        print("config: " + ", ".join(f"{k}={v}" for k, v in cfg.items()))
+    except ValueError as exc:
+        print(f"config: invalid environment ({exc})")
     hw = detect_hardware()
     print(f"hardware: {hw}")
     if hw != "cuda":

@@ -14,6 +14,7 @@ tileccl/ops.py:2378-2430).
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -63,8 +64,6 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
         # One multimem store reaches every peer: from three ranks on the shard leaves this
         # GPU once instead of ws - 1 times (the spare warps that push it are store-rate
         # bound).  With two ranks a multicast store also loops back to the sender.
-        import os
-
         use_multimem = (ws > 2 and ctx.heap.has_multicast
                         and os.environ.get("TILECCL_DISABLE_NVLS", "0") in ("", "0")) or (
             ws > 1 and ctx.heap.has_multicast

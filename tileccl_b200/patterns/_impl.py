@@ -2,7 +2,6 @@
 
 from __future__ import annotations
 
-from ..kernels import fused_gemm as fg
 from ..ops import _fused
 
 

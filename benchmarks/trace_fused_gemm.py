@@ -2,20 +2,24 @@
 """Per-tile timeline of the fused GEMM + collective kernel on real ranks.
 
 The kernel can stamp %globaltimer four times per tile and epilogue warp
-(accumulator ready / stores issued / older bulk stores complete / signalled).
-This script runs one all-gather shape and one reduce-scatter shape with the
-stamps on and prints, per phase, the median and mean time an epilogue warp
-spends in each section, plus when the CTAs finish: enough to see whether a run
-is bound by the tensor cores (long waits for the accumulator), by NVLink (long
-waits for bulk-store completion) or by signalling.
+(accumulator ready / stores issued / older bulk stores complete / signalled)
+and four times per CTA (kernel entry / roles start / incoming TileGroups seen /
+exit).  This script runs all-gather and reduce-scatter shapes with the stamps
+on, in the kernel form the operators use (CTA pairs), and prints where the time
+of one call goes: launch latency, the head before the first bulk store, the
+link-bound body, the tail after the last store, plus the median time an
+epilogue warp spends in each section.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
         benchmarks/trace_fused_gemm.py --ag 16384,4096,1024 --rs 16384,4096,2048
+
+Several shapes: separate them with ';'.  ``--one-cta`` traces the one-CTA form.
 """
 
 from __future__ import annotations
 
 import argparse
+import json
 import os
 import sys
 
@@ -26,16 +30,25 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
-def _write_timeline(path, label, plan, t, rank, max_ctas=16):
+def _slots_of_cta(plan, pair, b, n_slots):
+    """Trace slots (128-row tiles) that CTA `b` works on, in its visiting order."""
+    if pair:
+        pairs = plan.pair_grid // 2
+        return [2 * t + (b & 1) for t in range(b >> 1, n_slots // 2, pairs)]
+    return list(range(b, n_slots, plan.grid))
+
+
+def _write_timeline(path, label, plan, pair, t, rank, n_slots, max_ctas=16):
     """Device-clock timeline (one lane per CTA, epilogue warp 0): a span per tile from
     "accumulator ready" to "signalled", written with planning.runtime.TimelineRecorder."""
     from tileccl_b200.planning.runtime.timeline import TimelineRecorder
 
+    grid = plan.pair_grid if pair else plan.grid
     rec = TimelineRecorder(benchmark="trace_fused_gemm", path_name=label,
-                           metadata={"clock": "%globaltimer", "rank": rank, "grid": plan.grid})
+                           metadata={"clock": "%globaltimer", "rank": rank, "grid": grid})
     t0 = t[:, :, 0][t[:, :, 0] > 0].min()
-    for b in range(min(plan.grid, max_ctas)):
-        for i in range(b, t.shape[0], plan.grid):
+    for b in range(min(grid, max_ctas)):
+        for i in _slots_of_cta(plan, pair, b, n_slots):
             a, s3 = t[i, 0, 0], t[i, 0, 3]
             if a > 0 and s3 > 0:
                 rec.record_span(name=f"tile{i}", lane=f"cta{b}", start_ms=(a - t0) / 1e6,
@@ -44,49 +57,77 @@ def _write_timeline(path, label, plan, t, rank, max_ctas=16):
     rec.write_json(path)
 
 
-def _summary(label, plan, trace, tiles, ms, rank, timeline=None):
-    t = trace.cpu().numpy().astype(np.int64).reshape(tiles, 4, 4)
+def summarize(label, plan, pair, trace, ms, rank, timeline=None):
+    """Reduce one traced launch to a dict of microsecond figures (and print it on rank 0)."""
+    grid = plan.pair_grid if pair else plan.grid
+    raw = trace.cpu().numpy().astype(np.int64)
+    n_slots = (2 * ((plan.m_tiles_local + 1) // 2) * plan.n_tiles_local * plan.owners if pair
+               else plan.tiles_total)
+    t = raw[:n_slots * 16].reshape(n_slots, 4, 4)
+    cta = raw[n_slots * 16:n_slots * 16 + grid * 4].reshape(grid, 4)
     if timeline and rank == 0:
-        _write_timeline(timeline, label, plan, t, rank)
-    t0 = t[:, :, 0][t[:, :, 0] > 0].min()
-    rel = (t - t0) / 1e3
-    grid = plan.grid
+        _write_timeline(timeline, label, plan, pair, t, rank, n_slots)
+    entry0 = cta[:, 0][cta[:, 0] > 0].min()
+    rel = (t - entry0) / 1e3
+    rel[t == 0] = np.nan
+    crel = (cta - entry0) / 1e3
+    crel[cta == 0] = np.nan
     acc_wait, issue, compl, sig = [], [], [], []
     for b in range(grid):
         for w in range(4):
             prev = None
-            for i in range(b, tiles, grid):
+            for i in _slots_of_cta(plan, pair, b, n_slots):
                 a, s1, s2, s3 = rel[i, w]
+                if np.isnan(a):
+                    continue
                 if prev is not None:
                     acc_wait.append(a - prev)
                 issue.append(s1 - a)
-                if t[i, w, 2] > 0:
+                if not np.isnan(s2):
                     compl.append(s2 - s1)
                     sig.append(s3 - s2)
                 else:
                     sig.append(s3 - s1)
                 prev = s3
-    ends = np.array([rel[b::grid][:, :, 3].max() for b in range(grid)])
 
-    def mm(x):
-        return (float(np.median(x)), float(np.mean(x))) if len(x) else (-1.0, -1.0)
+    def med(x):
+        return round(float(np.median(x)), 2) if len(x) else None
 
+    out = {
+        "label": label, "event_us": round(ms * 1e3, 1), "grid": grid, "pair": pair,
+        "cta_entry_spread_us": round(float(np.nanmax(crel[:, 0])), 2),
+        "roles_start_us": round(float(np.nanmedian(crel[:, 1])), 2),
+        "first_acc_ready_us": round(float(np.nanmin(rel[:, :, 0])), 2),
+        "median_first_acc_ready_us": round(float(np.nanmedian(
+            [np.nanmin(rel[_slots_of_cta(plan, pair, b, n_slots)[:1], :, 0]) for b in range(grid)
+             if _slots_of_cta(plan, pair, b, n_slots)])), 2),
+        "last_acc_ready_us": round(float(np.nanmax(rel[:, :, 0])), 2),
+        "last_stores_issued_us": round(float(np.nanmax(rel[:, :, 1])), 2),
+        "last_signal_us": round(float(np.nanmax(rel[:, :, 3])), 2),
+        "incoming_seen_us": (round(float(np.nanmax(crel[:, 2])), 2)
+                             if not np.all(np.isnan(crel[:, 2])) else None),
+        "exit_us": round(float(np.nanmax(crel[:, 3])), 2),
+        "exit_min_us": round(float(np.nanmin(crel[:, 3])), 2),
+        "median_wait_acc_us": med(acc_wait), "median_issue_us": med(issue),
+        "median_wait_older_stores_us": med(compl), "median_signal_us": med(sig),
+    }
+    out["launch_overhead_us"] = round(out["event_us"] - out["exit_us"], 1)
     if rank == 0:
-        print(f"{label}: event time {ms * 1e3:.1f} us | last stamp {rel[:, :, 3].max():.1f} us | "
-              f"CTA end min/med/max {ends.min():.1f}/{np.median(ends):.1f}/{ends.max():.1f} us")
-        print("   per tile and epilogue warp, median/mean us: wait for accumulator %.2f/%.2f, "
-              "TMEM->smem->stores issued %.2f/%.2f, wait for older bulk stores %.2f/%.2f, "
-              "signal %.2f/%.2f" % (*mm(acc_wait), *mm(issue), *mm(compl), *mm(sig)), flush=True)
+        print(json.dumps(out), flush=True)
+    return out
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ag", default="16384,4096,1024", help="M,N,K of the GEMM + all-gather")
-    ap.add_argument("--rs", default="16384,4096,2048", help="M,N,K of the GEMM -> reduce-scatter")
+    ap.add_argument("--ag", default="16384,4096,1024", help="M,N,K of the GEMM + all-gather (';'-separated list)")
+    ap.add_argument("--rs", default="16384,4096,2048", help="M,N,K of the GEMM -> reduce-scatter (';'-separated list)")
     ap.add_argument("--iters", type=int, default=4)
+    ap.add_argument("--one-cta", action="store_true", help="trace the one-CTA form of the kernel")
     ap.add_argument("--timeline", default=None,
-                    help="write rank 0's per-CTA timeline of the all-gather run to this JSON file")
+                    help="write rank 0's per-CTA timeline of the first all-gather run to this JSON file")
     args = ap.parse_args()
+    if args.one_cta:
+        os.environ["TILECCL_GEMM_2SM"] = "0"
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -118,52 +159,63 @@ def main() -> None:
             torch.cuda.synchronize()
         return s.elapsed_time(e)
 
-    M, N, K = (int(x) for x in args.ag.split(","))
-    mloc = M // ws
-    A = (torch.randn(mloc, K, device=dev) / K ** 0.5).half()
-    B = torch.randn(K, N, device=dev).half()
-    C = ctx.zeros(M, N, dtype=torch.float16)
-    sig = ctx.zeros(ws * _fused.MAX_GROUPS, dtype=torch.int32)
-    m_tiles, n_tiles = -(-mloc // fg.BLOCK_M), -(-N // fg.BLOCK_N)
-    tiles = m_tiles * n_tiles
-    trace = torch.zeros(tiles * 16, dtype=torch.int64, device=dev)
-    region = rank * mloc * N * 2
-    plan = fg.FusedGemmPlan(fg.FusedGemmSpec(
-        mode=fg.MODE_PUSH_ALL, dtype=torch.float16, a_ptr=A.data_ptr(), a_rows=mloc, lda=K,
-        b_ptr=B.data_ptr(), b_cols=N, ldb=N, k=K, sub_m=mloc, sub_n=N,
-        out_ptrs=_fused._heap_offset_ptrs(ctx, C, region), ldo=N, out_rows=mloc, out_cols=N,
-        push_mode=_fused.default_push_mode(ctx), rank=rank, world_size=ws,
-        group_m_tiles=_fused.default_group_m_tiles(m_tiles), sig_local=sig.data_ptr(),
-        heap_stride=ctx.heap.stride, sig_stride=_fused.MAX_GROUPS, trace_ptr=trace.data_ptr(),
-        status_ptr=status))
-    ms = timed(plan, trace, wait_incoming=True)
-    _summary(f"GEMM+AG {M}x{N}x{K} ws={ws}", plan, trace, tiles, ms, rank, args.timeline)
-    dist.barrier()
+    def trace_buffer(m_tiles, n_tiles, owners):
+        words = 2 * ((m_tiles + 1) // 2) * n_tiles * owners * 16 + 4 * 1024
+        return torch.zeros(words, dtype=torch.int64, device=dev)
 
-    M, N, K = (int(x) for x in args.rs.split(","))
-    kloc, sub_m = K // ws, M // ws
-    A = (torch.randn(M, kloc, device=dev) / K ** 0.5).half()
-    B = torch.randn(kloc, N, device=dev).half()
-    C = torch.zeros(sub_m, N, device=dev, dtype=torch.float16)
-    sig = ctx.zeros(ws * _fused.MAX_GROUPS, dtype=torch.int32)
-    stage = ctx.zeros(2 * ws * sub_m * N, dtype=torch.float16)
-    dests = _fused._heap_offset_ptrs(ctx, stage)
-    dests[rank] = C.data_ptr()
-    m_tiles, n_tiles = -(-sub_m // fg.BLOCK_M), -(-N // fg.BLOCK_N)
-    tiles = m_tiles * n_tiles * ws
-    trace = torch.zeros(tiles * 16, dtype=torch.int64, device=dev)
-    lag = _fused.default_rs_own_lag(ws, m_tiles, n_tiles)
-    plan = fg.FusedGemmPlan(fg.FusedGemmSpec(
-        mode=fg.MODE_REDUCE_SCATTER, dtype=torch.float16, a_ptr=A.data_ptr(), a_rows=M, lda=kloc,
-        b_ptr=B.data_ptr(), b_cols=N, ldb=N, k=kloc, sub_m=sub_m, sub_n=N, out_ptrs=dests, ldo=N,
-        out_rows=sub_m, out_cols=N, push_mode=_fused.default_push_mode(ctx), rank=rank,
-        world_size=ws, split_axis=0, out_slot_elems=sub_m * N, out_slots=2 * ws,
-        group_m_tiles=_fused.default_group_m_tiles(m_tiles), sig_local=sig.data_ptr(),
-        heap_stride=ctx.heap.stride, sig_stride=_fused.MAX_GROUPS, stage_local=stage.data_ptr(),
-        rs_own_lag=lag, ident_ptr=fg.identity_operand(torch.float16, dev).data_ptr(),
-        trace_ptr=trace.data_ptr(), status_ptr=status))
-    ms = timed(plan, trace)
-    _summary(f"GEMM->RS {M}x{N}x{K} ws={ws} own_lag={lag}", plan, trace, tiles, ms, rank)
+    first = True
+    for shape in [s for s in args.ag.split(";") if s]:
+        M, N, K = (int(x) for x in shape.split(","))
+        mloc = M // ws
+        A = (torch.randn(mloc, K, device=dev) / K ** 0.5).half()
+        B = torch.randn(K, N, device=dev).half()
+        C = ctx.zeros(M, N, dtype=torch.float16)
+        sig = ctx.zeros(ws * _fused.MAX_GROUPS, dtype=torch.int32)
+        m_tiles, n_tiles = -(-mloc // fg.BLOCK_M), -(-N // fg.BLOCK_N)
+        trace = trace_buffer(m_tiles, n_tiles, 1)
+        region = rank * mloc * N * 2
+        plan = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_PUSH_ALL, dtype=torch.float16, a_ptr=A.data_ptr(), a_rows=mloc, lda=K,
+            b_ptr=B.data_ptr(), b_cols=N, ldb=N, k=K, sub_m=mloc, sub_n=N,
+            out_ptrs=_fused._heap_offset_ptrs(ctx, C, region), ldo=N, out_rows=mloc, out_cols=N,
+            push_mode=_fused.default_push_mode(ctx), rank=rank, world_size=ws,
+            group_m_tiles=_fused.default_group_m_tiles(m_tiles), sig_local=sig.data_ptr(),
+            heap_stride=ctx.heap.stride, sig_stride=_fused.MAX_GROUPS, trace_ptr=trace.data_ptr(),
+            status_ptr=status))
+        ms = timed(plan, trace, wait_incoming=True)
+        summarize(f"GEMM+AG {M}x{N}x{K} ws={ws}", plan, plan.pair_kernel, trace, ms, rank,
+                  args.timeline if first else None)
+        first = False
+        dist.barrier()
+        del plan
+
+    for shape in [s for s in args.rs.split(";") if s]:
+        M, N, K = (int(x) for x in shape.split(","))
+        kloc, sub_m = K // ws, M // ws
+        A = (torch.randn(M, kloc, device=dev) / K ** 0.5).half()
+        B = torch.randn(kloc, N, device=dev).half()
+        C = torch.zeros(sub_m, N, device=dev, dtype=torch.float16)
+        sig = ctx.zeros(ws * _fused.MAX_GROUPS, dtype=torch.int32)
+        stage = ctx.zeros(2 * ws * sub_m * N, dtype=torch.float16)
+        dests = _fused._heap_offset_ptrs(ctx, stage)
+        dests[rank] = C.data_ptr()
+        m_tiles, n_tiles = -(-sub_m // fg.BLOCK_M), -(-N // fg.BLOCK_N)
+        trace = trace_buffer(m_tiles, n_tiles, ws)
+        lag = _fused.default_rs_own_lag(ws, m_tiles, n_tiles)
+        plan = fg.FusedGemmPlan(fg.FusedGemmSpec(
+            mode=fg.MODE_REDUCE_SCATTER, dtype=torch.float16, a_ptr=A.data_ptr(), a_rows=M, lda=kloc,
+            b_ptr=B.data_ptr(), b_cols=N, ldb=N, k=kloc, sub_m=sub_m, sub_n=N, out_ptrs=dests, ldo=N,
+            out_rows=sub_m, out_cols=N, push_mode=_fused.default_push_mode(ctx), rank=rank,
+            world_size=ws, split_axis=0, out_slot_elems=sub_m * N, out_slots=2 * ws,
+            group_m_tiles=_fused.default_group_m_tiles(m_tiles), sig_local=sig.data_ptr(),
+            heap_stride=ctx.heap.stride, sig_stride=_fused.MAX_GROUPS, stage_local=stage.data_ptr(),
+            rs_own_lag=lag, ident_ptr=fg.identity_operand(torch.float16, dev).data_ptr(),
+            trace_ptr=trace.data_ptr(), status_ptr=status))
+        ms = timed(plan, trace)
+        summarize(f"GEMM->RS {M}x{N}x{K} ws={ws} own_lag={lag}", plan, plan.pair_kernel, trace, ms,
+                  rank)
+        dist.barrier()
+        del plan
     _fused.check_status(ctx)
     dist.barrier()
     ctx.heap.cleanup()

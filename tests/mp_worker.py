@@ -126,6 +126,14 @@ def main() -> int:
                 ops.scatter(x, sc, ctx=ctx, root=0)
                 check(f"scatter n{n}", sc, gather(x)[0][rank * (n // ws):(rank + 1) * (n // ws)], 1e-7)
                 dist.barrier()
+    # rooted collectives with the root changing from call to call
+    rb = ctx.zeros(8192, dtype=torch.float32)
+    for call, root in enumerate([0, 1, 0, ws - 1, 1]):
+        rb.fill_(float(10 * call + rank))
+        ops.broadcast(rb, ctx=ctx, root=root)
+        check(f"broadcast alternating root call {call}", rb,
+              torch.full_like(rb, float(10 * call + root)), 1e-7)
+    dist.barrier()
     coll.check_status(ctx.heap)
     os.environ["TILECCL_DISABLE_NVLS"] = "0"
     os.environ["TILECCL_FORCE_NVLS"] = "0"

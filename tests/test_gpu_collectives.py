@@ -70,6 +70,79 @@ def test_all_five_collectives(ctxs, dtype, numel):
         coll.check_status(c.heap)
 
 
+def test_rooted_collectives_with_alternating_roots(ctxs):
+    """broadcast / scatter accept any root on any call (every root has its own counters)."""
+    from tileccl_b200 import ops
+    from tileccl_b200.primitives import collectives as coll
+
+    ws = len(ctxs)
+    n = 4096 * ws
+    bufs = [c.zeros(n, dtype=torch.float32) for c in ctxs]
+    outs = [c.zeros(n // ws, dtype=torch.float32) for c in ctxs]
+    for call, root in enumerate([0, 1, 0, ws - 1, 1, 0]):
+        for r in range(ws):
+            bufs[r].fill_(float(100 * call + r))
+        for r, c in enumerate(ctxs):
+            ops.broadcast(bufs[r], ctx=c, root=root)
+        for r in range(ws):
+            assert float(bufs[r].min()) == float(bufs[r].max()) == float(100 * call + root), (call, r)
+        for r in range(ws):
+            bufs[r].copy_(torch.arange(n, device=bufs[r].device, dtype=torch.float32) + 1000 * r)
+        for r, c in enumerate(ctxs):
+            ops.scatter(bufs[r], outs[r], ctx=c, root=root)
+        for r in range(ws):
+            want = torch.arange(r * (n // ws), (r + 1) * (n // ws), dtype=torch.float32) + 1000 * root
+            assert torch.equal(outs[r].cpu(), want), (call, r)
+    for c in ctxs:
+        coll.check_status(c.heap)
+
+
+def test_reset_allocator_drops_internal_workspaces(ctxs):
+    """reset -> allocate -> all-reduce and fused op: library counters and staging are re-created
+    instead of aliasing the tensors allocated after the reset."""
+    from tileccl_b200 import ops
+
+    ws = len(ctxs)
+    xs = [c.randn(4096, dtype=torch.float32) for c in ctxs]
+    for x, c in zip(xs, ctxs):
+        ops.allreduce(x, ctx=c)                       # creates counters + one-shot staging
+    M, N, K = 256 * ws, 256, 128
+    A = [c.randn(M // ws, K, dtype=torch.float16) for c in ctxs]
+    B = [c.randn(K, N, dtype=torch.float16) for c in ctxs]
+    Cs = [c.zeros(M, N, dtype=torch.float16) for c in ctxs]
+    for r, c in enumerate(ctxs):
+        ops.gemm_allgather_rows(A[r], B[r], Cs[r], ctx=c)
+    for c in ctxs:
+        ops.check_status(c)
+    for c in ctxs:
+        c.barrier()
+    for c in ctxs:
+        c.heap.reset_allocator()
+    assert all(c.heap.bytes_allocated == 0 for c in ctxs)
+    # new user tensors now sit where the old counters / staging were; fill them with a pattern
+    guard = [c.empty(1 << 16, dtype=torch.int32) for c in ctxs]
+    for g in guard:
+        g.fill_(0x5A5A5A5A)
+    ys = [c.randn(4096, dtype=torch.float32) for c in ctxs]
+    want = sum(y.float().cpu() for y in ys)
+    for y, c in zip(ys, ctxs):
+        ops.allreduce(y, ctx=c)
+    for y in ys:
+        assert _rel(y.cpu(), want) < 1e-5
+    A = [c.randn(M // ws, K, dtype=torch.float16) for c in ctxs]
+    B = [c.randn(K, N, dtype=torch.float16) for c in ctxs]
+    Cs = [c.zeros(M, N, dtype=torch.float16) for c in ctxs]
+    for r, c in enumerate(ctxs):
+        ops.gemm_allgather_rows(A[r], B[r], Cs[r], ctx=c)
+    for c in ctxs:
+        ops.check_status(c)
+    ref = torch.cat([A[r].float().cpu() @ B[r].float().cpu() for r in range(ws)])
+    for r in range(ws):
+        assert _rel(Cs[r].cpu(), ref) < 2e-2
+    for g in guard:
+        assert int((g != 0x5A5A5A5A).sum()) == 0     # nothing of the library's wrote into user memory
+
+
 def test_allreduce_plan_metadata(ctxs):
     from tileccl_b200 import ops
 

@@ -37,7 +37,10 @@ def _noalloc_allreduce(fn, tensors):
 
 
 @pytest.mark.parametrize("dtype", list(DTYPES))
-@pytest.mark.parametrize("n_ranks,numel", [(2, 1000), (4, 4096), (8, 32768), (3, 72)])
+# 1001 / 1003 elements: byte counts that are no multiple of 16, so the scalar tail of both
+# phases (snapshot copy and per-element sum) runs too.
+@pytest.mark.parametrize("n_ranks,numel", [(2, 1000), (4, 4096), (8, 32768), (3, 72), (2, 1001),
+                                           (5, 1003)])
 def test_matches_heap_allreduce_two_calls_in_a_row(dtype, n_ranks, numel):
     import tileccl_b200 as tccl
     from tileccl_b200 import ops
@@ -83,6 +86,11 @@ def test_rejects_what_does_not_fit():
     nine = [torch.zeros(16, device="cuda", dtype=torch.float32) for _ in range(9)]
     assert _noalloc_allreduce(fn, nine) != 0
     assert b"n_ranks" in lib.tccl_last_error()
+    # an element count whose byte size wraps around 2**64 must be rejected, not run as empty
+    small = [torch.zeros(16, device="cuda", dtype=torch.float16) for _ in range(2)]
+    ptrs = (C.c_uint64 * 2)(*[t.data_ptr() for t in small])
+    assert fn(ptrs, 2, 0, 1 << 63, torch.cuda.current_stream().cuda_stream) != 0
+    assert b"exceeds the built-in scratch" in lib.tccl_last_error()
     ok = [torch.ones(256 * 1024 // 4, device="cuda", dtype=torch.float32) for _ in range(2)]
     assert _noalloc_allreduce(fn, ok) == 0            # exactly the maximum is accepted
     torch.cuda.synchronize()

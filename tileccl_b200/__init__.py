@@ -92,10 +92,23 @@ class TileCCLContext:
         self.device = str(heap.device)
         if getattr(heap, "local_group", None) is not None:
             self.local_group = heap.local_group
-        self._workspace_cache.clear()
-        self._state.clear()
+        self._drop_heap_state()
+        if hasattr(heap, "register_reset_hook"):
+            heap.register_reset_hook(self._drop_heap_state)
         _preload_kernels(heap.device)
         return self
+
+    def _drop_heap_state(self) -> None:
+        """Forget everything that points into the heap: named workspaces, the fused
+        operators' signal blocks / staging / native plans / epochs, cached collective
+        plans.  Runs when a heap is attached and when its allocator is reset."""
+        for st in self._state.get("ops", {}).values():
+            plan = st.get("plan") if isinstance(st, dict) else None
+            if plan is not None and hasattr(plan, "close"):
+                plan.close()
+        self._workspace_cache.clear()
+        self._state.clear()
+        self.__dict__.pop("_collective_plans", None)
 
     @property
     def torch_device(self):

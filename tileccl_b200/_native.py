@@ -142,6 +142,9 @@ class GemmPlanInfo(C.Structure):
         ("k_blocks", C.c_int32),
         ("smem_bytes", C.c_int32),
         ("push_grid", C.c_int32),
+        ("pair_kernel", C.c_int32),
+        ("pair_grid", C.c_int32),
+        ("trace_words", C.c_int64),
     ]
 
 
@@ -177,7 +180,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_heap_reset": [vp],
         "tccl_heap_bytes_allocated": [vp, C.POINTER(u64)],
         "tccl_collective_launch": [i32, i32, i32, i32, i32, i32, i32, i32, u32, u64, u64, u64, u64, u64,
-                                   u64, C.c_int64, u64, i32, u64, u64, u64],
+                                   u64, u64, C.c_int64, u64, i32, u64, u64, u64],
         "tccl_prim_test": [i32, i32, i32, i32, i32, u64, u64, u64, u64, u64, u64, u32, u32, u64, u64,
                            u64],
         "tccl_push_region": [u64, u64, C.c_int64, i32, i32, i32, i32, i32, C.c_int64, u64, u32, u64,

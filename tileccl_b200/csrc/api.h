@@ -113,7 +113,8 @@ typedef struct TcclGemmDesc {
   int32_t scatter_col_begin, scatter_col_end;
   int32_t grid;                  // 0 = one CTA per SM
   uint64_t status;               // uint32[8] in device memory, may be 0
-  uint64_t trace;                // uint64[tiles * 16] in device memory (4 stamps per epilogue warp), may be 0
+  uint64_t trace;                // uint64[TcclGemmPlanInfo::trace_words] in device memory, may be 0: 4 stamps per
+                                 // epilogue warp and 128-row tile, then 4 stamps per CTA
   uint64_t wait_budget_ns;       // 0 = default (2 s)
   int32_t tuning;                // bit 0: TileGroup signals after a completed bulk store are relaxed adds
   int32_t rs_own_lag;            // reduce-scatter: rounds by which the own (reducing) tile rows trail; 0 = all last
@@ -129,6 +130,9 @@ typedef struct TcclGemmPlanInfo {
   int32_t k_blocks;
   int32_t smem_bytes;
   int32_t push_grid;         // CTAs of a launch that performs the all-gather push
+  int32_t pair_kernel;       // 1: whole-order launches run the CTA-pair form
+  int32_t pair_grid;         // CTAs of such a launch
+  int64_t trace_words;       // uint64 words a trace buffer (TcclGemmDesc::trace) must hold
 } TcclGemmPlanInfo;
 
 int tccl_gemm_plan_create(const TcclGemmDesc* desc, void** plan_out);
@@ -172,11 +176,14 @@ int tccl_wait_groups(uint64_t sig, int32_t sig_stride, int32_t n_src, int32_t n_
 // op: 0 all-gather, 1 reduce-scatter, 2 all-reduce (two-shot), 3 all-reduce (one-shot),
 //     4 broadcast, 5 scatter.  dtype: 0 fp16, 1 bf16, 2 fp32, 3 raw bytes (copy ops only).
 // phase_mask: bit 0 announce, bit 1 move data, bit 2 wait for completion (7 = whole call).
+// staging / stage_slot (one-shot all-reduce): two parity halves, the second at
+// staging + stage_slot (0: directly behind the first, at the message size rounded to 16).
 // --------------------------------------------------------------------------
 int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
                            int32_t root, int32_t use_multimem, int32_t phase_mask, int32_t elem_size,
                            uint32_t epoch,
-                           uint64_t src, uint64_t dst, uint64_t staging, uint64_t counters,
+                           uint64_t src, uint64_t dst, uint64_t staging, uint64_t stage_slot,
+                           uint64_t counters,
                            uint64_t mc_base, uint64_t heap_base, int64_t heap_stride,
                            uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
                            uint64_t stream);

@@ -21,6 +21,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include "../api.h"
 #include "../device/ptx.cuh"
 #include "../device/tile_comm.cuh"
@@ -55,7 +57,8 @@ struct CollParams {
   uint32_t epoch;
   uint64_t src;        // local address (heap) of the input
   uint64_t dst;        // local address (heap) of the output (== src for in-place ops)
-  uint64_t staging;    // one-shot all-reduce: local staging, 2 parities x bytes
+  uint64_t staging;    // one-shot all-reduce: local staging, two parity halves
+  uint64_t stage_slot; // bytes between the halves (0: the message size rounded up to 16)
   uint64_t counters;   // local address of the counter block
   uint64_t mc_base;    // multicast alias of the heap (0 = none)
   uint64_t heap_base;  // this rank's heap base (to form multicast addresses)
@@ -402,7 +405,8 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const CollParams
   uint32_t* cta_done = counters + 16;
   const int ws = p.world_size;
   const uint64_t bytes = p.bytes;
-  const uint64_t slot = (bytes + 15) & ~static_cast<uint64_t>(15);
+  const uint64_t slot =
+      p.stage_slot != 0 ? p.stage_slot : (bytes + 15) & ~static_cast<uint64_t>(15);
   const uint64_t stage = p.staging + (p.epoch & 1u) * slot;
   const uint64_t n = bytes >> 4;
   const uint64_t gstride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
@@ -466,7 +470,7 @@ using namespace tileccl;
 extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
                                       int32_t root, int32_t use_multimem, int32_t phase_mask,
                                       int32_t elem_size, uint32_t epoch, uint64_t src, uint64_t dst, uint64_t staging,
-                                      uint64_t counters, uint64_t mc_base, uint64_t heap_base,
+                                      uint64_t stage_slot, uint64_t counters, uint64_t mc_base, uint64_t heap_base,
                                       int64_t heap_stride, uint64_t bytes, int32_t grid,
                                       uint64_t status, uint64_t budget_ns, uint64_t stream) {
   TCCL_CHECK_ARG(op >= kAllGather && op <= kScatter, "unknown collective");
@@ -486,12 +490,15 @@ extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, i
   p.op = op; p.dtype = dtype; p.rank = rank; p.world_size = world_size; p.root = root;
   p.use_multimem = use_multimem; p.phase_mask = phase_mask; p.epoch = epoch;
   p.elem_size = elem_size;
-  p.src = src; p.dst = dst; p.staging = staging; p.counters = counters; p.mc_base = mc_base;
+  p.src = src; p.dst = dst; p.staging = staging; p.stage_slot = stage_slot;
+  p.counters = counters; p.mc_base = mc_base;
   p.heap_base = heap_base; p.heap_stride = heap_stride; p.bytes = bytes; p.status = status;
   p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (op == kAllReduceOneShot) {
     TCCL_CHECK_ARG(staging != 0, "one-shot all-reduce needs a staging buffer");
+    TCCL_CHECK_ARG(stage_slot == 0 || (stage_slot % 16 == 0 && stage_slot >= bytes),
+                   "stage_slot must be a multiple of 16 and hold the message");
     allreduce_oneshot_kernel<<<grid, 512, 0, s>>>(p);
   } else {
     collective_kernel<<<grid, 512, 0, s>>>(p);
@@ -513,7 +520,10 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[TCCL_NOALLOC_SC
 
 namespace {
 constexpr int kNoAllocMaxDevices = 64;
-void* g_noalloc_scratch_ptr[kNoAllocMaxDevices] = {};
+// Device address of the array per device ordinal; filled on first use.  Atomic: two host
+// threads may make their first call on a device at the same time (both then resolve the
+// same address, which is harmless).
+std::atomic<void*> g_noalloc_scratch_ptr[kNoAllocMaxDevices];
 }  // namespace
 
 extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ranks, int32_t dtype,
@@ -524,8 +534,13 @@ extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ran
   TCCL_CHECK_ARG(dtype == kF16 || dtype == kBF16 || dtype == kF32,
                  "dtype must be 0 (fp16), 1 (bf16) or 2 (fp32)");
   const uint64_t elem = dtype == kF32 ? 4 : 2;
-  const uint64_t bytes = count * elem;
   TCCL_CHECK_ARG(count > 0, "count must be positive");
+  // Compare before multiplying: count * elem wraps for absurd counts.
+  TCCL_CHECK_ARG(count <= TCCL_NOALLOC_MAX_BYTES / elem,
+                 "message of " << count << " elements exceeds the built-in scratch ("
+                               << TCCL_NOALLOC_MAX_BYTES << " bytes per buffer); use the heap-based "
+                               << "all-reduce for larger messages");
+  const uint64_t bytes = count * elem;
   TCCL_CHECK_ARG(bytes <= TCCL_NOALLOC_MAX_BYTES,
                  "message of " << bytes << " bytes exceeds the built-in scratch ("
                                << TCCL_NOALLOC_MAX_BYTES << " bytes per buffer); use the heap-based "
@@ -536,14 +551,14 @@ extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ran
   int dev = 0;
   TCCL_CHECK_CUDA(cudaGetDevice(&dev));
   TCCL_CHECK_ARG(dev >= 0 && dev < kNoAllocMaxDevices, "device ordinal out of range");
-  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+  void* scratch_ptr = g_noalloc_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (scratch_ptr == nullptr) {
     // Once per device, with that device current: the device address of the array.
-    void* ptr = nullptr;
-    TCCL_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-    TCCL_CHECK_ARG(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
-    g_noalloc_scratch_ptr[dev] = ptr;
+    TCCL_CHECK_CUDA(cudaGetSymbolAddress(&scratch_ptr, g_noalloc_scratch));
+    TCCL_CHECK_ARG(scratch_ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    g_noalloc_scratch_ptr[dev].store(scratch_ptr, std::memory_order_release);
   }
-  const uint64_t scratch = reinterpret_cast<uint64_t>(g_noalloc_scratch_ptr[dev]);
+  const uint64_t scratch = reinterpret_cast<uint64_t>(scratch_ptr);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // The counters keep the previous call's values: they must start at zero.
   for (int r = 0; r < n_ranks; ++r)
@@ -563,6 +578,7 @@ extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ran
       p.epoch = 1;
       p.src = buffers[r]; p.dst = buffers[r];
       p.staging = scratch + r * uint64_t(TCCL_NOALLOC_RANK_BYTES);
+      p.stage_slot = TCCL_NOALLOC_MAX_BYTES;
       p.counters = p.staging + 2 * uint64_t(TCCL_NOALLOC_MAX_BYTES);
       p.mc_base = 0; p.heap_base = 0;
       p.heap_stride = TCCL_NOALLOC_RANK_BYTES;

@@ -222,17 +222,26 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   info.smem_bytes = kSmemTotal;
 
   // Launches that run the rank's whole tile order use CTA pairs (256 x 256 per pair, see
-  // gemm_sm100.cu); tile-range launches (emulated ranks, host-streamed operand), traced
-  // launches and explicit grids stay on the one-CTA form.
+  // gemm_sm100.cu); tile-range launches (emulated ranks, host-streamed operand) and
+  // explicit grids stay on the one-CTA form.
   const char* env = std::getenv("TILECCL_GEMM_2SM");
   const bool allowed = env == nullptr || env[0] != '0';
-  plan->pair_kernel = allowed && d.rot_m_tiles % 2 == 0 && d.trace == 0 && d.grid <= 0 && grid >= 2 &&
+  plan->pair_kernel = allowed && d.rot_m_tiles % 2 == 0 && d.grid <= 0 && grid >= 2 &&
                       grid % 2 == 0;
   if (plan->pair_kernel) {
     const int pair_tiles = ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
     const int pairs = grid / 2 < pair_tiles ? grid / 2 : pair_tiles;
     plan->pair_grid = 2 * pairs;
     plan->pair_push_grid = grid & ~1;
+  }
+  info.pair_kernel = plan->pair_kernel ? 1 : 0;
+  info.pair_grid = plan->pair_grid;
+  // uint64 words a trace buffer must hold: tile slots of the larger form + per-CTA stamps
+  {
+    const int64_t slots_one = info.tiles_total;
+    const int64_t slots_pair =
+        2ll * ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
+    info.trace_words = (slots_one > slots_pair ? slots_one : slots_pair) * 16 + 4ll * grid;
   }
   return kOk;
 }
@@ -284,11 +293,13 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   if (grid > tile_end - tile_begin) grid = tile_end - tile_begin;
   if (grid < 1) grid = 1;
   if (plan->pair_kernel && tile_begin == 0 && tile_end == total) {
+    p.trace_tile_slots = 2 * ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
     // (an all-gather-pushing launch has a fixed grid: the consumers count its CTAs)
     TCCL_CHECK_CUDA(launch_fused_gemm_pair(p, ag_push ? plan->pair_push_grid : plan->pair_grid,
                                            reinterpret_cast<cudaStream_t>(stream)));
     return kOk;
   }
+  p.trace_tile_slots = total;
   TCCL_CHECK_CUDA(launch_fused_gemm(p, grid, reinterpret_cast<cudaStream_t>(stream)));
   return kOk;
 }

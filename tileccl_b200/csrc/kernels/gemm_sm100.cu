@@ -156,6 +156,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   using G = Geo<kPair>;
   constexpr int kNS = G::kNumStages;
   extern __shared__ uint8_t smem_raw[];
+  const uint64_t t_entry = p.trace != 0 ? globaltimer_ns() : 0;
   // 128-byte swizzled tiles need 1024-byte aligned bases.
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t smem_epi = smem_base + G::kPipeBytes;
@@ -217,6 +218,17 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 
   WaitBudget wb;
   wb.start(p.wait_budget_ns, abort_flag);
+  // Trace layout: uint64[tile slots][4 epilogue warps][4] followed by uint64[CTAs][4]
+  // (kernel entry / roles start / epilogue or waiter done / exit).
+  uint64_t* const trace_tiles = reinterpret_cast<uint64_t*>(p.trace);
+  uint64_t* const trace_cta =
+      p.trace == 0 ? nullptr
+                   : trace_tiles + static_cast<int64_t>(p.trace_tile_slots) * (kEpiWarps * 4) +
+                         static_cast<int64_t>(blockIdx.x) * 4;
+  if (trace_cta != nullptr && threadIdx.x == 0) {
+    trace_cta[0] = t_entry;
+    trace_cta[1] = globaltimer_ns();
+  }
 
   // Tile iteration: 128-row tiles per CTA, or 256-row pair-tiles per CTA pair (the pair
   // form always runs the rank's whole tile order).
@@ -567,6 +579,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           break;
         }
       }
+      __syncwarp();
+      if (trace_cta != nullptr && lane == 0) trace_cta[2] = globaltimer_ns();
     }
   } else if (warp >= 4) {
     // -------------------------------- epilogue --------------------------------
@@ -631,7 +645,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
       tcgen05_fence_after();
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4] = globaltimer_ns();
+        trace_tiles[(static_cast<int64_t>(kPair ? 2 * t + cta : t) * kEpiWarps + q) * 4] = globaltimer_ns();
       const uint32_t t_acc = tmem_base + acc * kBN + (static_cast<uint32_t>(q * 32) << 16);
 
       for (int ch = 0; ch < n_chunks; ++ch) {
@@ -726,7 +740,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       if (!ok) break;
 
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 1] = globaltimer_ns();
+        trace_tiles[(static_cast<int64_t>(kPair ? 2 * t + cta : t) * kEpiWarps + q) * 4 + 1] = globaltimer_ns();
       // ---- TileGroup signalling: this slab of this tile is now on its way ----
       const bool signals = c.valid && p.world_size > 1 && p.sig_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter ||
@@ -752,7 +766,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
             if (n_chunks == 4) tma_store_wait_all<4 * kPend>(); else tma_store_wait_all<2 * kPend>();
             fence_proxy_async_all();
             if (p.trace != 0)
-              reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 2] =
+              trace_tiles[(static_cast<int64_t>(kPair ? 2 * t + cta : t) * kEpiWarps + q) * 4 + 2] =
                   globaltimer_ns();
             send_signal(pend_owner[0], pend_group[0], true);
           }
@@ -784,7 +798,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           red_release_sys_add(reinterpret_cast<uint32_t*>(p.sig_local) + group, 1u);
       }
       if (p.trace != 0 && lane == 0)
-        reinterpret_cast<uint64_t*>(p.trace)[(static_cast<int64_t>(t) * kEpiWarps + q) * 4 + 3] = globaltimer_ns();
+        trace_tiles[(static_cast<int64_t>(kPair ? 2 * t + cta : t) * kEpiWarps + q) * 4 + 3] = globaltimer_ns();
 
       if (++acc == kAccBufs) { acc = 0; acc_phase ^= 1u; }
     }
@@ -803,6 +817,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // touch its barriers; TMEM goes back only after every MMA and TMEM read is done.
   tcgen05_fence_before();
   __syncthreads();
+  if (trace_cta != nullptr && threadIdx.x == 0) trace_cta[3] = globaltimer_ns();
   if (kPair) cluster_sync_all();
   if (warp == 2) {
     tcgen05_fence_after();

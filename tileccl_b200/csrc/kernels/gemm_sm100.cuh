@@ -107,9 +107,12 @@ struct alignas(64) FusedGemmParams {
   // diagnostics
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;
-  // optional uint64[tiles][4 epilogue warps][4]:
-  // accumulator ready / stores issued / older stores complete / signalled
+  // optional uint64[trace_tile_slots][4 epilogue warps][4] (accumulator ready / stores
+  // issued / older stores complete / signalled) followed by uint64[CTAs][4] (kernel entry /
+  // roles start / incoming TileGroups seen / exit); a tile slot is a 128-row tile, in the
+  // CTA-pair form slot 2 * pair-tile + CTA
   uint64_t trace;
+  int32_t trace_tile_slots;
   int32_t tuning;                     // TuningBits
   int32_t rs_own_lag;                 // TileOrderShape::own_lag
 };

@@ -204,6 +204,9 @@ class FusedGemmPlan:
         self.k_blocks = info.k_blocks
         self.smem_bytes = info.smem_bytes
         self.push_grid = info.push_grid
+        self.pair_kernel = bool(info.pair_kernel)
+        self.pair_grid = info.pair_grid
+        self.trace_words = info.trace_words
 
     def launch(self, *, epoch: int = 1, a_gate_target: int = 0, tile_begin: int = 0,
                tile_end: int = -1, wait_incoming: bool = False, ag_push: bool = False,

@@ -154,6 +154,7 @@ class SymmetricHeap:
         self._group = _group
         self.local_group: Optional[LocalGroup] = None
         self._state: dict = {}
+        self._reset_hooks: list = []
         self._dirty = False  # True once reset_allocator() may have exposed used memory
         want_nvls = _want_nvls(nvls)
 
@@ -284,11 +285,32 @@ class SymmetricHeap:
 
     def reset_allocator(self) -> None:
         """Rewind the bump pointer.  Tensors handed out earlier become aliases; every
-        rank must have finished using them (call ``barrier()`` first)."""
+        rank must have finished using them (call ``barrier()`` first).
+
+        Collective: every rank resets at the same point of its program.  Everything the
+        library itself carved from the heap goes with the user tensors: the collectives'
+        counter blocks, staging areas and epochs kept here, and (through the reset hooks
+        that contexts register) the fused operators' signal blocks, staging, native plans
+        and workspaces.  They are re-created, zeroed, on next use, so a tensor allocated
+        after the reset can never alias a live counter.
+        """
         self._check_alive()
         _native.call("tccl_heap_reset", self._native.handle)
         self._ledger.reset()
         self._dirty = True
+        self._state.clear()
+        for ref in list(self._reset_hooks):
+            hook = ref()
+            if hook is None:
+                self._reset_hooks.remove(ref)
+            else:
+                hook()
+
+    def register_reset_hook(self, bound_method) -> None:
+        """Call ``bound_method()`` whenever ``reset_allocator`` runs (held weakly)."""
+        import weakref
+
+        self._reset_hooks.append(weakref.WeakMethod(bound_method))
 
     # ---------------------------------------------------------------- queries
     def get_heap_bases(self) -> torch.Tensor:

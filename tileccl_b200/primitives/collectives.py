@@ -159,8 +159,8 @@ def _run(heap, key, phases) -> None:
 
 
 def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbytes: int, *,
-            elem_size: int, root: int = 0, staging: int = 0, use_multimem: bool = False,
-            grid: Optional[int] = None, rv_extra=()) -> None:
+            elem_size: int, root: int = 0, staging: int = 0, stage_slot: int = 0,
+            use_multimem: bool = False, grid: Optional[int] = None, rv_extra=()) -> None:
     st = _counters(heap, kind)
     st["epoch"] += 1
     epoch = st["epoch"]
@@ -176,7 +176,7 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
         # of the current device (the heap's device).  This is the latency path: no closures,
         # no device switch.
         rc = st["fn"](op, dtype_code, heap.rank, heap.world_size, root, 1 if use_multimem else 0,
-                      7, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, counters,
+                      7, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, stage_slot, counters,
                       heap.multicast_base, heap.local_base, heap.stride, nbytes, grid, status,
                       st["budget_ns"], torch.cuda.current_stream().cuda_stream)
         if rc != 0:
@@ -188,7 +188,8 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
             with torch.cuda.device(heap.device):
                 _native.call(
                     "tccl_collective_launch", op, dtype_code, heap.rank, heap.world_size, root,
-                    1 if use_multimem else 0, mask, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, counters,
+                    1 if use_multimem else 0, mask, elem_size, epoch & 0xFFFFFFFF, src, dst, staging,
+                    stage_slot, counters,
                     heap.multicast_base, heap.local_base, heap.stride, nbytes, grid, status,
                     _budget_ns(), torch.cuda.current_stream().cuda_stream)
         return go
@@ -252,14 +253,16 @@ def allreduce(tensor: torch.Tensor, heap=None, op: str = "sum", *, ctx=None,
     code = _DTYPE_CODE[tensor.dtype]
     ptr = tensor.data_ptr()
     if ex.implementation == "device_one_shot":
-        slot = (nbytes + 15) // 16 * 16
-        stage_key = ("coll_stage", slot)
-        stage = heap._state.get(stage_key)
+        # One staging area (two parities of the largest one-shot message) and one counter
+        # block serve every message size: the parity halves sit at fixed offsets, so calls
+        # of different sizes alternate between them just like calls of one size.
+        stage = heap._state.get("coll_stage")
         if stage is None:
-            stage = heap.allocate_tensor((2 * slot,), torch.uint8)
-            heap._state[stage_key] = stage
-        _launch(heap, f"allreduce1:{slot}", OP_ALLREDUCE_ONE_SHOT, code, ptr, ptr, nbytes,
-                staging=stage.data_ptr(), grid=ex.grid_size, elem_size=tensor.element_size())
+            stage = heap.allocate_tensor((2 * ONE_SHOT_MAX_BYTES,), torch.uint8)
+            heap._state["coll_stage"] = stage
+        _launch(heap, "allreduce1", OP_ALLREDUCE_ONE_SHOT, code, ptr, ptr, nbytes,
+                staging=stage.data_ptr(), stage_slot=ONE_SHOT_MAX_BYTES, grid=ex.grid_size,
+                elem_size=tensor.element_size())
     else:
         _launch(heap, "allreduce2", OP_ALLREDUCE_TWO_SHOT, code, ptr, ptr, nbytes,
                 use_multimem=ex.use_multimem, grid=ex.grid_size, elem_size=tensor.element_size())
@@ -315,7 +318,9 @@ def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> to
     if heap.world_size == 1:
         return tensor
     nbytes = tensor.numel() * tensor.element_size()
-    _launch(heap, "broadcast", OP_BROADCAST, 3, tensor.data_ptr(), tensor.data_ptr(), nbytes,
+    # The rooted handshake only advances the counters between the root and the others, so
+    # every root has its own counter block and epoch (roots may alternate call by call).
+    _launch(heap, f"broadcast:{root}", OP_BROADCAST, 3, tensor.data_ptr(), tensor.data_ptr(), nbytes,
             root=root, use_multimem=_use_multimem(heap, nbytes), rv_extra=(root,),
             elem_size=tensor.element_size())
     return tensor
@@ -335,6 +340,6 @@ def scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, root: int 
     if heap.world_size == 1:
         output.view(-1).copy_(tensor.view(-1))
         return output
-    _launch(heap, "scatter", OP_SCATTER, 3, tensor.data_ptr(), output.data_ptr(), nbytes, root=root,
+    _launch(heap, f"scatter:{root}", OP_SCATTER, 3, tensor.data_ptr(), output.data_ptr(), nbytes, root=root,
             rv_extra=(root,), elem_size=tensor.element_size())
     return output

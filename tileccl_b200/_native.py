@@ -113,6 +113,8 @@ class GemmDesc(C.Structure):
         ("tuning", C.c_int32),
         ("rs_own_lag", C.c_int32),
         ("ident_ptr", C.c_uint64),
+        ("disable_cta_pairs", C.c_int32),
+        ("comm_ctas", C.c_int32),
     ]
 
 
@@ -154,7 +156,9 @@ _lib_lock = threading.Lock()
 
 def lib_path() -> Path:
     """The shared object to load; ``TILECCL_NATIVE_LIB`` names another build of it."""
-    override = os.environ.get("TILECCL_NATIVE_LIB")
+    from .utils.config import current
+
+    override = current().native_lib
     return Path(override) if override else _build.LIB_PATH
 
 
@@ -166,7 +170,8 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_gemm_plan_create": [C.POINTER(GemmDesc), C.POINTER(vp)],
         "tccl_gemm_plan_info": [vp, C.POINTER(GemmPlanInfo)],
         "tccl_gemm_plan_launch": [vp, u32, u32, i32, i32, i32, u64],
-        "tccl_gemm_plan_launch_streamed": [vp, u32, u32, i32, C.POINTER(StreamChunk), i32, u64, u64],
+        "tccl_gemm_plan_launch_streamed": [vp, u32, u32, i32, C.POINTER(StreamChunk), i32, u64, u64,
+                                           u64],
         "tccl_gemm_plan_destroy": [vp],
         "tccl_wait_groups": [u64, i32, i32, i32, u64, u32, i32, u64, u64, i32, u64],
         "tccl_device_count": [C.POINTER(i32)],
@@ -220,7 +225,9 @@ def load(build_if_missing: bool = True) -> C.CDLL:
             return _lib
         path = lib_path()
         if not path.exists():
-            if not build_if_missing or os.environ.get("TILECCL_NO_BUILD"):
+            from .utils.config import current
+
+            if not build_if_missing or current().no_build:
                 raise NativeError("load", -1, f"{path} is missing; run `python -m tileccl_b200._build`")
             _build.build()
         lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)

@@ -119,6 +119,8 @@ typedef struct TcclGemmDesc {
   int32_t tuning;                // bit 0: TileGroup signals after a completed bulk store are relaxed adds
   int32_t rs_own_lag;            // reduce-scatter: rounds by which the own (reducing) tile rows trail; 0 = all last
   uint64_t ident_ptr;            // reduce-scatter: 128 x 128 identity matrix of the operand dtype (row-major)
+  int32_t disable_cta_pairs;     // 1: whole-order launches also run the one-CTA form
+  int32_t comm_ctas;             // reserved (0)
 } TcclGemmDesc;
 
 typedef struct TcclGemmPlanInfo {
@@ -150,7 +152,8 @@ int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, in
 // readers of A); with flags bit 2 they only follow this plan's previous streamed call (the
 // caller promises that no other pending work on `stream` touches A), so the copy of one
 // problem overlaps the kernels of the previous one.  Bit 0 applies to the last run, bit 1 to
-// the first.
+// the first.  With `copy_stream2` != 0 the runs' copies alternate between the two copy
+// streams, so that the set-up of one copy hides under the transfer of the other.
 #define TCCL_STREAM_MAX_RANGES 64
 typedef struct TcclStreamChunk {
   int32_t tile_begin, tile_end;
@@ -162,7 +165,7 @@ typedef struct TcclStreamChunk {
 } TcclStreamChunk;
 int tccl_gemm_plan_launch_streamed(void* plan, uint32_t epoch, uint32_t a_gate_target,
                                    int32_t flags, const TcclStreamChunk* chunks, int32_t n_chunks,
-                                   uint64_t copy_stream, uint64_t stream);
+                                   uint64_t copy_stream, uint64_t copy_stream2, uint64_t stream);
 int tccl_gemm_plan_destroy(void* plan);
 
 // Consumer side of the TileGroup protocol as its own launch: waits until

@@ -29,7 +29,8 @@ static constexpr int kStatusWords = 8;
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  // "memory": the read must not move across barriers or the stores it brackets.
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)::"memory");
   return t;
 }
 

@@ -224,8 +224,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   // Launches that run the rank's whole tile order use CTA pairs (256 x 256 per pair, see
   // gemm_sm100.cu); tile-range launches (emulated ranks, host-streamed operand) and
   // explicit grids stay on the one-CTA form.
-  const char* env = std::getenv("TILECCL_GEMM_2SM");
-  const bool allowed = env == nullptr || env[0] != '0';
+  const bool allowed = d.disable_cta_pairs == 0;
   plan->pair_kernel = allowed && d.rot_m_tiles % 2 == 0 && d.grid <= 0 && grid >= 2 &&
                       grid % 2 == 0;
   if (plan->pair_kernel) {
@@ -307,12 +306,15 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
 extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint32_t a_gate_target,
                                               int32_t flags, const TcclStreamChunk* chunks,
                                               int32_t n_chunks, uint64_t copy_stream_,
-                                              uint64_t stream_) {
+                                              uint64_t copy_stream2_, uint64_t stream_) {
   TCCL_CHECK_ARG(plan_ != nullptr && chunks != nullptr && n_chunks >= 1, "bad argument");
   GemmPlan* plan = static_cast<GemmPlan*>(plan_);
-  cudaStream_t copy_stream = reinterpret_cast<cudaStream_t>(copy_stream_);
+  cudaStream_t copy_streams[2] = {reinterpret_cast<cudaStream_t>(copy_stream_),
+                                  reinterpret_cast<cudaStream_t>(copy_stream2_)};
+  const int n_copy_streams = copy_stream2_ != 0 && copy_stream2_ != copy_stream_ ? 2 : 1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  TCCL_CHECK_ARG(copy_stream != stream, "the copy stream must differ from the launch stream");
+  for (int c = 0; c < n_copy_streams; ++c)
+    TCCL_CHECK_ARG(copy_streams[c] != stream, "a copy stream must differ from the launch stream");
   while (static_cast<int>(plan->events.size()) < n_chunks + 1) {
     cudaEvent_t e;
     TCCL_CHECK_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
@@ -321,14 +323,17 @@ extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint3
   if ((flags & 4) != 0 && plan->streamed_before) {
     // The caller promises that nothing else pending on `stream` touches A: the copies only
     // have to follow this plan's own previous streamed call (its last launch read A).
-    TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->done_event, 0));
+    for (int c = 0; c < n_copy_streams; ++c)
+      TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_streams[c], plan->done_event, 0));
   } else {
     // Earlier work on `stream` may still read A: the copies wait for all of it.
     TCCL_CHECK_CUDA(cudaEventRecord(plan->events[n_chunks], stream));
-    TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_stream, plan->events[n_chunks], 0));
+    for (int c = 0; c < n_copy_streams; ++c)
+      TCCL_CHECK_CUDA(cudaStreamWaitEvent(copy_streams[c], plan->events[n_chunks], 0));
   }
   for (int i = 0; i < n_chunks; ++i) {
     const TcclStreamChunk& c = chunks[i];
+    cudaStream_t copy_stream = copy_streams[i % n_copy_streams];
     TCCL_CHECK_ARG(c.n_ranges >= 0 && c.n_ranges <= TCCL_STREAM_MAX_RANGES, "too many ranges");
     for (int r = 0; r < c.n_ranges; ++r)
       TCCL_CHECK_CUDA(cudaMemcpyAsync(reinterpret_cast<void*>(c.dst[r]),

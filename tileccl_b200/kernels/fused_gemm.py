@@ -9,13 +9,13 @@ dozen driver calls; launching it costs one kernel launch, so callers keep plans
 from __future__ import annotations
 
 import ctypes as C
-import os
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
 import torch
 
 from .. import _native
+from ..utils.config import current as _config
 
 MODE_GEMM = 0
 MODE_PUSH_ALL = 1
@@ -186,7 +186,9 @@ class FusedGemmPlan:
         d.trace = spec.trace_ptr
         d.rs_own_lag = spec.rs_own_lag
         d.ident_ptr = spec.ident_ptr
-        d.tuning = spec.tuning if spec.tuning >= 0 else int(os.environ.get("TILECCL_TUNING", "1"))
+        cfg = _config()
+        d.tuning = spec.tuning if spec.tuning >= 0 else cfg.tuning
+        d.disable_cta_pairs = 0 if cfg.gemm_cta_pairs else 1
         d.wait_budget_ns = spec.wait_budget_ns
         handle = C.c_void_p()
         _native.call("tccl_gemm_plan_create", C.byref(d), C.byref(handle))

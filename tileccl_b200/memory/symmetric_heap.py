@@ -203,7 +203,9 @@ class SymmetricHeap:
         box = [f"{os.getpid()}-{uuid.uuid4().hex[:12]}" if self._rank == 0 else None]
         dist.broadcast_object_list(box, src=0, group=self._group)
         job_id = str(box[0])
-        timeout_ms = int(os.environ.get("TILECCL_BOOTSTRAP_TIMEOUT_MS", "120000"))
+        from ..utils.config import current
+
+        timeout_ms = current().bootstrap_timeout_ms or 120000
         out = C.c_void_p()
         _native.call("tccl_heap_create_multiprocess", self._rank, self._world_size, self._size, dev,
                      job_id.encode(), 1 if want_nvls else 0, timeout_ms, C.byref(out))
@@ -588,4 +590,6 @@ class SymmetricHeap:
 def _want_nvls(flag: Optional[bool]) -> bool:
     if flag is not None:
         return bool(flag)
-    return os.environ.get("TILECCL_DISABLE_NVLS", "0") in ("", "0", "false", "False")
+    from ..utils.config import current
+
+    return current().nvls_allowed

@@ -18,13 +18,13 @@ staging), advances epochs, and decides how the launches of one call are ordered:
 from __future__ import annotations
 
 import ctypes as C
-import os
 from typing import Callable, Optional, Sequence
 
 import torch
 
 from .. import _native
 from ..kernels import fused_gemm as fg
+from ..utils.config import current as _config
 
 MAX_GROUPS = 64           # TileGroup counters per source rank in a signal block
 _DEFAULT_PUSH = {"stores": fg.PUSH_STORES, "tma": fg.PUSH_TMA, "multimem": fg.PUSH_MULTIMEM}
@@ -62,14 +62,13 @@ def check_status(ctx) -> None:
 
 
 def wait_budget_ns() -> int:
-    us = os.environ.get("TILECCL_WAIT_BUDGET_US")
-    return int(float(us) * 1000) if us else 0
+    return _config().wait_budget_ns
 
 
 def default_push_mode(ctx) -> int:
-    name = os.environ.get("TILECCL_PUSH_MODE", "").lower()
-    if name in _DEFAULT_PUSH:
-        mode = _DEFAULT_PUSH[name]
+    cfg = _config()
+    if cfg.push_mode_explicit:
+        mode = _DEFAULT_PUSH[cfg.push_mode]
         if mode == fg.PUSH_MULTIMEM and not (ctx.heap is not None and ctx.heap.has_multicast):
             raise RuntimeError("TILECCL_PUSH_MODE=multimem but no NVLS multicast mapping is bound")
         return mode
@@ -86,9 +85,9 @@ def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
     -> 0.174 / 0.166 / 0.154 / 0.161 ms): about 24 us of link time is the sweet spot.
     0 means "own rows last" (nothing to overlap, or too few rows).
     """
-    env = os.environ.get("TILECCL_RS_OWN_LAG")
+    env = _config().rs_own_lag
     if env is not None:
-        return max(0, int(env))
+        return max(0, env)
     if ws < 2 or m_tiles < 2:
         return 0
     round_bytes = (ws - 1) * n_tiles * fg.BLOCK_M * fg.BLOCK_N * 2
@@ -195,24 +194,37 @@ def visit_rows(m_tiles: int, owners: int, rank: int, world_size: int, own_lag: i
     return rows
 
 
-def _tile_row_chunks(plan, min_tiles: int = 2 * 148, max_chunks: int = 8) -> list:
+# Shares of the rank's tile rows given to successive runs of a host-streamed launch.  Few
+# runs keep the number of copies (each costs a gap on the copy engine) and launches low;
+# the falling sizes leave only a tenth of the math behind the last byte of the transfer.
+STREAM_RUN_SHARES = (0.40, 0.30, 0.20, 0.10)
+
+
+def _tile_row_chunks(plan, min_tiles: int = 148, shares: Sequence[float] = STREAM_RUN_SHARES) -> list:
     """Split the rank's tile order into runs of whole tile rows.
 
     Returns ``[(tile_begin, tile_end, [(row0, row1), ...]), ...]`` where the row
     ranges are the rows of A the run reads.  Runs follow the kernel's visiting
     order (rounds over the owners for reduce-scatter, see csrc/plan/tile_order.h),
     so the host copy of run i only has to stay ahead of the launch of run i.
+    Run sizes follow ``shares``; runs smaller than ``min_tiles`` tiles are merged
+    into their predecessor.
     """
     n_t = plan.n_tiles_local
     spec = plan.spec
     order = visit_rows(plan.m_tiles_local, plan.owners, spec.rank, spec.world_size,
                        getattr(spec, "rs_own_lag", 0))
     rows_total = len(order)
-    per_chunk = max(1, -(-min_tiles // n_t))
-    n_chunks = max(1, min(max_chunks, rows_total // per_chunk))
-    bounds = [round(i * rows_total / n_chunks) for i in range(n_chunks + 1)]
+    min_rows = max(1, -(-min_tiles // n_t))
+    bounds, acc = [0], 0.0
+    for share in shares[:-1]:
+        acc += share
+        b = min(rows_total, round(acc * rows_total))
+        if b - bounds[-1] >= min_rows and rows_total - b >= min_rows:
+            bounds.append(b)
+    bounds.append(rows_total)
     chunks = []
-    for i in range(n_chunks):
+    for i in range(len(bounds) - 1):
         r0, r1 = bounds[i], bounds[i + 1]
         if r1 <= r0:
             continue
@@ -264,6 +276,7 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
     st = op_state(ctx, ("h2d_stream",))
     if "stream" not in st:
         st["stream"] = torch.cuda.Stream(device=ctx.torch_device)
+        st["stream2"] = torch.cuda.Stream(device=ctx.torch_device)
     side, cur = st["stream"], torch.cuda.current_stream()
     key = (A.data_ptr(), a_host.data_ptr(), A.stride(0))
     prepared = getattr(plan, "_stream_chunks", None)
@@ -294,7 +307,9 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
                      launch_kw.get("a_gate_target", 0) & 0xFFFFFFFF,
                      (1 if wait_incoming else 0) | (2 if ag_push else 0)
                      | (4 if order == "plan" else 0), arr, len(chunks),
-                     side.cuda_stream, cur.cuda_stream)
+                     side.cuda_stream,
+                     st["stream2"].cuda_stream if _config().stream_copy_streams == 2 else 0,
+                     cur.cuda_stream)
         return
     side.wait_stream(cur)                       # earlier readers of A are done
     events = st.setdefault("events", [torch.cuda.Event() for _ in range(16)])

@@ -14,13 +14,13 @@ tileccl/ops.py:2378-2430).
 
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
 
 from ..kernels import fused_gemm as fg
 from ..ops import _fused
+from ..utils.config import current as _config
 
 
 def _gate_state(ctx, name: str) -> dict:
@@ -65,7 +65,7 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
         # GPU once instead of ws - 1 times (the spare warps that push it are store-rate
         # bound).  With two ranks a multicast store also loops back to the sender.
         use_multimem = (ws > 2 and ctx.heap.has_multicast
-                        and os.environ.get("TILECCL_DISABLE_NVLS", "0") in ("", "0")) or (
+                        and _config().nvls_allowed) or (
             ws > 1 and ctx.heap.has_multicast
             and _fused.default_push_mode(ctx) == fg.PUSH_MULTIMEM)
     key = ("ag_gemm", name, x_full.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, x_full.dtype,

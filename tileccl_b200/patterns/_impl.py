@@ -28,8 +28,8 @@ def run_two_kernel(ctx, name: str, A, B, C, spec, overlapped: bool) -> None:
 
 def pick_push_mode(ctx, preferred: int) -> int:
     """An explicit TILECCL_PUSH_MODE wins over the pattern's own choice."""
-    import os
+    from ..utils.config import current
 
-    if os.environ.get("TILECCL_PUSH_MODE"):
+    if current().push_mode_explicit:
         return _fused.default_push_mode(ctx)
     return preferred

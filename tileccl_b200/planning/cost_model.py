@@ -23,6 +23,12 @@ DTYPE_BYTES = {"float16": 2, "bfloat16": 2, "float32": 4, "float64": 8, "int8": 
                "fp16": 2, "bf16": 2, "fp32": 4}
 
 
+def _runtime_config():
+    from ..utils.config import current
+
+    return current()
+
+
 class Interconnect(Enum):
     PCIE_GEN4 = auto()
     PCIE_GEN5 = auto()
@@ -73,7 +79,7 @@ class HardwareProfile:
         shipped = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
             os.path.abspath(__file__)))), "calibration", "b200.json")
         for path, apply in ((peaks_path, _apply_peaks),
-                            (calibration_path or os.environ.get("TILECCL_CALIBRATION") or shipped,
+                            (calibration_path or _runtime_config().calibration or shipped,
                              _apply_calibration)):
             if path and os.path.exists(path):
                 try:

@@ -20,13 +20,13 @@ scatter         root pushes chunk r to rank r
 
 from __future__ import annotations
 
-import os
 from dataclasses import asdict, dataclass
 from typing import Optional
 
 import torch
 
 from .. import _native
+from ..utils.config import current as _config
 from ..kernels.fused_gemm import STATUS_WORDS, raise_on_status
 
 OP_ALLGATHER = 0
@@ -102,8 +102,7 @@ def check_status(heap) -> None:
 
 
 def _budget_ns() -> int:
-    us = os.environ.get("TILECCL_WAIT_BUDGET_US")
-    return int(float(us) * 1000) if us else 0
+    return _config().wait_budget_ns
 
 
 def _grid_for(nbytes: int, device: torch.device) -> int:
@@ -116,11 +115,12 @@ def _use_multimem(heap, nbytes: int) -> bool:
     to the sender through the switch and measures slower than plain peer stores
     (about 500 vs 700 GB/s), so the default is NVLS only from three ranks on;
     ``TILECCL_FORCE_NVLS=1`` uses it whenever it is bound, ``TILECCL_DISABLE_NVLS=1`` never."""
-    if not heap.has_multicast or os.environ.get("TILECCL_DISABLE_NVLS", "0") not in ("", "0"):
+    cfg = _config()
+    if not heap.has_multicast or cfg.disable_nvls:
         return False
     if nbytes % 16 != 0 or nbytes < 16:
         return False
-    if os.environ.get("TILECCL_FORCE_NVLS", "0") not in ("", "0"):
+    if cfg.force_nvls:
         return True
     return heap.world_size > 2
 

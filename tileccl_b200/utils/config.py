@@ -40,6 +40,10 @@ class RuntimeConfig:
     calibration: Optional[str] = None      # TILECCL_CALIBRATION: link-model JSON (default: calibration/b200.json)
     bootstrap_timeout_ms: Optional[int] = None  # TILECCL_BOOTSTRAP_TIMEOUT_MS
     native_lib: Optional[str] = None       # TILECCL_NATIVE_LIB: another build of the shared object
+    no_build: bool = False                 # TILECCL_NO_BUILD: never compile the shared object on import
+    stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
+    comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
+    push_mode_explicit: bool = False       # TILECCL_PUSH_MODE was set (it then overrides a pattern's own choice)
     # feature gates kept from the reference
     experimental_multiprocess_device_collectives: bool = False
     force_multiprocess_transport: Optional[str] = None
@@ -62,10 +66,32 @@ class RuntimeConfig:
             calibration=e.get("TILECCL_CALIBRATION") or None,
             bootstrap_timeout_ms=_opt_int(e, "TILECCL_BOOTSTRAP_TIMEOUT_MS"),
             native_lib=e.get("TILECCL_NATIVE_LIB") or None,
-            experimental_multiprocess_device_collectives=_flag(
-                e, "TileCCL_ENABLE_EXPERIMENTAL_MULTIPROCESS_DEVICE_COLLECTIVES"),
+            no_build=_flag(e, "TILECCL_NO_BUILD"),
+            stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
+            comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
+            push_mode_explicit=bool(e.get("TILECCL_PUSH_MODE")),
+            experimental_multiprocess_device_collectives=(
+                (e.get("TileCCL_ENABLE_EXPERIMENTAL_MULTIPROCESS_DEVICE_COLLECTIVES") or "")
+                .strip().lower() in ("1", "true", "yes", "on")),
             force_multiprocess_transport=e.get("TileCCL_FORCE_MULTIPROCESS_TRANSPORT") or None,
         )
 
     def to_dict(self) -> dict:
         return asdict(self)
+
+    @property
+    def wait_budget_ns(self) -> int:
+        """Budget of every device-side wait in nanoseconds; 0 = the kernels' default (2 s)."""
+        return int(self.wait_budget_us * 1000) if self.wait_budget_us else 0
+
+    @property
+    def nvls_allowed(self) -> bool:
+        return not self.disable_nvls
+
+
+def current() -> RuntimeConfig:
+    """The configuration in force right now.  Every module of the library that depends on an
+    environment switch asks here (nothing else reads ``TILECCL_*`` variables); the environment
+    is read afresh on every call, so a variable set mid-program takes effect at the next plan
+    or launch that consults it."""
+    return RuntimeConfig.from_env()

@@ -10,7 +10,6 @@ variable is accepted but not required.
 
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 _TRUTHY_VALUES = {"1", "true", "yes", "on"}
@@ -39,13 +38,16 @@ def multiprocess_device_collectives_enabled() -> bool:
 
 def multiprocess_device_collectives_requested() -> bool:
     """Whether the opt-in variable of the reference is set to a truthy value."""
-    value = os.environ.get(MULTIPROCESS_DEVICE_COLLECTIVES_ENV, "")
-    return value.strip().lower() in _TRUTHY_VALUES
+    from .config import current
+
+    return current().experimental_multiprocess_device_collectives
 
 
 def forced_multiprocess_transport() -> Optional[str]:
     """Transport forced through the environment, or ``None`` for automatic choice."""
-    raw = os.environ.get(FORCE_MULTIPROCESS_TRANSPORT_ENV)
+    from .config import current
+
+    raw = current().force_multiprocess_transport
     if raw is None or not raw.strip():
         return None
     value = raw.strip().lower()

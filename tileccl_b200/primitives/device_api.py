@@ -7,7 +7,10 @@ and are meant to be included by CUDA kernels.  This module keeps every name
 importable from Python (``from tileccl.primitives import tile_put``) and says
 where the implementation lives; calling one from the host raises.
 
-The host-callable test harness for them is :mod:`tileccl_b200.primitives.harness`.
+To use them, write a ``.cu`` kernel that includes the headers and build / launch it
+with :mod:`tileccl_b200.userkernel` (``examples/custom_kernel.cu`` shows one).  The
+host-callable test harness for single primitives is
+:mod:`tileccl_b200.primitives.harness`.
 """
 
 from __future__ import annotations
@@ -26,7 +29,8 @@ class DevicePrimitive:
     def __call__(self, *args, **kwargs):
         raise RuntimeError(
             f"{self.name} is a CUDA device function (csrc/device/{self.header}); include the header "
-            "in a kernel, or drive it from Python through tileccl_b200.primitives.harness")
+            "in a kernel (tileccl_b200.userkernel compiles and launches one), or drive it from "
+            "Python through tileccl_b200.primitives.harness")
 
     def __repr__(self) -> str:
         return f"<device primitive {self.name} ({self.header})>"
@@ -125,12 +129,27 @@ tile_release_credit = _p("tile_release_credit", _SYNC, "void tile_release_credit
 tile_barrier = _p("tile_barrier", _SYNC, "bool tile_barrier(w, counter, epoch, const WaitBudget&)",
                   "All-ranks barrier on a counter that only grows.")
 # ---- collectives as device building blocks -------------------------------------
-_COLL = "../kernels/collectives.cu"
-tile_allreduce = _p("tile_allreduce", _COLL, "collective_kernel (op 2) / allreduce_oneshot_kernel", "All-reduce (sum).")
-tile_allgather = _p("tile_allgather", _COLL, "collective_kernel (op 0)", "All-gather.")
-tile_scatter = _p("tile_scatter", _COLL, "collective_kernel (op 5)", "Scatter from a root.")
-tile_reduce_scatter = _p("tile_reduce_scatter", _COLL, "collective_kernel (op 1)", "Reduce-scatter (sum).")
-tile_broadcast = _p("tile_broadcast", _COLL, "collective_kernel (op 4)", "Broadcast from a root.")
+_COLL = "tile_collectives.cuh"
+tile_allreduce = _p("tile_allreduce", _COLL,
+                    "bool tile_allreduce(w, sym_buf, bytes, dtype, use_mc, const TileCollSync&, const WaitBudget&)",
+                    "In-place sum over all ranks: announce, wait, pull-sum-push own share, publish, wait "
+                    "(data phase alone: tile_allreduce_chunk).")
+tile_allgather = _p("tile_allgather", _COLL,
+                    "void tile_allgather(w, src, sym_dst, bytes, elem_size, use_mc, TileCoop) / "
+                    "bool tile_allgather(..., const TileCollSync&, const WaitBudget&)",
+                    "Own chunk into slot `rank` of every rank's output (multimem.st with NVLS).")
+tile_scatter = _p("tile_scatter", _COLL,
+                  "void tile_scatter(w, src, sym_dst, bytes, root, elem_size, TileCoop) / "
+                  "bool tile_scatter(..., const TileCollSync&, const WaitBudget&)",
+                  "Root pushes chunk r to rank r.")
+tile_reduce_scatter = _p("tile_reduce_scatter", _COLL,
+                         "void tile_reduce_scatter(w, sym_src, dst, bytes, dtype, use_mc, TileCoop) / "
+                         "bool tile_reduce_scatter(..., const TileCollSync&, const WaitBudget&)",
+                         "Sum of chunk `rank` over all ranks into a local buffer (multimem.ld_reduce with NVLS).")
+tile_broadcast = _p("tile_broadcast", _COLL,
+                    "void tile_broadcast(w, sym_buf, bytes, root, elem_size, use_mc, TileCoop) / "
+                    "bool tile_broadcast(..., const TileCollSync&, const WaitBudget&)",
+                    "Root's buffer into the same place of every other rank's heap.")
 
 MEMORY = ["tile_load", "tile_store", "tile_copy", "make_block_offsets"]
 COMMUNICATION = ["translate_ptr", "remote_load", "remote_store", "tile_remote_load",

@@ -31,6 +31,32 @@ def run(heap, op: str, *, peer: int = 0, a: int = 0, b: int = 0, nbytes: int = 0
     return [x & 0xFFFFFFFF for x in result.tolist()]
 
 
+def run_concurrent(calls) -> list:
+    """Launch one primitive per entry of ``calls`` (``(heap, op, kwargs)``), all before the
+    first synchronise, and return each launch's result words.  For primitives whose ranks
+    wait for one another (``barrier``): only on heaps whose ranks own different GPUs, since
+    launches that share a GPU must never wait on each other."""
+    devs = [h.device for h, _, _ in calls]
+    if len({str(d) for d in devs}) != len(devs):
+        raise ValueError("run_concurrent needs every rank on its own GPU")
+    results = []
+    for heap, op, kw in calls:
+        kw = dict(kw)
+        budget_us = kw.pop("budget_us", 1e6)
+        result = torch.zeros(4, dtype=torch.int32, device=heap.device)
+        results.append(result)
+        with torch.cuda.device(heap.device):
+            _native.call("tccl_prim_test", OPS[op], kw.get("sub_op", 0), heap.rank, heap.world_size,
+                         kw.get("peer", 0), heap.window_base, heap.stride, heap.multicast_base,
+                         kw.get("a", 0), kw.get("b", 0), kw.get("nbytes", 0),
+                         kw.get("value", 0) & 0xFFFFFFFF, kw.get("value2", 0) & 0xFFFFFFFF,
+                         result.data_ptr(), int(budget_us * 1000),
+                         torch.cuda.current_stream().cuda_stream)
+    for d in devs:
+        torch.cuda.synchronize(d)
+    return [[x & 0xFFFFFFFF for x in r.tolist()] for r in results]
+
+
 def translate(heap, ptr: int, to_rank: int) -> int:
     words = run(heap, "translate", peer=to_rank, a=ptr)
     return words[0] | (words[1] << 32)

@@ -154,6 +154,29 @@ def test_timeline_schema_roundtrip(tmp_path):
         TimelineEvent("x", "l", 2.0, 1.0)
     with pytest.raises(ValueError):
         TimelineEvent("x", "l", 0.0, 1.0, source="")
+    rec.render_svg(tmp_path / "timeline.svg")
+    svg = (tmp_path / "timeline.svg").read_text()
+    assert svg.startswith("<svg") and svg.count("<rect") >= 1 + 3 + 1      # background, lanes, one span
+    assert "rank1/tiles" in svg and "time (ms)" in svg
+
+
+def test_only_the_config_module_reads_library_environment_variables():
+    """Every TILECCL_* / TileCCL_* switch is read in utils/config.py and nowhere else."""
+    import pathlib
+    import re
+
+    import tileccl_b200
+
+    root = pathlib.Path(tileccl_b200.__file__).parent
+    pat = re.compile(r"(environ|getenv)[^\n]*(TILECCL_|TileCCL_)")
+    offenders = []
+    for path in list(root.rglob("*.py")) + list(root.rglob("*.cc")) + list(root.rglob("*.cu")):
+        if path.name == "config.py" and path.parent.name == "utils":
+            continue
+        for i, line in enumerate(path.read_text().splitlines(), 1):
+            if pat.search(line):
+                offenders.append(f"{path.relative_to(root)}:{i}")
+    assert not offenders, offenders
 
 
 def test_runtime_config_snapshot_of_the_environment():

@@ -97,25 +97,54 @@ def bench_gemm(quick: bool = False) -> dict:
 
 
 def bench_p2p(world_size: int = 0, quick: bool = False) -> dict:
-    """Peer put / get bandwidth through the symmetric heap (device kernels, rank 0 <-> rank 1)."""
+    """Point-to-point primitives between rank 0 and rank 1 through the symmetric heap:
+    ``translate_ptr`` (one launch of pointer arithmetic), small ``tile_put`` / ``tile_get``
+    latency (one CTA, device time of one launch) and grid-wide put / get bandwidth.
+    Counterpart of the reference's translate / put / get benchmark behind ``tileccl bench p2p``
+    (tileccl/cli.py:212)."""
     torch = _torch()
-    ctxs = _contexts(world_size or min(2, torch.cuda.device_count()), 1 << 30)
+    from tileccl_b200 import _native
+    from tileccl_b200.primitives import harness
+    from tileccl_b200.utils.profiling import device_time_ms
+
+    ctxs = _contexts(world_size or min(2, max(2, torch.cuda.device_count())), 1 << 30)
     try:
         rows = []
-        if len(ctxs) < 2:
-            return {"suite": "p2p", "rows": [], "note": "needs two ranks"}
-        from tileccl_b200.primitives import collectives
+        h0 = ctxs[0].heap
+        dev0 = ctxs[0].torch_device
+        shared_gpu = len({str(c.torch_device) for c in ctxs[:2]}) < 2
+        small = [c.zeros(2048, dtype=torch.float32) for c in ctxs]
+        result = torch.zeros(4, dtype=torch.int32, device=dev0)
 
-        sizes = [1 << 20, 64 << 20] if quick else [64 << 10, 1 << 20, 16 << 20, 256 << 20]
-        for nbytes in sizes:
-            src = [c.zeros(nbytes // 2, dtype=torch.float16) for c in ctxs]
-            dst = [c.zeros(nbytes // 2, dtype=torch.float16) for c in ctxs]
-            ms = _time_group(ctxs, lambda r: collectives.broadcast(src[r], ctxs[r].heap, root=0),
-                             warmup=3, iters=10)
-            rows.append({"name": f"broadcast_root0_{nbytes}B", "ms": ms,
-                         "gbps": nbytes / ms / 1e6})
-            del src, dst
-        return {"suite": "p2p", "world_size": len(ctxs), "rows": rows, "timestamp": time.time()}
+        def prim(op, nbytes):
+            _native.call("tccl_prim_test", harness.OPS[op], 0, 0, h0.world_size, 1, h0.window_base,
+                         h0.stride, 0, small[0].data_ptr(), small[0].data_ptr(), nbytes, 0, 0,
+                         result.data_ptr(), 10 ** 9, torch.cuda.current_stream().cuda_stream)
+
+        with torch.cuda.device(dev0):
+            for op, nbytes in (("translate", 0), ("put", 16), ("put", 8192), ("get", 16),
+                               ("get", 8192)):
+                ms = device_time_ms(lambda: prim(op, nbytes), warmup=5, iters=50)
+                rows.append({"name": f"{op}_{nbytes}B_one_cta", "us": ms * 1e3})
+            sizes = [16 << 20] if quick else [1 << 20, 16 << 20, 256 << 20]
+            sms = torch.cuda.get_device_properties(dev0).multi_processor_count
+            for nbytes in sizes:
+                src = ctxs[0].zeros(nbytes // 4, dtype=torch.float32)
+                for c in ctxs[1:]:
+                    c.zeros(nbytes // 4, dtype=torch.float32)        # same offset on every rank
+                for direction, name in ((0, "put"), (1, "get")):
+                    grid = max(1, min(2 * sms, nbytes // 16 // 512 // 8))
+                    ms = device_time_ms(
+                        lambda: _native.call("tccl_p2p_copy", direction, 0, h0.world_size, 1,
+                                             h0.window_base, h0.stride, src.data_ptr(),
+                                             src.data_ptr(), nbytes, grid,
+                                             torch.cuda.current_stream().cuda_stream),
+                        warmup=3, iters=10, flush_l2_bytes=_FLUSH_BYTES)
+                    rows.append({"name": f"{name}_{nbytes}B_grid{grid}", "ms": ms,
+                                 "gbps": nbytes / ms / 1e6})
+        return {"suite": "p2p", "world_size": len(ctxs), "rows": rows, "timestamp": time.time(),
+                "note": ("both ranks share one GPU: the numbers are local-memory figures"
+                         if shared_gpu else "rank 0 and rank 1 on different GPUs")}
     finally:
         _cleanup(ctxs)
 

@@ -255,6 +255,12 @@ int tccl_plan_tile_order_ex(int32_t m_tiles_local, int32_t n_tiles_local, int32_
 // 11 credit (sub_op 0 acquire, 1 release), 12 try_wait, 13 translate,
 // 14 put_mc, 15 get_reduce.  `result` is uint32[4] in device memory.
 // --------------------------------------------------------------------------
+// Grid-wide point-to-point copy with the tile_put / tile_get accessors: direction 0 puts the
+// local `a` into `peer`'s `b`, direction 1 gets `peer`'s `a` into the local `b` (symmetric
+// addresses are given as addresses in the caller's heap).
+int tccl_p2p_copy(int32_t direction, int32_t rank, int32_t world_size, int32_t peer,
+                  uint64_t window_base, uint64_t stride, uint64_t a, uint64_t b, uint64_t bytes,
+                  int32_t grid, uint64_t stream);
 int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t world_size, int32_t peer,
                    uint64_t window_base, uint64_t stride, uint64_t mc_base, uint64_t a, uint64_t b,
                    uint64_t n, uint32_t value, uint32_t value2, uint64_t result, uint64_t budget_ns,

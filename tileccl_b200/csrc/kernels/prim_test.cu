@@ -5,8 +5,7 @@
 #include <cuda_runtime.h>
 
 #include "../api.h"
-#include "../device/tile_comm.cuh"
-#include "../device/tile_sync.cuh"
+#include "../device/tile_collectives.cuh"
 #include "../runtime/errors.h"
 
 namespace tileccl {
@@ -112,9 +111,53 @@ __global__ void prim_test_kernel(const PrimArgs x) {
   }
 }
 
+// Grid-wide put (local a -> peer's b) or get (peer's a -> local b) of a large buffer with
+// the same 16-byte accessors as tile_put / tile_get: the bandwidth side of the
+// point-to-point benchmark.
+__global__ void __launch_bounds__(512) p2p_copy_kernel(SymmWindow w, int direction, int peer,
+                                                       uint64_t a, uint64_t b, uint64_t bytes) {
+  const TileCoop grid = tile_coop_grid();
+  if (direction == 0) {
+    char* dst = translate_ptr(w, reinterpret_cast<char*>(b), w.rank, peer);
+    coll_detail::copy_vec(dst, reinterpret_cast<const char*>(a), bytes, 16, grid);
+  } else {
+    const char* src = translate_ptr(w, reinterpret_cast<char*>(a), w.rank, peer);
+    char* dst = reinterpret_cast<char*>(b);
+    const uint64_t n = bytes >> 4;
+    constexpr int kU = 8;
+    uint64_t i = grid.tid;
+    for (; i + (kU - 1) * grid.nthreads < n; i += kU * grid.nthreads) {
+      uint4 v[kU];
+#pragma unroll
+      for (int j = 0; j < kU; ++j) v[j] = ld_remote_v4(src + ((i + j * grid.nthreads) << 4));
+#pragma unroll
+      for (int j = 0; j < kU; ++j)
+        *reinterpret_cast<uint4*>(dst + ((i + j * grid.nthreads) << 4)) = v[j];
+    }
+    for (; i < n; i += grid.nthreads)
+      *reinterpret_cast<uint4*>(dst + (i << 4)) = ld_remote_v4(src + (i << 4));
+  }
+}
+
 }  // namespace tileccl
 
 using namespace tileccl;
+
+extern "C" int tccl_p2p_copy(int32_t direction, int32_t rank, int32_t world_size, int32_t peer,
+                             uint64_t window_base, uint64_t stride, uint64_t a, uint64_t b,
+                             uint64_t bytes, int32_t grid, uint64_t stream) {
+  TCCL_CHECK_ARG(direction == 0 || direction == 1, "direction must be 0 (put) or 1 (get)");
+  TCCL_CHECK_ARG(rank >= 0 && rank < world_size && peer >= 0 && peer < world_size, "bad rank/peer");
+  TCCL_CHECK_ARG(a % 16 == 0 && b % 16 == 0 && bytes % 16 == 0,
+                 "buffers and size must be multiples of 16 bytes");
+  TCCL_CHECK_ARG(grid >= 1, "grid must be >= 1");
+  SymmWindow w;
+  w.base = window_base; w.stride = stride; w.mc_base = 0; w.rank = rank; w.world_size = world_size;
+  p2p_copy_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(w, direction, peer, a, b,
+                                                                             bytes);
+  TCCL_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
 
 extern "C" int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t world_size,
                               int32_t peer, uint64_t window_base, uint64_t stride, uint64_t mc_base,
@@ -142,6 +185,8 @@ extern "C" int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t 
 namespace tileccl {
 cudaError_t preload_prim_kernels() {
   cudaFuncAttributes a;
-  return cudaFuncGetAttributes(&a, prim_test_kernel);
+  cudaError_t e = cudaFuncGetAttributes(&a, prim_test_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, p2p_copy_kernel);
+  return e;
 }
 }  // namespace tileccl

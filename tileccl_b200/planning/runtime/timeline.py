@@ -17,9 +17,12 @@ from typing import Any, Iterable, Mapping, Optional, Sequence
 
 SCHEMA = "tileccl.timeline.v1"
 
+# Colours of the categories this library's own traces use; anything else gets a hue
+# derived from the category name (see _colour_of).
 _CATEGORY_COLORS = {
-    "producer": "#4c78a8", "ingress": "#b279a2", "frontier": "#f58518", "compute": "#54a24b",
-    "aggregation": "#e45756", "marker": "#333333", "span": "#72b7b2", "comm": "#b279a2",
+    "compute": "#2e7d32", "mma": "#1b5e20", "epilogue": "#1565c0", "push": "#ef6c00",
+    "comm": "#ef6c00", "wait": "#9e9e9e", "signal": "#6a1b9a", "copy": "#00838f",
+    "marker": "#212121", "span": "#546e7a",
 }
 
 
@@ -146,6 +149,12 @@ class TimelineRecorder:
                             title=title or f"{self.benchmark}: {self.path_name}",
                             lane_order=lane_order)
 
+    def render_svg(self, path, *, title: Optional[str] = None,
+                   lane_order: Optional[Sequence[str]] = None) -> None:
+        render_timeline_svg(self._events, Path(path),
+                            title=title or f"{self.benchmark}: {self.path_name}",
+                            lane_order=lane_order)
+
 
 def events_from_device_trace(done_ns: Sequence[int], *, lane: str, rank: Optional[int] = None,
                              start_ns: Optional[int] = None, name: str = "tile",
@@ -162,39 +171,119 @@ def events_from_device_trace(done_ns: Sequence[int], *, lane: str, rank: Optiona
             for i, t in stamps]
 
 
-def render_timeline_png(events: Sequence[TimelineEvent], path: Path, *, title: str,
-                        lane_order: Optional[Sequence[str]] = None) -> None:
-    """Lane diagram (matplotlib, Agg backend: no display needed)."""
-    if not events:
-        raise ValueError("Cannot render an empty timeline")
-    try:
-        import matplotlib
-
-        matplotlib.use("Agg")
-        import matplotlib.pyplot as plt
-    except ImportError as exc:  # pragma: no cover - depends on the environment
-        raise RuntimeError("matplotlib is not installed; write_json() is the portable artefact") from exc
+def _lanes_of(events: Sequence[TimelineEvent], lane_order: Optional[Sequence[str]]) -> list:
     lanes = list(lane_order) if lane_order is not None else []
     for ev in events:
         if ev.lane not in lanes:
             lanes.append(ev.lane)
-    ypos = {lane: len(lanes) - i for i, lane in enumerate(lanes)}
-    fig, ax = plt.subplots(figsize=(12, max(2.8, 0.55 * len(lanes) + 1.6)))
+    return lanes
+
+
+def _colour_of(ev: TimelineEvent) -> str:
+    if ev.color:
+        return ev.color
+    known = _CATEGORY_COLORS.get(ev.category)
+    if known:
+        return known
+    # categories without an entry get a stable hue derived from their name
+    hue = sum(ord(ch) * (i + 7) for i, ch in enumerate(ev.category)) % 360
+    return f"hsl({hue}, 55%, 48%)"
+
+
+def render_timeline_svg(events: Sequence[TimelineEvent], path: Path, *, title: str,
+                        lane_order: Optional[Sequence[str]] = None, width: int = 1200) -> None:
+    """Lane diagram as a stand-alone SVG file, written with nothing but the standard library
+    (one row per lane, one rectangle per span, one tick per marker, a time axis in ms)."""
+    if not events:
+        raise ValueError("Cannot render an empty timeline")
+    from xml.sax.saxutils import escape
+
+    lanes = _lanes_of(events, lane_order)
+    t0 = min(ev.start_ms for ev in events)
+    t1 = max(ev.end_ms for ev in events)
+    span = max(t1 - t0, 1e-9)
+    label_w = 12 + 7 * max(len(lane) for lane in lanes)
+    row_h, top, bottom = 26, 44, 40
+    plot_w = max(200, width - label_w - 24)
+    height = top + row_h * len(lanes) + bottom
+
+    def x_of(t_ms: float) -> float:
+        return label_w + (t_ms - t0) / span * plot_w
+
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" '
+           f'font-family="monospace" font-size="11">',
+           f'<rect width="{width}" height="{height}" fill="white"/>',
+           f'<text x="{label_w}" y="20" font-size="14">{escape(title)}</text>']
+    for i, lane in enumerate(lanes):
+        y = top + i * row_h
+        shade = "#f4f4f4" if i % 2 == 0 else "#ffffff"
+        out.append(f'<rect x="{label_w}" y="{y}" width="{plot_w}" height="{row_h}" fill="{shade}"/>')
+        out.append(f'<text x="{label_w - 6}" y="{y + row_h * 0.65:.1f}" text-anchor="end">'
+                   f'{escape(lane)}</text>')
+    row = {lane: i for i, lane in enumerate(lanes)}
     for ev in events:
-        y = ypos[ev.lane]
-        color = ev.color or _CATEGORY_COLORS.get(ev.category, "#72b7b2")
-        if ev.duration_ms == 0:
-            ax.vlines(ev.start_ms, y - 0.25, y + 0.25, color=color, linewidth=1.2)
+        y = top + row[ev.lane] * row_h
+        colour = _colour_of(ev)
+        tip = f"{ev.name} [{ev.category}] {ev.start_ms:.4f}-{ev.end_ms:.4f} ms"
+        if ev.end_ms > ev.start_ms:
+            w_px = max(0.5, x_of(ev.end_ms) - x_of(ev.start_ms))
+            out.append(f'<rect x="{x_of(ev.start_ms):.2f}" y="{y + 4}" width="{w_px:.2f}" '
+                       f'height="{row_h - 8}" fill="{colour}"><title>{escape(tip)}</title></rect>')
         else:
-            ax.barh(y, ev.duration_ms, left=ev.start_ms, height=0.5, color=color, alpha=0.9)
+            x = x_of(ev.start_ms)
+            out.append(f'<line x1="{x:.2f}" x2="{x:.2f}" y1="{y + 2}" y2="{y + row_h - 2}" '
+                       f'stroke="{colour}" stroke-width="1.5"><title>{escape(tip)}</title></line>')
         if ev.label:
-            ax.text(ev.start_ms + ev.duration_ms / 2, y + 0.3, ev.label, fontsize=7, ha="center")
-    ax.set_yticks([ypos[lane] for lane in lanes])
-    ax.set_yticklabels(lanes)
-    ax.set_xlabel("time (ms)")
-    ax.set_title(title)
-    ax.grid(axis="x", alpha=0.3)
+            out.append(f'<text x="{x_of((ev.start_ms + ev.end_ms) / 2):.2f}" y="{y + 3}" '
+                       f'text-anchor="middle" font-size="9">{escape(ev.label)}</text>')
+    axis_y = top + row_h * len(lanes)
+    for k in range(11):
+        t = t0 + span * k / 10
+        x = x_of(t)
+        out.append(f'<line x1="{x:.2f}" x2="{x:.2f}" y1="{top}" y2="{axis_y + 4}" stroke="#bbbbbb" '
+                   f'stroke-width="0.5"/>')
+        out.append(f'<text x="{x:.2f}" y="{axis_y + 18}" text-anchor="middle">{t:.3f}</text>')
+    out.append(f'<text x="{label_w + plot_w / 2:.1f}" y="{axis_y + 34}" text-anchor="middle">'
+               f'time (ms)</text></svg>')
+    path = Path(path)
     path.parent.mkdir(parents=True, exist_ok=True)
-    fig.tight_layout()
-    fig.savefig(path, dpi=130)
-    plt.close(fig)
+    path.write_text("\n".join(out), encoding="utf-8")
+
+
+def render_timeline_png(events: Sequence[TimelineEvent], path: Path, *, title: str,
+                        lane_order: Optional[Sequence[str]] = None) -> None:
+    """Raster version of :func:`render_timeline_svg` for callers that ask for a PNG (needs
+    matplotlib, headless Agg canvas).  Spans of one lane and colour are drawn as one
+    ``broken_barh`` collection, markers as one event plot per lane."""
+    if not events:
+        raise ValueError("Cannot render an empty timeline")
+    try:
+        from matplotlib.backends.backend_agg import FigureCanvasAgg
+        from matplotlib.figure import Figure
+    except ImportError as exc:  # pragma: no cover - depends on the environment
+        raise RuntimeError("matplotlib is not installed; write_json() and render_svg() need "
+                           "nothing beyond the standard library") from exc
+    lanes = _lanes_of(events, lane_order)
+    fig = Figure(figsize=(11.5, 1.2 + 0.4 * len(lanes)), dpi=120)
+    FigureCanvasAgg(fig)
+    ax = fig.add_subplot(111)
+    for row, lane in enumerate(lanes):
+        mine = [ev for ev in events if ev.lane == lane]
+        by_colour: dict = {}
+        for ev in mine:
+            if ev.end_ms > ev.start_ms:
+                by_colour.setdefault(_colour_of(ev), []).append((ev.start_ms, ev.end_ms - ev.start_ms))
+        for colour, spans in by_colour.items():
+            ax.broken_barh(spans, (row - 0.35, 0.7), facecolors=colour if not colour.startswith("hsl")
+                           else "#5f9ea0")
+        ticks = [ev.start_ms for ev in mine if ev.end_ms == ev.start_ms]
+        if ticks:
+            ax.eventplot(ticks, lineoffsets=row, linelengths=0.7, colors="black", linewidths=0.8)
+    ax.set_ylim(len(lanes) - 0.5, -0.5)          # first lane on top
+    ax.set_yticks(range(len(lanes)), labels=lanes)
+    ax.set_xlabel("time (ms)")
+    ax.set_title(title, loc="left")
+    ax.grid(True, axis="x", linewidth=0.3)
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    fig.savefig(path, bbox_inches="tight")

@@ -123,6 +123,9 @@ def main() -> None:
     ap.add_argument("--rs", default="16384,4096,2048", help="M,N,K of the GEMM -> reduce-scatter (';'-separated list)")
     ap.add_argument("--iters", type=int, default=4)
     ap.add_argument("--one-cta", action="store_true", help="trace the one-CTA form of the kernel")
+    ap.add_argument("--steady", action="store_true",
+                    help="launch the iterations back to back (flush, launch, flush, launch ...) "
+                         "without a barrier in between, as a training loop would, and trace the last")
     ap.add_argument("--timeline", default=None,
                     help="write rank 0's per-CTA timeline of the first all-gather run to this JSON file")
     args = ap.parse_args()
@@ -143,6 +146,19 @@ def main() -> None:
 
     def timed(plan, trace, **kw):
         ep = 0
+        if args.steady:
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.synchronize()
+            for _ in range(max(args.iters, 2)):
+                ep += 1
+                flush.zero_()
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                plan.launch(epoch=ep, **kw)
+                e.record()
+            torch.cuda.synchronize()
+            return s.elapsed_time(e)
         for _ in range(args.iters):
             ep += 1
             flush.zero_()

@@ -99,6 +99,56 @@ def main() -> int:
           torch.cat([A4s[r].float() @ B4s[r].float() for r in range(ws)]), 5e-3)
     dist.barrier()
 
+    # Entry handshake: back-to-back all-gathers into the same C with a slow consumer on
+    # rank 0 in between.  The peers' second call must not overwrite rank 0's C before rank 0
+    # has entered that call itself, i.e. before its consumer (sleep + snapshot) has run.
+    M, N, K = 512 * ws, 1024, 256
+    mloc = M // ws
+    Ae = ctx.randn(mloc, K, dtype=torch.float16)
+    Ae.mul_(K ** -0.5)
+    Be = ctx.randn(K, N, dtype=torch.float16)
+    Ce = ctx.zeros(M, N, dtype=torch.float16)
+    snap = torch.empty_like(Ce)
+    for rep in range(3):
+        Ae.copy_(torch.full_like(Ae, 0.01 * (rep + 1)))       # call 1 data
+        _fused.push_all(ctx, "t_entry", Ae, Be, Ce, region_row0=rank * mloc, region_col0=0)
+        want1 = torch.cat([t.float() @ b.float() for t, b in zip(gather(Ae), gather(Be))])
+        if rank == 0:
+            torch.cuda._sleep(20_000_000)                      # ~10 ms: the slow consumer
+        snap.copy_(Ce)
+        Ae.copy_(torch.full_like(Ae, -0.02 * (rep + 1)))       # call 2 data
+        _fused.push_all(ctx, "t_entry", Ae, Be, Ce, region_row0=rank * mloc, region_col0=0)
+        ops.check_status(ctx)
+        check(f"entry handshake: consumer of call 1 (rep {rep})", snap, want1, 5e-3)
+        want2 = torch.cat([t.float() @ b.float() for t, b in zip(gather(Ae), gather(Be))])
+        check(f"entry handshake: call 2 (rep {rep})", Ce, want2, 5e-3)
+        dist.barrier()
+
+    # tile_barrier across processes, and the two NVLS verbs when a multicast mapping is bound
+    from tileccl_b200.primitives import harness
+
+    bar = ctx.heap.allocate_signal_buffer(8)
+    dist.barrier()
+    for epoch in (1, 2, 3):
+        res = harness.run(ctx.heap, "barrier", a=bar.data_ptr(), value=epoch, budget_us=2e6)
+        assert res[0] == 1 and int(bar[0]) == epoch * ws, (res, bar.tolist())
+    if ctx.heap.has_multicast:
+        src = ctx.zeros(2048, dtype=torch.float32)
+        dst = ctx.zeros(2048, dtype=torch.float32)
+        src.copy_(torch.arange(2048, dtype=torch.float32, device=dev) * (rank + 1))
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == ws - 1:       # one multicast store per 16 bytes lands the tile on every rank
+            harness.run(ctx.heap, "put_mc", a=src.data_ptr(), b=dst.data_ptr(), nbytes=8192)
+        torch.cuda.synchronize()
+        dist.barrier()
+        check("tile_put_mc", dst, torch.arange(2048, dtype=torch.float32, device=dev) * ws, 1e-7)
+        dist.barrier()
+        harness.run(ctx.heap, "get_reduce", a=src.data_ptr(), b=dst.data_ptr(), nbytes=8192, sub_op=2)
+        check("tile_get_reduce", dst,
+              torch.arange(2048, dtype=torch.float32, device=dev) * sum(range(1, ws + 1)), 1e-6)
+        dist.barrier()
+
     for nvls_off in ("1", "0"):
         os.environ["TILECCL_DISABLE_NVLS"] = nvls_off
         os.environ["TILECCL_FORCE_NVLS"] = "1"       # also at two ranks

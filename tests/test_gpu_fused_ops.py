@@ -181,3 +181,51 @@ def test_contract_errors(ctxs):
         ops.gemm_reducescatter(a, b, c.zeros(128, 128 // ws, dtype=torch.float16), ctx=c, implementation="reference")
     with pytest.raises(ValueError):
         ops.gemm_allscatter(a, b, c.zeros(128, 128, dtype=torch.float16), ctx=c, pattern="telepathy")
+
+
+def test_fused_kernel_abort_path_then_normal_call(ctxs, monkeypatch):
+    """The owner phase of a reduce-scatter launched with no producer before it: the producer
+    warp's wait for the peers' TileGroups runs out (site 40), every role of the kernel winds
+    down (loads drained, MMAs committed, TMEM freed) and the launch returns.  The same
+    context then runs a normal call."""
+    from tileccl_b200 import ops
+    from tileccl_b200.kernels.fused_gemm import TileCCLTimeoutError
+    from tileccl_b200.ops import _fused
+
+    ws, dtype = len(ctxs), torch.float16
+    if not ctxs[0].emulated:
+        pytest.skip("phase-split launches exist for ranks that share a GPU")
+    monkeypatch.setenv("TILECCL_WAIT_BUDGET_US", "3000")     # baked into the plans built below
+    M, N, K = 128 * ws * 2, 512, 64 * ws
+    A = [_randn(c, M, K // ws, dtype, K ** -0.5) for c in ctxs]
+    B = [_randn(c, K // ws, N, dtype) for c in ctxs]
+    C = [torch.zeros(M // ws, N, dtype=dtype, device=c.torch_device) for c in ctxs]
+
+    def run_all():
+        for r, c in enumerate(ctxs):
+            ops.gemm_reducescatter_rows(A[r], B[r], C[r], ctx=c)
+        for c in ctxs:
+            ops.check_status(c)
+
+    run_all()
+    c0 = ctxs[0]
+    plans = [st["plan"] for key, st in c0._state["ops"].items()
+             if isinstance(key, tuple) and key[0] == "reduce_scatter" and "plan" in st]
+    assert len(plans) == 1
+    plan = plans[0]
+    n_remote = plan.tiles_per_owner * (ws - 1)
+    with torch.cuda.device(c0.torch_device):
+        plan.launch(epoch=2, tile_begin=n_remote)            # epoch 2 was never produced
+    with pytest.raises(TileCCLTimeoutError) as err:
+        ops.check_status(c0)
+    assert "'where': 40" in str(err.value) and "peer signal" in str(err.value)
+    run_all()                                                # status cleared, counters untouched
+    full = sum(A[r].float().cpu() @ B[r].float().cpu() for r in range(ws))
+    for r in range(ws):
+        assert _rel(C[r].cpu(), full[r * M // ws:(r + 1) * M // ws]) < TOL[dtype]
+    # recover(): counters and epochs restart from zero, collectively, and calls keep working
+    for c in ctxs:
+        ops.recover(c)
+    run_all()
+    for r in range(ws):
+        assert _rel(C[r].cpu(), full[r * M // ws:(r + 1) * M // ws]) < TOL[dtype]

@@ -26,3 +26,16 @@ def test_multiprocess_ranks(ws):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "MP_WORKER_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])
+
+
+@pytest.mark.parametrize("ws", [2, 4, 8])
+def test_stress_thousands_of_calls_with_changing_inputs(ws):
+    """Every result of 2000 back-to-back all-gather and reduce-scatter calls is checked on
+    the device, with the relaxed and with the release form of the TileGroup signal."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_stress.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker, "--calls", "2000"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert out.returncode == 0 and "MP_STRESS_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])

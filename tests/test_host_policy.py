@@ -199,3 +199,49 @@ def test_runtime_config_snapshot_of_the_environment():
         RuntimeConfig.from_env({"TILECCL_PUSH_MODE": "carrier-pigeon"})
     with pytest.raises(Exception):
         cfg.push_mode = "tma"            # frozen
+
+
+def test_nvlink_facts_from_a_fake_nvml():
+    """Link count, generation and rate come from NVML queries (here: a fake of the API)."""
+    from types import SimpleNamespace as NS
+
+    from tileccl_b200.backends.nvml import nvlink_facts
+
+    class FakeNvml:
+        NVML_FI_DEV_NVLINK_SPEED_MBPS_COMMON = 90
+        calls = []
+
+        def nvmlDeviceGetHandleByIndex(self, i):
+            return ("h", i)
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            self.calls.append(link)
+            if link >= 18:
+                raise RuntimeError("invalid link")
+            return 1
+
+        def nvmlDeviceGetNvLinkVersion(self, h, link):
+            return 7
+
+        def nvmlDeviceGetFieldValues(self, h, fields):
+            return [NS(nvmlReturn=0, value=NS(uiVal=50000))]
+
+    f = nvlink_facts(0, nvml=FakeNvml())
+    assert (f.links_active, f.generation, f.source) == (18, 5, "nvml")
+    assert abs(f.gbps_per_direction - 900.0) < 1e-6
+
+    class NoSpeed(FakeNvml):
+        def nvmlDeviceGetFieldValues(self, h, fields):
+            raise RuntimeError("not supported")
+
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            return 1 if link < 12 else 0
+
+    g = nvlink_facts(0, nvml=NoSpeed())
+    assert (g.links_active, g.source) == (12, "nvml-partial") and g.gbps_per_direction == 600.0
+
+    class Down(FakeNvml):
+        def nvmlDeviceGetNvLinkState(self, h, link):
+            return 0
+
+    assert nvlink_facts(0, nvml=Down()) is None

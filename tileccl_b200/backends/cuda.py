@@ -14,7 +14,8 @@ import ctypes as C
 from .. import _native
 from .base import BackendInterface, DeviceProperties, TopologyInfo
 
-# Per-direction, per-GPU NVLink bandwidth in GB/s by compute capability major.
+# Fallback when NVML cannot be asked (see backends/nvml.py for the measured facts):
+# per-direction, per-GPU NVLink bandwidth in GB/s by compute capability major.
 _NVLINK_GBPS = {8: 300.0, 9: 450.0, 10: 900.0}
 _NVLINK_GEN = {8: 3, 9: 4, 10: 5}
 _NVLINK_LINKS = {8: 12, 9: 18, 10: 18}
@@ -23,6 +24,7 @@ PCIE_GBPS = 32.0
 
 class CUDABackend(BackendInterface):
     name = "cuda"
+    _nvml = None      # a module with the pynvml API; None = import pynvml on demand
 
     def device_count(self) -> int:
         n = C.c_int32()
@@ -78,10 +80,21 @@ class CUDABackend(BackendInterface):
             link, bw = "PCIe", PCIE_GBPS
         else:
             link, bw = "none", 0.0
+        gen = _NVLINK_GEN.get(major, 0) if link in ("NVSwitch", "NVLink") else 0
+        links = _NVLINK_LINKS.get(major, 0) if link in ("NVSwitch", "NVLink") else 0
+        if link in ("NVSwitch", "NVLink"):
+            # Link count, generation and line rate as NVML reports them (read-only queries).
+            from .nvml import nvlink_facts
+
+            facts = nvlink_facts(0, nvml=self._nvml)
+            if facts is not None:
+                links = facts.links_active
+                gen = facts.generation or gen
+                bw = facts.gbps_per_direction or bw
         return TopologyInfo(
             num_gpus=n, backend="cuda", link_type=link,
-            nvlink_generation=_NVLINK_GEN.get(major, 0) if link in ("NVSwitch", "NVLink") else 0,
-            links_per_gpu=_NVLINK_LINKS.get(major, 0) if link in ("NVSwitch", "NVLink") else 0,
+            nvlink_generation=gen,
+            links_per_gpu=links,
             peer_access_matrix=access, native_atomics_matrix=atomics, bandwidth_gbps=bw,
             is_fully_connected=full, multicast_supported=mc, num_compute_units=props.compute_units)
 

@@ -121,6 +121,8 @@ typedef struct TcclGemmDesc {
   uint64_t ident_ptr;            // reduce-scatter: 128 x 128 identity matrix of the operand dtype (row-major)
   int32_t disable_cta_pairs;     // 1: whole-order launches also run the one-CTA form
   int32_t comm_ctas;             // reserved (0)
+  uint64_t entry_local;          // uint32[world_size] "calls entered" counters of this rank on the heap
+                                 // (entry handshake of the modes that store into peers' buffers), 0 = off
 } TcclGemmDesc;
 
 typedef struct TcclGemmPlanInfo {
@@ -142,7 +144,8 @@ int tccl_gemm_plan_info(void* plan, TcclGemmPlanInfo* out);
 // epoch: 1, 2, 3 ... per launch on the plan's signal block (ignored by mode 0).
 // tile_end < 0 runs to the last tile.  flags: bit 0 = also wait for every peer's
 // TileGroups before the kernel exits (push-all), bit 1 = perform the all-gather push
-// of the A operand (an empty tile range is then allowed: push only).
+// of the A operand (an empty tile range is then allowed: push only), bit 3 = this is the
+// first launch of its call: tell the peers that this rank has entered it (entry handshake).
 int tccl_gemm_plan_launch(void* plan, uint32_t epoch, uint32_t a_gate_target, int32_t tile_begin,
                           int32_t tile_end, int32_t flags, uint64_t stream);
 // The same launch while the A operand is still arriving from pinned host memory: for each

@@ -183,6 +183,10 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
                    "all-gather push needs 16-byte aligned buffers and size");
     TCCL_CHECK_ARG(d.a_gate != 0 && d.heap_stride != 0, "all-gather push needs gate counters");
   }
+  p.entry_local = d.entry_local;
+  if (d.entry_local != 0)
+    TCCL_CHECK_ARG(d.heap_stride != 0 && d.entry_local % 4 == 0,
+                   "the entry handshake needs the heap stride and aligned counters");
   p.scatter_col_begin = d.scatter_col_begin;
   p.scatter_col_end = d.scatter_col_end;
   p.status = d.status;
@@ -283,6 +287,7 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   p.a_gate_target = a_gate_target;
   p.wait_incoming = (flags & 1) ? 1 : 0;
   p.do_ag_push = ag_push ? 1 : 0;
+  p.announce_entry = (flags & 8) ? 1 : 0;
   int grid = plan->info.grid;
   if (ag_push) {
     // Every CTA contributes one arrival to the peers' gate counters, so the grid of a
@@ -343,7 +348,7 @@ extern "C" int tccl_gemm_plan_launch_streamed(void* plan_, uint32_t epoch, uint3
     TCCL_CHECK_CUDA(cudaStreamWaitEvent(stream, plan->events[i], 0));
     int f = 0;
     if (i == n_chunks - 1) f |= flags & 1;
-    if (i == 0) f |= flags & 2;
+    if (i == 0) f |= flags & (2 | 8);
     int rc = tccl_gemm_plan_launch(plan_, epoch, a_gate_target, c.tile_begin, c.tile_end, f,
                                    stream_);
     if (rc != kOk) return rc;

@@ -242,6 +242,31 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   const bool comm_push = p.world_size > 1 && p.push_mode != kPushTma &&
                          (p.mode == kModePushAll || p.mode == kModeAllScatter);
 
+  // Entry handshake (see FusedGemmParams::entry_local).  Warp-collective: lane d polls
+  // peer d's "entered" word; returns false (status 45) when a peer never shows up.
+  auto wait_peers_entered = [&]() -> bool {
+    if (p.entry_local == 0 || p.world_size <= 1) return true;
+    bool ok_lane = true;
+    if (lane < p.world_size && lane != p.rank) {
+      uint32_t seen = 0;
+      if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.entry_local) + lane, p.epoch, wb,
+                        &seen)) {
+        report_status(status, kStatusTimeoutSignal, 45, p.epoch, seen, p.rank, lane);
+        *abort_flag = 1;
+        ok_lane = false;
+      }
+    }
+    return __all_sync(0xffffffffu, ok_lane);
+  };
+  auto announce_entry = [&]() {
+    if (p.entry_local == 0 || !p.announce_entry || p.world_size <= 1 || blockIdx.x != 0) return;
+    if (lane < p.world_size && lane != p.rank)
+      red_release_sys_add(
+          reinterpret_cast<uint32_t*>(static_cast<int64_t>(p.entry_local) +
+                                      static_cast<int64_t>(lane - p.rank) * p.heap_stride) + p.rank,
+          1u);
+  };
+
   // ------------------------- communication warps (2, 3) -------------------------
   // Warp 2 forwards rows [0, 64) of every finished tile, warp 3 rows [64, 128): one
   // warp-wide 16-byte load per tile row from this rank's C (still in L2), one store per
@@ -253,6 +278,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     const int rpi = 32 / vpr;        // tile rows covered by one warp-wide access
     const int lrow = lane / vpr, lvec = lane % vpr;
     uint32_t n_tiles = 0;
+    if (!wait_peers_entered()) return;
     for (int t = first; t < tile_end; t += step) {
       ++n_tiles;
       const uint32_t want = n_tiles * kEpiWarps;
@@ -328,6 +354,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // adds one arrival to the peers' gate counter when its part has been performed.
   auto ag_push_role = [&](int part) {
     if (p.ag_bytes == 0 || !p.do_ag_push || p.world_size <= 1) return;
+    if (!wait_peers_entered()) return;
     constexpr int U = 8;
     const char* src = reinterpret_cast<const char*>(p.ag_src);
     const uint64_t nvec = p.ag_bytes >> 4;
@@ -558,6 +585,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       }
     }
   } else if (warp == 2) {
+    announce_entry();
     ag_push_role(0);
     if (comm_push) comm_role(0);
   } else if (warp == 3) {
@@ -592,6 +620,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     uint32_t acc = 0, acc_phase = 0;
     uint32_t buf = 0;
     bool ok = true;
+    // Peer copies issued by this warp (bulk stores) must not start before the peers have
+    // entered this call; checked once, right before the first of them.
+    bool peers_entered = !(p.world_size > 1 && p.push_mode == kPushTma && p.entry_local != 0 &&
+                           (p.mode == kModePushAll || p.mode == kModeAllScatter));
     // lane 0: the last kPend tiles whose signals have not been sent yet ([0] = oldest)
     bool pend_valid[kPend] = {};
     bool slab_pending = false;   // lane 0: a slab whose completion the comm warps still await
@@ -729,6 +761,14 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           // Peer copies: one bulk store per destination here, or (other push modes) left
           // to the communication warps, which forward the tile once it is complete.
           if (push_all && p.world_size > 1 && p.push_mode == kPushTma) {
+            if (!peers_entered) {
+              if (!wait_peers_entered()) {
+                ok = false;
+                if (lane == 0) tma_store_commit();   // the local store issued above
+                break;
+              }
+              peers_entered = true;
+            }
             if (lane == 0)
               for (int d = 1; d < p.world_size; ++d)
                 tma_store_3d(&p.tma_out[(p.rank + d) % p.world_size], col0, y, 0, sbuf);

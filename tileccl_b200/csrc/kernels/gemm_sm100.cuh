@@ -102,6 +102,13 @@ struct alignas(64) FusedGemmParams {
   uint64_t ag_src, ag_dst, ag_mc_dst;
   uint64_t ag_bytes;
   int32_t do_ag_push;
+  // Entry handshake of the modes that write into buffers the peers also read (push-all,
+  // all-scatter, all-gather of the A operand): uint32[world_size] on this rank, word s
+  // counts the calls rank s has entered.  A rank adds 1 to word `rank` on every peer when
+  // its kernel starts (its stream has then finished whatever read the previous call's
+  // data) and stores into peer d only once word d here has reached `epoch`.  0 = off.
+  uint64_t entry_local;
+  int32_t announce_entry;             // this launch is the first of its call: announce it
   // column slice pushed by all-scatter
   int32_t scatter_col_begin, scatter_col_end;
   // diagnostics

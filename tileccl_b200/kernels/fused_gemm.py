@@ -129,6 +129,7 @@ class FusedGemmSpec:
     rs_own_lag: int = 0         # reduce-scatter: rounds the own tile rows trail (0 = all last)
     ident_ptr: int = 0          # reduce-scatter: 128 x 128 identity of `dtype` (see identity_operand)
     wait_budget_ns: int = 0
+    entry_local: int = 0        # uint32[world_size] entry-handshake counters on the heap (0 = off)
 
 
 def count_launches(n: int) -> None:
@@ -190,6 +191,7 @@ class FusedGemmPlan:
         d.tuning = spec.tuning if spec.tuning >= 0 else cfg.tuning
         d.disable_cta_pairs = 0 if cfg.gemm_cta_pairs else 1
         d.wait_budget_ns = spec.wait_budget_ns
+        d.entry_local = spec.entry_local
         handle = C.c_void_p()
         _native.call("tccl_gemm_plan_create", C.byref(d), C.byref(handle))
         self._handle = handle
@@ -212,13 +214,15 @@ class FusedGemmPlan:
 
     def launch(self, *, epoch: int = 1, a_gate_target: int = 0, tile_begin: int = 0,
                tile_end: int = -1, wait_incoming: bool = False, ag_push: bool = False,
+               announce_entry: bool = True,
                stream: Optional[torch.cuda.Stream] = None) -> None:
         global LAUNCH_COUNT
         s = stream if stream is not None else torch.cuda.current_stream()
         LAUNCH_COUNT += 1
         rc = self._launch_fn(self._handle, epoch & 0xFFFFFFFF, a_gate_target & 0xFFFFFFFF,
                              tile_begin, tile_end,
-                             (1 if wait_incoming else 0) | (2 if ag_push else 0), s.cuda_stream)
+                             (1 if wait_incoming else 0) | (2 if ag_push else 0)
+                             | (8 if announce_entry else 0), s.cuda_stream)
         if rc != 0:
             _native.check("tccl_gemm_plan_launch", rc)
 

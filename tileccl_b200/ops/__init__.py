@@ -26,7 +26,7 @@ from typing import Any, Optional
 import torch
 
 from . import _fused
-from ._fused import check_status
+from ._fused import check_status, recover
 from ..kernels.fused_gemm import TileCCLTimeoutError
 
 __all__ = [
@@ -41,7 +41,7 @@ __all__ = [
     "ReduceScatterPlan",
     "GemmAllScatterContract", "GemmAllGatherContract", "GemmReduceScatterContract",
     "AllGatherGemmReduceScatterContract",
-    "check_status", "TileCCLTimeoutError",
+    "check_status", "recover", "TileCCLTimeoutError",
 ]
 
 _STORAGE_KINDS = ("symmetric",)

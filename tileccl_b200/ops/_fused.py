@@ -61,6 +61,41 @@ def check_status(ctx) -> None:
     fg.raise_on_status(st)
 
 
+def recover(ctx) -> None:
+    """Bring the fused operators of this context back to a clean state after a device wait
+    gave up (``TileCCLTimeoutError``): a call that was cut short leaves its TileGroup
+    counters between two epochs, so later calls would wait for counts that never come.
+
+    Collective: every rank calls it at the same point, with none of its kernels in flight.
+    All ranks meet, every counter block and arrival counter of this context is zeroed, the
+    epochs restart at zero, and the ranks meet again before anyone launches.
+    """
+    ctx.barrier()
+    for st in ctx._state.get("ops", {}).values():
+        if not isinstance(st, dict):
+            continue
+        for name in ("sig", "entry", "gate", "counters", "bands"):
+            t = st.get(name)
+            if isinstance(t, torch.Tensor):
+                t.zero_()
+        if "epoch" in st:
+            st["epoch"] = 0
+    status = ctx._state.get("status")
+    if status is not None:
+        status.zero_()
+    heap = ctx.heap
+    if heap is not None:
+        # the stand-alone collectives keep their counter blocks and epochs on the heap object
+        for key, st in heap._state.items():
+            if isinstance(key, tuple) and key and key[0] == "coll" and isinstance(st, dict):
+                st["counters"].zero_()
+                st["epoch"] = 0
+        hs = heap._state.get("status")
+        if hs is not None:
+            hs.zero_()
+    ctx.barrier()
+
+
 def wait_budget_ns() -> int:
     return _config().wait_budget_ns
 
@@ -154,7 +189,21 @@ def _signal_state(ctx, signame: str) -> dict:
     st = op_state(ctx, ("sig", signame))
     if "sig" not in st:
         st["sig"] = ctx.workspace(f"sig:{signame}", ctx.world_size * MAX_GROUPS, dtype=torch.int32)
+        # "calls entered" counters of the entry handshake (see entry_ptr)
+        st["entry"] = ctx.workspace(f"entry:{signame}", 8, dtype=torch.int32)
     return st
+
+
+def entry_ptr(ctx, st: dict) -> int:
+    """Address of the entry-handshake counters of a signal state, or 0 when the handshake is
+    not needed.  A kernel that stores into its peers' copy of a buffer (the all-gathered C, the
+    gathered A operand) first waits until those peers have entered the same call: their
+    streams have then finished whatever read the previous call's data, so back-to-back calls
+    on one buffer need no barrier from the caller.  Ranks that share a GPU are launched phase
+    by phase on one stream and need none of this."""
+    if ctx.world_size <= 1 or not _in_kernel_waits_ok(ctx):
+        return 0
+    return st["entry"].data_ptr()
 
 
 def _heap_offset_ptrs(ctx, tensor: torch.Tensor, extra_bytes: int = 0) -> list:
@@ -306,7 +355,7 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
                      launch_kw.get("epoch", 1) & 0xFFFFFFFF,
                      launch_kw.get("a_gate_target", 0) & 0xFFFFFFFF,
                      (1 if wait_incoming else 0) | (2 if ag_push else 0)
-                     | (4 if order == "plan" else 0), arr, len(chunks),
+                     | (4 if order == "plan" else 0) | 8, arr, len(chunks),
                      side.cuda_stream,
                      st["stream2"].cuda_stream if _config().stream_copy_streams == 2 else 0,
                      cur.cuda_stream)
@@ -322,7 +371,7 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
         cur.wait_event(ev)
         last = i == len(chunks) - 1
         plan.launch(tile_begin=t0, tile_end=t1, wait_incoming=wait_incoming and last,
-                    ag_push=ag_push and i == 0, **launch_kw)
+                    ag_push=ag_push and i == 0, announce_entry=i == 0, **launch_kw)
 
 
 # --------------------------------------------------------------------------
@@ -380,6 +429,7 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
             sub_m=Mloc, sub_n=N, out_ptrs=dests, ldo=C.stride(0), out_rows=Mloc, out_cols=N,
             b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws, out_mc_ptr=mc,
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
+            entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0,
             status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
         plan = st["plan"]
         if ws > 1:
@@ -568,6 +618,7 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
             out_cols=N, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws,
             out_mc_ptr=mc, group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride,
             sig_stride=MAX_GROUPS, scatter_col_begin=col_begin, scatter_col_end=col_end,
+            entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0,
             status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
         plan = st["plan"]
         if ws > 1:

@@ -27,6 +27,7 @@ def _gate_state(ctx, name: str) -> dict:
     st = _fused.op_state(ctx, ("gate", name))
     if "gate" not in st:
         st["gate"] = ctx.workspace(f"gate:{name}", 8, dtype=torch.int32)
+        st["entry"] = ctx.workspace(f"gate_entry:{name}", 8, dtype=torch.int32)
     return st
 
 
@@ -86,6 +87,7 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
             spec.heap_stride = ctx.heap.stride
             spec.a_gate = gate["gate"].data_ptr()
             spec.a_gate_rows_per_rank = mloc
+            spec.entry_local = _fused.entry_ptr(ctx, gate)
             spec.ag_src = region
             spec.ag_dst = region
             spec.ag_bytes = shard_bytes
@@ -102,7 +104,8 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
                                                              tile_end=0, ag_push=True)),
                   _fused._on_device(ctx, lambda: plan.launch(a_gate_target=target))]
     else:
-        phases = [_fused._on_device(ctx, lambda: plan.launch(a_gate_target=target, ag_push=True))]
+        phases = [_fused._on_device(ctx, lambda: plan.launch(epoch=gate["epoch"],
+                                                             a_gate_target=target, ag_push=True))]
     _fused.run_phases(ctx, ("ag_gemm", name, M, N, K, gate["epoch"]), phases)
     return out
 

@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--push-mode", default=None, choices=[None, "stores", "tma", "multimem"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-align", action="store_true",
+                    help="do not align the ranks on the device before each timed problem")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the S0 (cuBLAS + NCCL) and TP-MLP sections")
     ap.add_argument("--reference-mode", default="auto", choices=["auto", "single-process"],
@@ -148,6 +150,26 @@ def load_peaks():
         return {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
 
 
+class RankAligner:
+    """Brings the ranks' streams to the same point before a timed problem: a tiny NCCL
+    all-reduce on the launching stream, after the L2 flush and before the start event.  The
+    256 MiB flush does not take the same time on every GPU; without this its jitter (the
+    maximum over N ranks) is billed to the operator, because every fused call ends only when
+    the slowest peer's data has arrived.  It is the barrier-before-timing of the usual
+    collective benchmarks, used for every arm alike, outside the timed events; the host never
+    blocks on it."""
+
+    def __init__(self, torch, world, device, enabled=True):
+        self.world, self.enabled = world, enabled and world > 1
+        self.token = torch.zeros(1, device=device) if self.enabled else None
+
+    def __call__(self):
+        if self.enabled:
+            import torch.distributed as dist
+
+            dist.all_reduce(self.token)
+
+
 def verify_problems(torch, probs, world, rank, device):
     """fp32 torch product of every problem (operands gathered over NCCL) against the fused
     result of the last call.  Returns the largest max-abs error relative to max |reference|."""
@@ -176,7 +198,7 @@ def verify_problems(torch, probs, world, rank, device):
     return max_over_ranks([worst], world, device)[0]
 
 
-def run_s0(torch, probs, world, device, flush, steps, warmup):
+def run_s0(torch, probs, world, device, flush, steps, warmup, align=lambda: None):
     """S0 of the reference's README: library GEMM, then the bulk library collective
     (torch.matmul + NCCL), on the same operands and with the same timing as the fused arm."""
     if world > 1:
@@ -204,6 +226,7 @@ def run_s0(torch, probs, world, device, flush, steps, warmup):
     for _ in range(max(warmup, 3)):
         for it in items:
             flush.zero_()
+            align()
             run(it)
     torch.cuda.synchronize()
     if world > 1:
@@ -214,6 +237,7 @@ def run_s0(torch, probs, world, device, flush, steps, warmup):
         row = []
         for it in items:
             flush.zero_()
+            align()
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             run(it)
@@ -231,7 +255,7 @@ def run_s0(torch, probs, world, device, flush, steps, warmup):
                           for p, ms in zip(probs, per)}}
 
 
-def run_tp_mlp(torch, ctx, world, rank, device, flush, steps, warmup):
+def run_tp_mlp(torch, ctx, world, rank, device, flush, steps, warmup, align=lambda: None):
     """Tensor-parallel SwiGLU MLP block, bf16, 8192 tokens, hidden 4096, FFN 14336 sharded:
     all-gather -> gate/up GEMM + SiLU-gate -> down GEMM -> reduce-scatter (two fused launches)."""
     from tileccl_b200.models.tp_mlp import TPMLP
@@ -245,12 +269,14 @@ def run_tp_mlp(torch, ctx, world, rank, device, flush, steps, warmup):
     ctx.barrier()
     for _ in range(max(warmup, 3)):
         flush.zero_()
+        align()
         mlp.forward()
     check_status(ctx)
     ctx.barrier()
     evs = []
     for _ in range(steps):
         flush.zero_()
+        align()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         mlp.forward()
@@ -311,9 +337,11 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    align = RankAligner(torch, world, device, not args.no_align)
     for _ in range(max(args.warmup, 3)):
         for p in probs:
             flush.zero_()
+            align()
             run_one(p)
     sync_all()
     ops.check_status(ctx)
@@ -330,6 +358,7 @@ def run_ours(args):
         row = []
         for p in probs:
             flush.zero_()
+            align()
             s = torch.cuda.Event(enable_timing=True)
             e = torch.cuda.Event(enable_timing=True)
             s.record()
@@ -417,9 +446,9 @@ def run_ours(args):
 
     extras = {}
     if not args.no_extras:
-        extras["s0"] = run_s0(torch, probs, world, device, flush, args.steps, args.warmup)
+        extras["s0"] = run_s0(torch, probs, world, device, flush, args.steps, args.warmup, align)
         extras["tp_mlp"] = run_tp_mlp(torch, ctx, world, rank, device, flush, args.steps,
-                                      args.warmup)
+                                      args.warmup, align)
 
     peaks = load_peaks()
     shapes = {}
@@ -447,6 +476,9 @@ def run_ours(args):
                        "parallelism": f"tp{world} row-sharded",
                        "l2": "256 MiB flush write before every problem, outside the timed events",
                        "timing": "CUDA events per problem, max over ranks, mean over steps",
+                       "rank_alignment": ("none" if args.no_align or world == 1 else
+                                          "tiny NCCL all-reduce on the stream after the flush, "
+                                          "before the start event (every arm)"),
                        "push_mode": os.environ.get("TILECCL_PUSH_MODE", "tma"),
                        "nvls_bound": bool(ctx.heap.has_multicast),
                        "roofline_peaks": peaks,
@@ -558,9 +590,11 @@ def run_reference(args):
                 dist.barrier()
                 torch.cuda.synchronize()
 
+        align = RankAligner(torch, world, device, not args.no_align)
         for _ in range(max(args.warmup, 3)):
             for p in probs:
                 flush.zero_()
+                align()
                 run_one(p)
         sync_all()
         sampler = ClockSampler(local)
@@ -572,6 +606,7 @@ def run_reference(args):
             row = []
             for p in probs:
                 flush.zero_()
+                align()
                 s = torch.cuda.Event(enable_timing=True)
                 e = torch.cuda.Event(enable_timing=True)
                 s.record()

@@ -64,7 +64,7 @@ def summarize(label, plan, pair, trace, ms, rank, timeline=None):
     n_slots = (2 * ((plan.m_tiles_local + 1) // 2) * plan.n_tiles_local * plan.owners if pair
                else plan.tiles_total)
     t = raw[:n_slots * 16].reshape(n_slots, 4, 4)
-    cta = raw[n_slots * 16:n_slots * 16 + grid * 4].reshape(grid, 4)
+    cta = raw[n_slots * 16:n_slots * 16 + grid * 8].reshape(grid, 8)
     if timeline and rank == 0:
         _write_timeline(timeline, label, plan, pair, t, rank, n_slots)
     entry0 = cta[:, 0][cta[:, 0] > 0].min()
@@ -106,12 +106,25 @@ def summarize(label, plan, pair, trace, ms, rank, timeline=None):
         "last_signal_us": round(float(np.nanmax(rel[:, :, 3])), 2),
         "incoming_seen_us": (round(float(np.nanmax(crel[:, 2])), 2)
                              if not np.all(np.isnan(crel[:, 2])) else None),
-        "exit_us": round(float(np.nanmax(crel[:, 3])), 2),
-        "exit_min_us": round(float(np.nanmin(crel[:, 3])), 2),
+        "epilogue_done_us": round(float(np.nanmax(crel[:, 4:8])), 2),
+        "epilogue_done_min_us": round(float(np.nanmin(np.nanmax(crel[:, 4:8], axis=1))), 2),
         "median_wait_acc_us": med(acc_wait), "median_issue_us": med(issue),
         "median_wait_older_stores_us": med(compl), "median_signal_us": med(sig),
     }
-    out["launch_overhead_us"] = round(out["event_us"] - out["exit_us"], 1)
+    end = max(out["epilogue_done_us"], out["incoming_seen_us"] or 0.0)
+    out["event_minus_kernel_span_us"] = round(out["event_us"] - end, 1)
+    # how long this rank sat waiting for its peers' data after its own pushes were done
+    out["wait_for_peers_us"] = (round(out["incoming_seen_us"] - out["epilogue_done_us"], 2)
+                                if out["incoming_seen_us"] is not None else None)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        rows = [None] * dist.get_world_size()
+        dist.all_gather_object(rows, {k: out[k] for k in ("event_us", "epilogue_done_us",
+                                                          "incoming_seen_us", "wait_for_peers_us",
+                                                          "first_acc_ready_us")})
+        for k in ("event_us", "epilogue_done_us", "incoming_seen_us", "wait_for_peers_us"):
+            vals = [r[k] for r in rows if r[k] is not None]
+            if vals:
+                out[f"{k}_ranks_min_max"] = [min(vals), max(vals)]
     if rank == 0:
         print(json.dumps(out), flush=True)
     return out
@@ -176,7 +189,7 @@ def main() -> None:
         return s.elapsed_time(e)
 
     def trace_buffer(m_tiles, n_tiles, owners):
-        words = 2 * ((m_tiles + 1) // 2) * n_tiles * owners * 16 + 4 * 1024
+        words = 2 * ((m_tiles + 1) // 2) * n_tiles * owners * 16 + 8 * 1024
         return torch.zeros(words, dtype=torch.int64, device=dev)
 
     first = True

@@ -95,3 +95,34 @@ def test_measured_profile_reads_files(tmp_path):
     p = HardwareProfile.b200_measured(str(peaks), str(cal))
     assert p.gemm_tflops_fp16 == 1628.4 and p.alpha_us == 2.0 and p.min_comm_us == 3.0
     assert HardwareProfile.b200_measured("/nonexistent", "/nonexistent").bandwidth_gb_s == pytest.approx(900)
+
+
+def test_calibration_file_sizes_the_tile_groups(tmp_path, monkeypatch):
+    """tau_min of the calibration file in force decides how many tile rows form a TileGroup."""
+    import json
+
+    from tileccl_b200.ops import _fused, _tile_group_info
+    from tileccl_b200.planning.cost_model import calibrated_tau_min_bytes
+
+    monkeypatch.delenv("TILECCL_CALIBRATION", raising=False)
+    shipped = calibrated_tau_min_bytes()
+    assert 256 * 1024 <= shipped <= 2 * 1024 * 1024            # measured: a bit under one 4096-wide tile row
+    assert _fused.default_group_m_tiles(64, 16) == 1            # gate shapes: one row per group
+    assert _tile_group_info(8192, 4096)["group_m_tiles"] == 1
+    coarse = tmp_path / "coarse.json"
+    coarse.write_text(json.dumps({"alpha_us": 1.0, "beta_us_per_byte": 1e-6,
+                                  "in_kernel": {"alpha_us": 4.0, "beta_us_per_byte": 1.5e-6,
+                                                "tau_min_bytes": 8 << 20}}))
+    monkeypatch.setenv("TILECCL_CALIBRATION", str(coarse))
+    assert calibrated_tau_min_bytes() == 8 << 20
+    info = _tile_group_info(8192, 4096)
+    assert info["group_m_tiles"] == 8 and info["n_groups"] == 8 and info["calibration"] == str(coarse)
+    assert _fused.default_group_m_tiles(4, 16) == 4             # never more rows than there are
+    # without an in-kernel section the reference's constant applies
+    plain = tmp_path / "plain.json"
+    plain.write_text(json.dumps({"alpha_us": 1.0, "beta_us_per_byte": 1e-6}))
+    monkeypatch.setenv("TILECCL_CALIBRATION", str(plain))
+    assert calibrated_tau_min_bytes() == 262144
+    # the in-kernel fit is what the cost model predicts with
+    monkeypatch.setenv("TILECCL_CALIBRATION", str(coarse))
+    assert HardwareProfile.b200_measured("/nonexistent").alpha_us == 4.0

@@ -244,7 +244,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     const int64_t slots_one = info.tiles_total;
     const int64_t slots_pair =
         2ll * ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
-    info.trace_words = (slots_one > slots_pair ? slots_one : slots_pair) * 16 + 4ll * grid;
+    info.trace_words = (slots_one > slots_pair ? slots_one : slots_pair) * 16 + 8ll * grid;
   }
   return kOk;
 }

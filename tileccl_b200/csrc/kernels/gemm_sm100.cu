@@ -218,13 +218,14 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 
   WaitBudget wb;
   wb.start(p.wait_budget_ns, abort_flag);
-  // Trace layout: uint64[tile slots][4 epilogue warps][4] followed by uint64[CTAs][4]
-  // (kernel entry / roles start / epilogue or waiter done / exit).
+  // Trace layout: uint64[tile slots][4 epilogue warps][4] followed by uint64[CTAs][8]
+  // (kernel entry / roles start / incoming TileGroups seen / after the final CTA barrier /
+  // epilogue warp 0..3 done, i.e. its last bulk store complete and last signal sent).
   uint64_t* const trace_tiles = reinterpret_cast<uint64_t*>(p.trace);
   uint64_t* const trace_cta =
       p.trace == 0 ? nullptr
                    : trace_tiles + static_cast<int64_t>(p.trace_tile_slots) * (kEpiWarps * 4) +
-                         static_cast<int64_t>(blockIdx.x) * 4;
+                         static_cast<int64_t>(blockIdx.x) * 8;
   if (trace_cta != nullptr && threadIdx.x == 0) {
     trace_cta[0] = t_entry;
     trace_cta[1] = globaltimer_ns();
@@ -850,6 +851,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
 #pragma unroll
       for (int i = 0; i < kPend; ++i)
         if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
+      if (trace_cta != nullptr) trace_cta[4 + q] = globaltimer_ns();
     }
   }
 

@@ -115,9 +115,9 @@ struct alignas(64) FusedGemmParams {
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;
   // optional uint64[trace_tile_slots][4 epilogue warps][4] (accumulator ready / stores
-  // issued / older stores complete / signalled) followed by uint64[CTAs][4] (kernel entry /
-  // roles start / incoming TileGroups seen / exit); a tile slot is a 128-row tile, in the
-  // CTA-pair form slot 2 * pair-tile + CTA
+  // issued / older stores complete / signalled) followed by uint64[CTAs][8] (kernel entry /
+  // roles start / incoming TileGroups seen / final CTA barrier passed / epilogue warp 0..3
+  // done); a tile slot is a 128-row tile, in the CTA-pair form slot 2 * pair-tile + CTA
   uint64_t trace;
   int32_t trace_tile_slots;
   int32_t tuning;                     // TuningBits

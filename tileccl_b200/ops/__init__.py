@@ -72,6 +72,20 @@ def _cached_plan(ctx, key, build):
     return plan
 
 
+def _tile_group_info(rows: int, cols: int, elem_bytes: int = 2) -> dict:
+    """TileGroup geometry a fused launch over a ``rows x cols`` sub-problem will use: the
+    planner's P0 rule with tau_min from the calibration file (see
+    ``_fused.default_group_m_tiles``).  Part of the plans' ``to_dict()``."""
+    from ..kernels import fused_gemm as fg
+    from ..planning.cost_model import calibrated_tau_min_bytes, calibration_path
+
+    m_tiles = -(-rows // fg.BLOCK_M)
+    n_tiles = -(-cols // fg.BLOCK_N)
+    gm = _fused.default_group_m_tiles(m_tiles, n_tiles, elem_bytes)
+    return {"group_m_tiles": gm, "n_groups": -(-m_tiles // gm), "tile": [fg.BLOCK_M, fg.BLOCK_N],
+            "tau_min_bytes": calibrated_tau_min_bytes(), "calibration": calibration_path()}
+
+
 def _check_storage(storage_kind: str) -> None:
     if storage_kind not in _STORAGE_KINDS:
         raise ValueError(f"storage_kind must be one of {_STORAGE_KINDS}, got {storage_kind!r}")
@@ -310,9 +324,15 @@ class GemmAllGatherPlan:
         return C
 
     def to_dict(self) -> dict:
-        return {"op": "gemm_allgather", "contract": self.contract.to_dict(),
-                "storage_kind": self.storage_kind, "kernel": "fused_gemm_sm100/push_all",
-                "signal_mode": "counting", "wait_mode": "wait_ge"}
+        c = self.contract
+        rows = c.M if c.layout == "columns" else c.M // c.world_size
+        cols = c.shard_cols if c.layout == "columns" else c.full_N
+        d = {"op": "gemm_allgather", "contract": c.to_dict(),
+             "storage_kind": self.storage_kind, "kernel": "fused_gemm_sm100/push_all",
+             "signal_mode": "counting", "wait_mode": "wait_ge",
+             "tile_groups": _tile_group_info(rows, cols)}
+        d["group_m_tiles"] = d["tile_groups"]["group_m_tiles"]
+        return d
 
 
 def _resolve_gemm_allgather_contract(A, B, C, ctx, layout, storage_kind, b_is_nk=False):
@@ -426,10 +446,14 @@ class GemmReduceScatterPlan:
         return C
 
     def to_dict(self) -> dict:
-        return {"op": "gemm_reducescatter", "contract": self.contract.to_dict(),
-                "implementation": self.implementation, "storage_kind": self.storage_kind,
-                "kernel": "fused_gemm_sm100/reduce_scatter", "signal_mode": "counting",
-                "wait_mode": "wait_ge", "partials": "16-bit staged, fp32 reduction in rank order"}
+        c = self.contract
+        d = {"op": "gemm_reducescatter", "contract": c.to_dict(),
+             "implementation": self.implementation, "storage_kind": self.storage_kind,
+             "kernel": "fused_gemm_sm100/reduce_scatter", "signal_mode": "counting",
+             "wait_mode": "wait_ge", "partials": "16-bit staged, fp32 reduction in rank order",
+             "tile_groups": _tile_group_info(c.out_rows, c.out_cols)}
+        d["group_m_tiles"] = d["tile_groups"]["group_m_tiles"]
+        return d
 
 
 def _resolve_gemm_reducescatter_contract(A, B, C, ctx, layout, storage_kind, b_is_nk=False):

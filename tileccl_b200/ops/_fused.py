@@ -131,9 +131,19 @@ def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
     return lag if 1 <= lag < m_tiles else 0
 
 
-def default_group_m_tiles(m_tiles: int) -> int:
-    """Finest TileGroup (one tile row) unless that would need more than MAX_GROUPS counters."""
-    return max(1, -(-m_tiles // MAX_GROUPS))
+def default_group_m_tiles(m_tiles: int, n_tiles: Optional[int] = None, elem_bytes: int = 2) -> int:
+    """Tile rows per TileGroup: the planner's P0 rule (a group carries at least tau_min bytes,
+    tileccl_v2/tile_group.py:116-117 in the reference) with tau_min taken from the calibration
+    file, and never more than MAX_GROUPS groups.  For the 4096-column gate shapes one tile row
+    (1 MiB) already exceeds the calibrated tau_min, so groups are single rows."""
+    finest = max(1, -(-m_tiles // MAX_GROUPS))
+    if not n_tiles:
+        return finest
+    from ..planning.cost_model import calibrated_tau_min_bytes
+
+    row_bytes = n_tiles * fg.BLOCK_M * fg.BLOCK_N * elem_bytes
+    need = -(-calibrated_tau_min_bytes() // row_bytes)
+    return max(1, min(m_tiles, max(finest, need)))
 
 
 # --------------------------------------------------------------------------
@@ -409,7 +419,7 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
         fast(wait)              # repeated call on the same buffers: epoch + launch only
         return
     m_tiles = -(-Mloc // fg.BLOCK_M)
-    gm = group_m_tiles or default_group_m_tiles(m_tiles)
+    gm = group_m_tiles or default_group_m_tiles(m_tiles, -(-N // fg.BLOCK_N), A.element_size())
     sigst = _signal_state(ctx, f"push_all:{name}:{Mloc}x{N}x{K}:g{gm}") if ws > 1 else st
     if "plan" not in st:
         region_bytes = (region_row0 * C.stride(0) + region_col0) * C.element_size()
@@ -526,7 +536,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
         fast()
         return
     m_tiles = -(-sub_m // fg.BLOCK_M)
-    gm = group_m_tiles or default_group_m_tiles(m_tiles)
+    gm = group_m_tiles or default_group_m_tiles(m_tiles, -(-sub_n // fg.BLOCK_N), A.element_size())
     sigst = (_signal_state(ctx, f"reduce_scatter:{name}:{M}x{N}x{K}:a{split_axis}:g{gm}:{A.dtype}")
              if ws > 1 else st)
     if "plan" not in st:
@@ -600,7 +610,7 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
            B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, push_mode)
     st = op_state(ctx, key)
     m_tiles = -(-M // fg.BLOCK_M)
-    gm = default_group_m_tiles(m_tiles)
+    gm = default_group_m_tiles(m_tiles, -(-N // fg.BLOCK_N), A.element_size())
     sigst = _signal_state(ctx, f"all_scatter:{name}:{M}x{N}x{K}:g{gm}") if ws > 1 else st
     if "plan" not in st:
         if ws > 1:

@@ -76,11 +76,8 @@ class HardwareProfile:
         next to the package (measured on an 8 x B200 NVSwitch machine) is used.
         """
         prof = _PRESETS[Interconnect.NVLINK_5]
-        shipped = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
-            os.path.abspath(__file__)))), "calibration", "b200.json")
         for path, apply in ((peaks_path, _apply_peaks),
-                            (calibration_path or _runtime_config().calibration or shipped,
-                             _apply_calibration)):
+                            (globals()["calibration_path"](calibration_path), _apply_calibration)):
             if path and os.path.exists(path):
                 try:
                     with open(path) as f:
@@ -101,10 +98,48 @@ def _apply_peaks(prof: HardwareProfile, data: dict) -> HardwareProfile:
 
 
 def _apply_calibration(prof: HardwareProfile, data: dict) -> HardwareProfile:
-    return replace(prof, alpha_us=float(data["alpha_us"]),
-                   beta_us_per_byte=float(data["beta_us_per_byte"]),
-                   min_comm_us=float(data.get("min_comm_us", 0.0)),
+    """A calibration file may carry two fits.  ``in_kernel`` (preferred): alpha / beta of the
+    push phase *inside* the fused kernel, from its %globaltimer trace (fixed in-kernel
+    overhead and achieved link rate).  Top level: a whole collective launch per message size
+    (includes launch latency and the three-phase protocol)."""
+    src = data.get("in_kernel") if isinstance(data.get("in_kernel"), dict) else data
+    return replace(prof, alpha_us=float(src["alpha_us"]),
+                   beta_us_per_byte=float(src["beta_us_per_byte"]),
+                   min_comm_us=float(src.get("min_comm_us", 0.0)),
                    name=prof.name + " (calibrated)")
+
+
+def calibration_path(explicit: Optional[str] = None) -> str:
+    """The link-model file in force: explicit argument, else ``TILECCL_CALIBRATION``, else the
+    ``calibration/b200.json`` that ships next to the package."""
+    shipped = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(
+        os.path.abspath(__file__)))), "calibration", "b200.json")
+    return explicit or _runtime_config().calibration or shipped
+
+
+def load_calibration(path: Optional[str] = None) -> dict:
+    """Contents of the calibration file (empty dict when it cannot be read)."""
+    try:
+        with open(calibration_path(path)) as f:
+            data = json.load(f)
+        return data if isinstance(data, dict) else {}
+    except (OSError, ValueError):
+        return {}
+
+
+DEFAULT_TAU_MIN_BYTES = 262144   # the reference's P2P saturation size (tileccl_v2/tile_group.py:22)
+
+
+def calibrated_tau_min_bytes(path: Optional[str] = None) -> int:
+    """Smallest TileGroup worth signalling on its own, from the calibration file: the bytes
+    the link moves while one TileGroup signal becomes visible to its consumer
+    (``in_kernel.tau_min_bytes``).  Finer groups only add counters that a consumer cannot
+    observe any sooner.  Falls back to the reference's constant."""
+    data = load_calibration(path)
+    ik = data.get("in_kernel")
+    if isinstance(ik, dict) and ik.get("tau_min_bytes"):
+        return max(1, int(ik["tau_min_bytes"]))
+    return DEFAULT_TAU_MIN_BYTES
 
 
 _PRESETS = {

@@ -26,6 +26,7 @@
 #include "../api.h"
 #include "../device/ptx.cuh"
 #include "../device/tile_collectives.cuh"
+#include "../device/tile_ll.cuh"
 #include "../runtime/errors.h"
 
 namespace tileccl {
@@ -172,9 +173,139 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const CollParams
   }
 }
 
+// ---------------------------------------------------------------------------
+// Low-latency copy collectives (all-gather, broadcast, scatter) for small messages:
+// data and flag travel in the same 16-byte store (device/tile_ll.cuh), so a call is one
+// NVLink write latency plus one poll instead of announce / move / publish / wait.
+// ---------------------------------------------------------------------------
+struct LLParams {
+  int32_t op, rank, world_size, root, phase_mask;
+  uint32_t epoch;        // 1, 2, 3 ... per call on this staging + counter block (also the flag)
+  uint64_t src, dst;     // local addresses
+  uint64_t stage;        // this rank's staging: [2 parities][n_slots][kLLSlotBytes]
+  int32_t n_slots;       // world_size (all-gather: one slot per source) or 1 (rooted ops)
+  uint64_t counters;     // this rank's block: [0, 8) acknowledgements from rank d, [16] cta_done
+  int64_t heap_stride;
+  uint32_t bytes;        // payload per (source, destination), multiple of 8, <= kLLMaxBytes
+  uint64_t status, budget_ns;
+};
+
+__global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
+  __shared__ uint32_t abort_word;
+  __shared__ int failed, is_last;
+  if (threadIdx.x == 0) { abort_word = 0; failed = 0; }
+  __syncthreads();
+  WaitBudget wb;
+  wb.start(p.budget_ns, &abort_word);
+  uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
+  uint32_t* counters = reinterpret_cast<uint32_t*>(p.counters);
+  const int ws = p.world_size, rank = p.rank;
+  const bool rooted = p.op != kAllGather;
+  const bool sender = !rooted || rank == p.root;
+  const bool receiver = !rooted || rank != p.root;
+  const uint32_t parity = p.epoch & 1u;
+  const uint64_t parity_off = static_cast<uint64_t>(parity) * p.n_slots * kLLSlotBytes;
+  const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
+  auto peer_addr = [&](uint64_t local, int r) {
+    return local + static_cast<uint64_t>(static_cast<int64_t>(r - rank) * p.heap_stride);
+  };
+
+  if ((p.phase_mask & 1) && sender) {
+    // The parity half about to be written was last used two calls ago: every receiver must
+    // have acknowledged that call.
+    if (p.epoch > 2) {
+      const int d = threadIdx.x;
+      if (d < ws && d != rank) {
+        uint32_t seen = 0;
+        if (!tile_wait_ge(counters + d, p.epoch - 2u, wb, &seen)) {
+          report_status(status, kStatusTimeoutSignal, 70, p.epoch - 2u, seen, rank, d);
+          failed = 1;
+        }
+      }
+      __syncthreads();
+    }
+    if (!failed) {
+      const int slot = rooted ? 0 : rank;
+      for (int k = 1; k < ws; ++k) {
+        const int d = (rank + k) % ws;
+        const char* src = reinterpret_cast<const char*>(p.src) +
+                          (p.op == kScatter ? static_cast<uint64_t>(d) * p.bytes : 0);
+        char* lines = reinterpret_cast<char*>(peer_addr(p.stage, d)) + parity_off +
+                      static_cast<uint64_t>(slot) * kLLSlotBytes;
+        ll_send(lines, src, p.bytes, p.epoch, tid, nthreads);
+      }
+      // this rank's own part never leaves the GPU
+      if (p.op == kAllGather || p.op == kScatter) {
+        const char* src = reinterpret_cast<const char*>(p.src) +
+                          (p.op == kScatter ? static_cast<uint64_t>(rank) * p.bytes : 0);
+        char* dst = reinterpret_cast<char*>(p.dst) +
+                    (p.op == kAllGather ? static_cast<uint64_t>(rank) * p.bytes : 0);
+        if (src != dst)
+          for (uint32_t i = tid; i < (p.bytes >> 3); i += nthreads)
+            reinterpret_cast<uint2*>(dst)[i] = reinterpret_cast<const uint2*>(src)[i];
+      }
+    }
+  }
+
+  if ((p.phase_mask & 2) && receiver) {
+    const char* stage = reinterpret_cast<const char*>(p.stage) + parity_off;
+    bool ok = true;
+    if (rooted) {
+      ok = ll_recv(reinterpret_cast<char*>(p.dst), stage, p.bytes, p.epoch, tid, nthreads, wb);
+    } else {
+      for (int k = 1; k < ws && ok; ++k) {
+        const int s = (rank + ws - k) % ws;
+        ok = ll_recv(reinterpret_cast<char*>(p.dst) + static_cast<uint64_t>(s) * p.bytes,
+                     stage + static_cast<uint64_t>(s) * kLLSlotBytes, p.bytes, p.epoch, tid,
+                     nthreads, wb);
+      }
+    }
+    if (!ok) report_status(status, kStatusTimeoutSignal, 71, p.epoch, 0, rank, 0);
+    // Acknowledge once every CTA of this launch has consumed its lines.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t old = atomicAdd(counters + 16, 1u);
+      is_last = (old == gridDim.x - 1) ? 1 : 0;
+      if (is_last) counters[16] = 0;
+    }
+    __syncthreads();
+    if (is_last) {
+      const int s = threadIdx.x;
+      if (s < ws && s != rank && (!rooted || s == p.root))
+        red_release_sys_add(reinterpret_cast<uint32_t*>(peer_addr(p.counters, s)) + rank, 1u);
+    }
+  }
+}
+
 }  // namespace tileccl
 
 using namespace tileccl;
+
+extern "C" int tccl_collective_ll_launch(int32_t op, int32_t rank, int32_t world_size, int32_t root,
+                                         int32_t phase_mask, uint32_t epoch, uint64_t src,
+                                         uint64_t dst, uint64_t stage, uint64_t counters,
+                                         int64_t heap_stride, uint64_t bytes, int32_t grid,
+                                         uint64_t status, uint64_t budget_ns, uint64_t stream) {
+  TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter,
+                 "the low-latency path moves copies only (all-gather, broadcast, scatter)");
+  TCCL_CHECK_ARG(world_size >= 2 && world_size <= kMaxRanks, "world_size must be 2..8");
+  TCCL_CHECK_ARG(rank >= 0 && rank < world_size && root >= 0 && root < world_size, "bad rank/root");
+  TCCL_CHECK_ARG(bytes > 0 && bytes <= kLLMaxBytes && bytes % 8 == 0,
+                 "low-latency messages are multiples of 8 bytes, at most " << kLLMaxBytes);
+  TCCL_CHECK_ARG(src % 8 == 0 && dst % 8 == 0 && stage % 16 == 0 && stage != 0 && counters != 0,
+                 "buffers must be 8-byte aligned and staging / counters present");
+  TCCL_CHECK_ARG(epoch != 0, "epoch starts at 1");
+  TCCL_CHECK_ARG(grid >= 1 && grid <= 32, "grid must be 1..32");
+  LLParams p;
+  p.op = op; p.rank = rank; p.world_size = world_size; p.root = root; p.phase_mask = phase_mask;
+  p.epoch = epoch; p.src = src; p.dst = dst; p.stage = stage;
+  p.n_slots = op == kAllGather ? world_size : 1;
+  p.counters = counters; p.heap_stride = heap_stride; p.bytes = static_cast<uint32_t>(bytes);
+  p.status = status; p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
+  ll_copy_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  TCCL_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
 
 extern "C" int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
                                       int32_t root, int32_t use_multimem, int32_t phase_mask,
@@ -304,6 +435,7 @@ cudaError_t preload_collective_kernels() {
   cudaFuncAttributes a;
   cudaError_t e = cudaFuncGetAttributes(&a, collective_kernel);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, allreduce_oneshot_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ll_copy_kernel);
   return e;
 }
 }  // namespace tileccl

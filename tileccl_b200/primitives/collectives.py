@@ -201,6 +201,55 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
     _run(heap, (kind, nbytes, epoch) + tuple(rv_extra), phases)
 
 
+LL_SLOT_BYTES = 128 * 1024      # staging per (parity, source): 64 KiB of payload as 16-byte lines
+LL_MAX_BYTES = 64 * 1024
+
+
+def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
+    """Low-latency path?  Small per-peer messages that are multiples of 8 bytes."""
+    limit = min(LL_MAX_BYTES, _config().ll_max_bytes)
+    return (heap.world_size > 1 and 0 < per_peer_bytes <= limit and per_peer_bytes % 8 == 0
+            and all(p % 8 == 0 for p in ptrs))
+
+
+def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int, *,
+               root: int = 0) -> None:
+    """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store."""
+    st = heap._state.get(("coll_ll", kind))
+    if st is None:
+        slots = heap.world_size if op == OP_ALLGATHER else 1
+        st = {"stage": heap.allocate_zeroed((2 * slots * LL_SLOT_BYTES,), torch.uint8),
+              "counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0,
+              "status_ptr": _status(heap).data_ptr(), "fn": getattr(_native.load(),
+                                                                   "tccl_collective_ll_launch")}
+        st["stage_ptr"], st["counters_ptr"] = st["stage"].data_ptr(), st["counters"].data_ptr()
+        heap._state[("coll_ll", kind)] = st
+    st["epoch"] += 1
+    epoch = st["epoch"]
+    lines = per_peer_bytes // 8 * (heap.world_size - 1)      # lines this rank sends or receives
+    grid = max(1, min(8, lines // 2048))
+
+    def go(mask: int):
+        rc = st["fn"](op, heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, src, dst,
+                      st["stage_ptr"], st["counters_ptr"], heap.stride, per_peer_bytes, grid,
+                      st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            _native.check("tccl_collective_ll_launch", rc)
+
+    if not heap.emulated and heap.local_group is None:
+        go(3)
+        return
+
+    def on_dev(mask):
+        def run():
+            with torch.cuda.device(heap.device):
+                go(mask)
+        return run
+
+    phases = [on_dev(1), on_dev(2)] if heap.emulated else [on_dev(3)]
+    _run(heap, ("ll:" + kind, per_peer_bytes, epoch, root), phases)
+
+
 def _heap_of(heap, ctx):
     if heap is None and ctx is not None:
         heap = ctx.heap
@@ -280,6 +329,9 @@ def allgather(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, ctx=None
     if heap.world_size == 1:
         output.view(-1).copy_(tensor.view(-1))
         return output
+    if _ll_ok(heap, nbytes, tensor.data_ptr(), output.data_ptr()):
+        _launch_ll(heap, "allgather", OP_ALLGATHER, tensor.data_ptr(), output.data_ptr(), nbytes)
+        return output
     _launch(heap, "allgather", OP_ALLGATHER, 3, tensor.data_ptr(), output.data_ptr(), nbytes,
             use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
     return output
@@ -318,6 +370,10 @@ def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> to
     if heap.world_size == 1:
         return tensor
     nbytes = tensor.numel() * tensor.element_size()
+    if _ll_ok(heap, nbytes, tensor.data_ptr()):
+        _launch_ll(heap, f"broadcast:{root}", OP_BROADCAST, tensor.data_ptr(), tensor.data_ptr(),
+                   nbytes, root=root)
+        return tensor
     # The rooted handshake only advances the counters between the root and the others, so
     # every root has its own counter block and epoch (roots may alternate call by call).
     _launch(heap, f"broadcast:{root}", OP_BROADCAST, 3, tensor.data_ptr(), tensor.data_ptr(), nbytes,
@@ -339,6 +395,10 @@ def scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, root: int 
     nbytes = output.numel() * output.element_size()
     if heap.world_size == 1:
         output.view(-1).copy_(tensor.view(-1))
+        return output
+    if _ll_ok(heap, nbytes, tensor.data_ptr(), output.data_ptr()):
+        _launch_ll(heap, f"scatter:{root}", OP_SCATTER, tensor.data_ptr(), output.data_ptr(), nbytes,
+                   root=root)
         return output
     _launch(heap, f"scatter:{root}", OP_SCATTER, 3, tensor.data_ptr(), output.data_ptr(), nbytes, root=root,
             rv_extra=(root,), elem_size=tensor.element_size())

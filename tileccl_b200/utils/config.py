@@ -42,6 +42,7 @@ class RuntimeConfig:
     native_lib: Optional[str] = None       # TILECCL_NATIVE_LIB: another build of the shared object
     no_build: bool = False                 # TILECCL_NO_BUILD: never compile the shared object on import
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
+    ll_max_bytes: int = 65536              # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency copy collectives (0 = off)
     comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
     push_mode_explicit: bool = False       # TILECCL_PUSH_MODE was set (it then overrides a pattern's own choice)
     # feature gates kept from the reference
@@ -68,6 +69,7 @@ class RuntimeConfig:
             native_lib=e.get("TILECCL_NATIVE_LIB") or None,
             no_build=_flag(e, "TILECCL_NO_BUILD"),
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
+            ll_max_bytes=min(65536, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or 65536))),
             comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
             push_mode_explicit=bool(e.get("TILECCL_PUSH_MODE")),
             experimental_multiprocess_device_collectives=(

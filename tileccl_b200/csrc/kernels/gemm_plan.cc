@@ -15,7 +15,8 @@
 
 namespace tileccl {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream,
+                                   bool bounce);
 cudaError_t preload_gemm_kernels();
 cudaError_t preload_collective_kernels();
 cudaError_t preload_push_kernels();
@@ -299,8 +300,11 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   if (plan->pair_kernel && tile_begin == 0 && tile_end == total) {
     p.trace_tile_slots = 2 * ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
     // (an all-gather-pushing launch has a fixed grid: the consumers count its CTAs)
+    // A launch that pushes the A operand trades one operand stage for the bounce ring its
+    // communication warps copy through.
     TCCL_CHECK_CUDA(launch_fused_gemm_pair(p, ag_push ? plan->pair_push_grid : plan->pair_grid,
-                                           reinterpret_cast<cudaStream_t>(stream)));
+                                           reinterpret_cast<cudaStream_t>(stream),
+                                           ag_push && p.ag_mc_dst == 0));
     return kOk;
   }
   p.trace_tile_slots = total;

@@ -134,9 +134,17 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
 #endif
 static constexpr int kPend = TCCL_SIGNAL_DELAY_TILES;
 
-template <bool kPair>
+// kBounce (CTA pairs only): one operand stage is given up for a 32 KB bounce ring through
+// which warps 2 and 3 push the all-gathered A operand to the peers as bulk copies.
+static constexpr int kBounceSlotBytes = 8192;
+static constexpr int kBounceSlotsPerWarp = 2;
+
+template <bool kPair, bool kBounce = false>
 struct Geo {
-  static constexpr int kNumStages = kPair ? TCCL_PAIR_STAGES : kStages;
+  static_assert(kPair || !kBounce, "the bounce ring exists in the CTA-pair form only");
+  static constexpr int kNumStages = kPair ? (kBounce ? TCCL_PAIR_STAGES - 1 : TCCL_PAIR_STAGES)
+                                          : kStages;
+  static constexpr int kBounceBytes = kBounce ? 2 * kBounceSlotsPerWarp * kBounceSlotBytes : 0;
   // staging buffers per epilogue warp: a deeper ring lets the epilogue run further ahead of
   // bulk stores that the link has not taken yet
   static constexpr int kEpi = kPair ? TCCL_PAIR_EPI_BUFS : kEpiBufs;
@@ -144,16 +152,16 @@ struct Geo {
   static constexpr int kBytes = kStageABytes + kBBytes;
   static constexpr int kBBoxes = kPair ? kBN / 2 / 64 : kBN / 64;   // 64-column boxes of an MN-major B
   static constexpr int kPipeBytes = kNumStages * kBytes;
-  static_assert(kPipeBytes + kEpiWarps * kEpi * kEpiBufBytes <= kSmemPipe + kSmemEpi,
-                "operand ring + staging exceed their shared-memory budget");
+  static_assert(kPipeBytes + kEpiWarps * kEpi * kEpiBufBytes + kBounceBytes <= kSmemPipe + kSmemEpi,
+                "operand ring + staging + bounce ring exceed their shared-memory budget");
 };
 
 }  // namespace
 
-template <bool kPair>
+template <bool kPair, bool kBounce>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
-  using G = Geo<kPair>;
+  using G = Geo<kPair, kBounce>;
   constexpr int kNS = G::kNumStages;
   extern __shared__ uint8_t smem_raw[];
   const uint64_t t_entry = p.trace != 0 ? globaltimer_ns() : 0;
@@ -179,7 +187,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // communication warps poll it to learn which tiles of C they may forward.
   const uint32_t done_count = tmem_slot + 8;
   volatile uint32_t* done_count_g = tmem_slot_g + 2;
-  static_assert(8 * (2 * kNS + 2 * kAccBufs + 1) + 16 <= kSmemCtl, "control block overflow");
+  static_assert(8 * (2 * kNS + 2 * kAccBufs + 1) + 16 <= 200, "control block overflow");
+  const uint32_t smem_bounce = smem_epi + kEpiWarps * G::kEpi * kEpiBufBytes;
+  const uint32_t bar_bounce = smem_ctl + 200;                 // 2 warps x 2 slots x 8 B
+  static_assert(200 + 8 * 2 * kBounceSlotsPerWarp <= kSmemCtl, "control block overflow");
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -197,6 +208,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       mbar_init(bar_acc_empty + 8 * a, kPair ? 2 * kEpiWarps : kEpiWarps);
     }
     mbar_init(bar_drain, 1);
+    if (kBounce)
+      for (int i = 0; i < 2 * kBounceSlotsPerWarp; ++i) mbar_init(bar_bounce + 8 * i, 1);
     *abort_flag = 0;
     *done_count_g = 0;
     mbar_fence_init();
@@ -356,6 +369,54 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   auto ag_push_role = [&](int part) {
     if (p.ag_bytes == 0 || !p.do_ag_push || p.world_size <= 1) return;
     if (!wait_peers_entered()) return;
+    if (kBounce) {
+      // Bulk copies through the bounce ring: local shard -> shared memory -> peer, 8 KB at a
+      // time, two slots per warp.  Destinations go in the order rank-1, rank-2, ...: a
+      // consumer visits the shards in the order own, rank+1, rank+2, ..., so at every moment
+      // each rank receives the shard it needs next from exactly one sender.  A destination's
+      // gate counter is raised as soon as this warp's part for it has landed.
+      if (lane != 0) return;
+      const char* src = reinterpret_cast<const char*>(p.ag_src);
+      const uint64_t n_chunks = (p.ag_bytes + kBounceSlotBytes - 1) / kBounceSlotBytes;
+      const uint32_t my_smem = smem_bounce + part * kBounceSlotsPerWarp * kBounceSlotBytes;
+      const uint32_t my_bar = bar_bounce + part * kBounceSlotsPerWarp * 8;
+      uint32_t use = 0;
+      bool ok = true;
+      for (int k = 1; ok && k < p.world_size; ++k) {
+        const int dest = (p.rank - k + p.world_size) % p.world_size;
+        char* dst = reinterpret_cast<char*>(static_cast<int64_t>(p.ag_dst) +
+                                            static_cast<int64_t>(dest - p.rank) * p.heap_stride);
+        for (uint64_t c = static_cast<uint64_t>(blockIdx.x) * 2 + part; c < n_chunks;
+             c += static_cast<uint64_t>(gridDim.x) * 2) {
+          const uint32_t slot = use % kBounceSlotsPerWarp;
+          const uint32_t phase = (use / kBounceSlotsPerWarp) & 1u;
+          const uint64_t off = c * kBounceSlotBytes;
+          const uint32_t bytes = static_cast<uint32_t>(
+              p.ag_bytes - off < kBounceSlotBytes ? p.ag_bytes - off : kBounceSlotBytes);
+          // the store that last read this slot (kBounceSlotsPerWarp uses ago) is done with it
+          tma_store_wait_read<kBounceSlotsPerWarp - 1>();
+          mbar_expect_tx(my_bar + 8 * slot, bytes);
+          bulk_load(my_smem + slot * kBounceSlotBytes, src + off, bytes, my_bar + 8 * slot);
+          if (!mbar_wait(my_bar + 8 * slot, phase, wb)) {
+            report_status(status, kStatusTimeoutMbarrier, 13, 0, 0, p.rank, static_cast<uint32_t>(c));
+            ok = false;
+            break;
+          }
+          bulk_store(dst + off, my_smem + slot * kBounceSlotBytes, bytes);
+          tma_store_commit();
+          ++use;
+        }
+        tma_store_wait_all<0>();          // this warp's part for `dest` has landed
+        fence_proxy_async_all();
+        if (ok)
+          red_release_sys_add(
+              reinterpret_cast<uint32_t*>(static_cast<int64_t>(p.a_gate) +
+                                          static_cast<int64_t>(dest - p.rank) * p.heap_stride) +
+                  p.rank,
+              1u);
+      }
+      return;
+    }
     constexpr int U = 8;
     const char* src = reinterpret_cast<const char*>(p.ag_src);
     const uint64_t nvec = p.ag_bytes >> 4;
@@ -900,10 +961,13 @@ static cudaError_t launch_fused_gemm_attrs_once() {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 64 && !attr_set[dev]) {
-    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<false>,
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<false, false>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<true>,
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<true, false>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(fused_gemm_sm100_kernel<true, true>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
@@ -914,12 +978,13 @@ static cudaError_t launch_fused_gemm_attrs_once() {
 cudaError_t launch_fused_gemm(const FusedGemmParams& p, int grid, cudaStream_t stream) {
   cudaError_t e = launch_fused_gemm_attrs_once();
   if (e != cudaSuccess) return e;
-  fused_gemm_sm100_kernel<false><<<grid, kThreads, kSmemTotal, stream>>>(p);
+  fused_gemm_sm100_kernel<false, false><<<grid, kThreads, kSmemTotal, stream>>>(p);
   return cudaGetLastError();
 }
 
 // The CTA-pair form: clusters of two CTAs, `grid` even, always the rank's whole tile order.
-cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream) {
+cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStream_t stream,
+                                   bool bounce) {
   cudaError_t e = launch_fused_gemm_attrs_once();
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
@@ -934,14 +999,16 @@ cudaError_t launch_fused_gemm_pair(const FusedGemmParams& p, int grid, cudaStrea
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, fused_gemm_sm100_kernel<true>, p);
+  if (bounce) return cudaLaunchKernelEx(&cfg, fused_gemm_sm100_kernel<true, true>, p);
+  return cudaLaunchKernelEx(&cfg, fused_gemm_sm100_kernel<true, false>, p);
 }
 
 // Forces the module that holds these kernels onto the current device (see tccl_preload_kernels).
 cudaError_t preload_gemm_kernels() {
   cudaFuncAttributes a;
-  cudaError_t e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<false>);
-  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<true>);
+  cudaError_t e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<false, false>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<true, false>);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, fused_gemm_sm100_kernel<true, true>);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, wait_groups_kernel);
   if (e == cudaSuccess) e = launch_fused_gemm_attrs_once();
   return e;

@@ -62,13 +62,13 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
         raise ValueError(f"rows per rank ({mloc}) must be a multiple of {fg.BLOCK_M} so that no "
                          "tile mixes rows of two ranks")
     if use_multimem is None:
-        # One multimem store reaches every peer: from three ranks on the shard leaves this
-        # GPU once instead of ws - 1 times (the spare warps that push it are store-rate
-        # bound).  With two ranks a multicast store also loops back to the sender.
-        use_multimem = (ws > 2 and ctx.heap.has_multicast
-                        and _config().nvls_allowed) or (
-            ws > 1 and ctx.heap.has_multicast
-            and _fused.default_push_mode(ctx) == fg.PUSH_MULTIMEM)
+        # Default: unicast bulk copies through the kernel's bounce ring, destinations ordered
+        # so that every consumer receives the shard it needs next (a multicast store delivers
+        # all shards at the same slow pace, which stalls the GEMM after its own rows).
+        # TILECCL_PUSH_MODE=multimem selects one multimem store per 16 bytes instead.
+        use_multimem = (ws > 1 and ctx.heap.has_multicast and _config().nvls_allowed
+                        and _config().push_mode_explicit
+                        and _fused.default_push_mode(ctx) == fg.PUSH_MULTIMEM)
     key = ("ag_gemm", name, x_full.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K, x_full.dtype,
            epi, b_is_nk, use_multimem)
     st = _fused.op_state(ctx, key)

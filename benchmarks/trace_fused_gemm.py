@@ -73,7 +73,24 @@ def summarize(label, plan, pair, trace, ms, rank, timeline=None):
     crel = (cta - entry0) / 1e3
     crel[cta == 0] = np.nan
     acc_wait, issue, compl, sig = [], [], [], []
-    for b in range(grid):
+    from tileccl_b200.utils.config import current
+
+    dynamic = current().dynamic_tiles
+    if dynamic:
+        # tiles are handed out at run time: no fixed per-CTA sequence to walk, so only the
+        # per-tile sections are summarised (not the wait between a CTA's consecutive tiles)
+        for i in range(n_slots):
+            for w in range(4):
+                a, s1, s2, s3 = rel[i, w]
+                if np.isnan(a):
+                    continue
+                issue.append(s1 - a)
+                if not np.isnan(s2):
+                    compl.append(s2 - s1)
+                    sig.append(s3 - s2)
+                else:
+                    sig.append(s3 - s1)
+    for b in range(0 if dynamic else grid):
         for w in range(4):
             prev = None
             for i in _slots_of_cta(plan, pair, b, n_slots):
@@ -95,12 +112,12 @@ def summarize(label, plan, pair, trace, ms, rank, timeline=None):
 
     out = {
         "label": label, "event_us": round(ms * 1e3, 1), "grid": grid, "pair": pair,
+        "dynamic_tiles": dynamic,
         "cta_entry_spread_us": round(float(np.nanmax(crel[:, 0])), 2),
         "roles_start_us": round(float(np.nanmedian(crel[:, 1])), 2),
         "first_acc_ready_us": round(float(np.nanmin(rel[:, :, 0])), 2),
         "median_first_acc_ready_us": round(float(np.nanmedian(
-            [np.nanmin(rel[_slots_of_cta(plan, pair, b, n_slots)[:1], :, 0]) for b in range(grid)
-             if _slots_of_cta(plan, pair, b, n_slots)])), 2),
+            np.sort(np.nanmin(rel[:, :, 0], axis=1))[:max(1, grid // (2 if pair else 1))])), 2),
         "last_acc_ready_us": round(float(np.nanmax(rel[:, :, 0])), 2),
         "last_stores_issued_us": round(float(np.nanmax(rel[:, :, 1])), 2),
         "last_signal_us": round(float(np.nanmax(rel[:, :, 3])), 2),

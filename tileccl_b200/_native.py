@@ -115,6 +115,8 @@ class GemmDesc(C.Structure):
         ("ident_ptr", C.c_uint64),
         ("disable_cta_pairs", C.c_int32),
         ("comm_ctas", C.c_int32),
+        ("dynamic_tiles", C.c_int32),
+        ("reserved0", C.c_int32),
         ("entry_local", C.c_uint64),
     ]
 

@@ -121,6 +121,8 @@ typedef struct TcclGemmDesc {
   uint64_t ident_ptr;            // reduce-scatter: 128 x 128 identity matrix of the operand dtype (row-major)
   int32_t disable_cta_pairs;     // 1: whole-order launches also run the one-CTA form
   int32_t comm_ctas;             // reserved (0)
+  int32_t dynamic_tiles;         // 1: whole-order launches hand tiles to CTAs from a global counter
+  int32_t reserved0;
   uint64_t entry_local;          // uint32[world_size] "calls entered" counters of this rank on the heap
                                  // (entry handshake of the modes that store into peers' buffers), 0 = off
 } TcclGemmDesc;

@@ -109,6 +109,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same test with acquire semantics at cluster scope: for barriers whose arrival publishes
+// data that another CTA of the cluster wrote into this CTA's shared memory.
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and raises the CTA abort flag) on time-out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitBudget& wb) {
   for (uint32_t it = 0;; ++it) {
@@ -257,6 +270,10 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t smem_addr, uint32_t ran
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 32-bit store into the shared memory of a CTA of the cluster (address from mapa_shared).
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 // One arrival on an mbarrier that lives in another CTA of the cluster.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {

@@ -36,7 +36,9 @@ struct GemmPlan {
   std::vector<cudaEvent_t> events;   // streamed launches: one per run of tiles, + 1
   cudaEvent_t done_event = nullptr;  // end of the last streamed call on its launch stream
   bool streamed_before = false;
+  uint32_t* sched = nullptr;         // dynamic tile scheduler: {next position, exited CTAs}
   ~GemmPlan() {
+    if (sched != nullptr) cudaFree(sched);
     for (cudaEvent_t e : events) cudaEventDestroy(e);
     if (done_event != nullptr) cudaEventDestroy(done_event);
   }
@@ -238,6 +240,11 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     plan->pair_grid = 2 * pairs;
     plan->pair_push_grid = grid & ~1;
   }
+  if (d.dynamic_tiles != 0) {
+    // Two counters that every whole-order launch finds, and leaves, at zero.
+    TCCL_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&plan->sched), 2 * sizeof(uint32_t)));
+    TCCL_CHECK_CUDA(cudaMemset(plan->sched, 0, 2 * sizeof(uint32_t)));
+  }
   info.pair_kernel = plan->pair_kernel ? 1 : 0;
   info.pair_grid = plan->pair_grid;
   // uint64 words a trace buffer must hold: tile slots of the larger form + per-CTA stamps
@@ -289,6 +296,11 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   p.wait_incoming = (flags & 1) ? 1 : 0;
   p.do_ag_push = ag_push ? 1 : 0;
   p.announce_entry = (flags & 8) ? 1 : 0;
+  // Whole-order launches hand tiles out dynamically; tile-range launches (several launches
+  // share one order) keep the fixed round-robin assignment.
+  p.sched_counter = (plan->sched != nullptr && tile_begin == 0 && tile_end == total && total > 0)
+                        ? reinterpret_cast<uint64_t>(plan->sched)
+                        : 0;
   int grid = plan->info.grid;
   if (ag_push) {
     // Every CTA contributes one arrival to the peers' gate counters, so the grid of a

@@ -188,6 +188,13 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   const uint32_t done_count = tmem_slot + 8;
   volatile uint32_t* done_count_g = tmem_slot_g + 2;
   static_assert(8 * (2 * kNS + 2 * kAccBufs + 1) + 16 <= 200, "control block overflow");
+  // Tile-index ring of the dynamic scheduler: the scheduling thread (TMA producer; in a
+  // pair the leader's) publishes positions of the tile order, every other role consumes them.
+  constexpr int kSched = 4;
+  const uint32_t bar_sched_full = smem_ctl + 256;                    // kSched x 8 B
+  const uint32_t bar_sched_empty = bar_sched_full + 8 * kSched;      // kSched x 8 B
+  const uint32_t sched_tile = bar_sched_empty + 8 * kSched;          // kSched x 4 B
+  static_assert(256 + 16 * kSched + 4 * kSched <= kSmemCtl, "control block overflow");
   const uint32_t smem_bounce = smem_epi + kEpiWarps * G::kEpi * kEpiBufBytes;
   const uint32_t bar_bounce = smem_ctl + 200;                 // 2 warps x 2 slots x 8 B
   static_assert(200 + 8 * 2 * kBounceSlotsPerWarp <= kSmemCtl, "control block overflow");
@@ -208,6 +215,12 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       mbar_init(bar_acc_empty + 8 * a, kPair ? 2 * kEpiWarps : kEpiWarps);
     }
     mbar_init(bar_drain, 1);
+    for (int i = 0; i < kSched; ++i) {
+      mbar_init(bar_sched_full + 8 * i, 1);
+      // readers of a slot: MMA thread + four epilogue warps, in a pair those of both CTAs
+      // (the peer's TMA producer reads in place of its idle MMA thread)
+      mbar_init(bar_sched_empty + 8 * i, kPair ? 2 * (1 + kEpiWarps) : 1 + kEpiWarps);
+    }
     if (kBounce)
       for (int i = 0; i < 2 * kBounceSlotsPerWarp; ++i) mbar_init(bar_bounce + 8 * i, 1);
     *abort_flag = 0;
@@ -255,6 +268,45 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   // multimem stores read back from this rank's copy of C) rather than by the epilogue.
   const bool comm_push = p.world_size > 1 && p.push_mode != kPushTma &&
                          (p.mode == kModePushAll || p.mode == kModeAllScatter);
+
+  // ---------------------------- dynamic tile scheduling ----------------------------
+  // SMs do not get equal shares of the link, so with a fixed round-robin assignment the
+  // slowest SMs finish long after the others (and a reduce-scatter owner waits for the
+  // slowest pusher of every TileGroup).  Here positions of the tile order are handed out
+  // one at a time from a global counter instead.
+  const bool dyn = p.sched_counter != 0 && !comm_push;
+  // Scheduling thread: publish position `t` (-1 = no more tiles) as the n-th entry.
+  auto sched_publish = [&](uint32_t n, int t) -> bool {
+    const uint32_t slot = n % kSched, ph = (n / kSched) & 1u;
+    if (!mbar_wait(bar_sched_empty + 8 * slot, ph ^ 1u, wb)) return false;
+    st_shared_cluster_u32(kPair ? mapa_shared(sched_tile + 4 * slot, 0) : sched_tile + 4 * slot,
+                          static_cast<uint32_t>(t));
+    if (kPair) {
+      st_shared_cluster_u32(mapa_shared(sched_tile + 4 * slot, 1), static_cast<uint32_t>(t));
+      mbar_arrive_cluster(mapa_shared(bar_sched_full + 8 * slot, 0));
+      mbar_arrive_cluster(mapa_shared(bar_sched_full + 8 * slot, 1));
+    } else {
+      mbar_arrive(bar_sched_full + 8 * slot);
+    }
+    return true;
+  };
+  // Any other role (one thread per role): the n-th entry; -2 when the wait gave up.
+  auto sched_consume = [&](uint32_t n) -> int {
+    const uint32_t slot = n % kSched, ph = (n / kSched) & 1u;
+    for (uint32_t it = 0;; ++it) {
+      if (mbar_try_wait_cluster(bar_sched_full + 8 * slot, ph)) break;
+      if (wb.expired(it)) { *abort_flag = 1; return -2; }
+    }
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(sched_tile + 4 * slot) : "memory");
+    if (kPair) mbar_arrive_cluster(mapa_shared(bar_sched_empty + 8 * slot, 0));
+    else mbar_arrive(bar_sched_empty + 8 * slot);
+    return static_cast<int>(v);
+  };
+  auto sched_fetch = [&]() -> int {
+    const uint32_t v = atomicAdd(reinterpret_cast<uint32_t*>(p.sched_counter), 1u);
+    return v < static_cast<uint32_t>(tile_end) ? static_cast<int>(v) : -1;
+  };
 
   // Entry handshake (see FusedGemmParams::entry_local).  Warp-collective: lane d polls
   // peer d's "entered" word; returns false (status 45) when a peer never shows up.
@@ -463,7 +515,24 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       tma_prefetch_desc(&p.tma_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = first; ok && t < tile_end; t += step) {
+      for (uint32_t n_seq = 0; ok; ++n_seq) {
+        int t;
+        if (dyn) {
+          if (leader) {
+            t = sched_fetch();
+            if (!sched_publish(n_seq, t)) {
+              report_status(status, kStatusTimeoutMbarrier, 14, 0, 0, p.rank, n_seq);
+              ok = false;
+              break;
+            }
+          } else {
+            t = sched_consume(n_seq);
+          }
+          if (t < 0) break;
+        } else {
+          t = first + static_cast<int>(n_seq) * step;
+          if (t >= tile_end) break;
+        }
         const TileCoord c = decode_tile<kPair>(p, t, cta);
         if (p.a_gate != 0 && c.valid) {
           // Rows of A written by a peer: wait for that peer's arrival counter.
@@ -599,7 +668,15 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int t = first; ok && t < tile_end; t += step) {
+      for (uint32_t n_seq = 0; ok; ++n_seq) {
+        int t;
+        if (dyn) {
+          t = sched_consume(n_seq);
+          if (t < 0) break;
+        } else {
+          t = first + static_cast<int>(n_seq) * step;
+          if (t >= tile_end) break;
+        }
         if (!mbar_wait(bar_acc_empty + 8 * acc, acc_phase ^ 1u, wb)) {
           report_status(status, kStatusTimeoutMbarrier, 20, 0, 0, p.rank, t);
           ok = false;
@@ -712,7 +789,17 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           add(peer_counter(p, (p.rank + d) % p.world_size, p.rank, g));
       }
     };
-    for (int t = first; ok && t < tile_end; t += step) {
+    for (uint32_t n_seq = 0; ok; ++n_seq) {
+      int t;
+      if (dyn) {
+        t = 0;
+        if (lane == 0) t = sched_consume(n_seq);
+        t = __shfl_sync(0xffffffffu, t, 0);
+        if (t < 0) break;
+      } else {
+        t = first + static_cast<int>(n_seq) * step;
+        if (t >= tile_end) break;
+      }
       const TileCoord c = decode_tile<kPair>(p, t, cta);
       const int group = c.lm / p.group_m_tiles;
       const bool reduce_here = p.mode == kModeReduceScatter && c.owner == p.rank;
@@ -921,6 +1008,15 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   tcgen05_fence_before();
   __syncthreads();
   if (trace_cta != nullptr && threadIdx.x == 0) trace_cta[3] = globaltimer_ns();
+  if (p.sched_counter != 0 && threadIdx.x == 0) {
+    // The last CTA to get here leaves the scheduler's counters at zero for the next launch.
+    uint32_t* sc = reinterpret_cast<uint32_t*>(p.sched_counter);
+    if (atomicAdd(sc + 1, 1u) == gridDim.x - 1) {
+      sc[0] = 0;
+      sc[1] = 0;
+      __threadfence();
+    }
+  }
   if (kPair) cluster_sync_all();
   if (warp == 2) {
     tcgen05_fence_after();

@@ -25,7 +25,7 @@ static constexpr int kEpiBufBytes = kSlabM * kChunkN * 2;  // 4 KiB per (warp, b
 static constexpr int kEpiBufs = 2;
 static constexpr int kSmemPipe = kStages * kStageBytes;
 static constexpr int kSmemEpi = kEpiWarps * kEpiBufs * kEpiBufBytes;
-static constexpr int kSmemCtl = 256;
+static constexpr int kSmemCtl = 512;
 static constexpr int kSmemTotal = kSmemPipe + kSmemEpi + kSmemCtl + 1024;  // + alignment slack
 
 static constexpr int kMaxRanks = 8;
@@ -111,6 +111,10 @@ struct alignas(64) FusedGemmParams {
   int32_t announce_entry;             // this launch is the first of its call: announce it
   // column slice pushed by all-scatter
   int32_t scatter_col_begin, scatter_col_end;
+  // Dynamic tile scheduling (launches that run the rank's whole tile order): uint32[2] in
+  // device memory, {next position in the tile order, CTAs that have exited}; both are zero
+  // between launches (the last CTA to exit resets them).  0 = static round-robin.
+  uint64_t sched_counter;
   // diagnostics
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;

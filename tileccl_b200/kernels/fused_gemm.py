@@ -190,6 +190,7 @@ class FusedGemmPlan:
         cfg = _config()
         d.tuning = spec.tuning if spec.tuning >= 0 else cfg.tuning
         d.disable_cta_pairs = 0 if cfg.gemm_cta_pairs else 1
+        d.dynamic_tiles = 1 if cfg.dynamic_tiles else 0
         d.wait_budget_ns = spec.wait_budget_ns
         d.entry_local = spec.entry_local
         handle = C.c_void_p()

@@ -245,3 +245,28 @@ def test_nvlink_facts_from_a_fake_nvml():
             return 0
 
     assert nvlink_facts(0, nvml=Down()) is None
+
+
+def test_pattern_options_select_the_launch_shape_or_are_rejected():
+    """COMM_SMS / COMPUTE_SMS are honoured by the two-kernel patterns and rejected where the
+    communication role is a set of warps inside every compute CTA."""
+    from types import SimpleNamespace as NS
+
+    from tileccl_b200.patterns import (BulkSyncPattern, FusedSequentialPattern,
+                                       ProducerConsumerPattern, WGSpecializedPattern)
+
+    ctx = NS(rank=0, world_size=2, backend=None)
+    pc = ProducerConsumerPattern(ctx, COMPUTE_SMS=120, COMM_SMS=24)
+    shape = pc.launch_shape()
+    assert (shape.compute_sms, shape.comm_sms, shape.policy) == (120, 24, "two_kernels")
+    assert BulkSyncPattern(ctx).launch_shape().comm_sms == 32            # default push grid
+    wg = WGSpecializedPattern(ctx, COMPUTE_SMS=96, BLOCK_M=128, BLOCK_N=128, BLOCK_K=64)
+    assert wg.launch_shape().compute_sms == 96 and wg.launch_shape().comm_sms == 0
+    with pytest.raises(ValueError, match="COMM_SMS"):
+        WGSpecializedPattern(ctx, COMM_SMS=16)
+    with pytest.raises(ValueError, match="COMM_SMS"):
+        FusedSequentialPattern(ctx, COMPUTE_SMS=100, COMM_SMS=48)
+    with pytest.raises(ValueError, match="128 x 256 x 64"):
+        WGSpecializedPattern(ctx, BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
+    with pytest.raises(TypeError):
+        WGSpecializedPattern(ctx, FANCY=1)

@@ -130,6 +130,7 @@ class FusedGemmSpec:
     ident_ptr: int = 0          # reduce-scatter: 128 x 128 identity of `dtype` (see identity_operand)
     wait_budget_ns: int = 0
     entry_local: int = 0        # uint32[world_size] entry-handshake counters on the heap (0 = off)
+    cta_pairs: Optional[bool] = None   # kernel form of whole-order launches (None: TILECCL_GEMM_2SM)
 
 
 def count_launches(n: int) -> None:
@@ -189,7 +190,8 @@ class FusedGemmPlan:
         d.ident_ptr = spec.ident_ptr
         cfg = _config()
         d.tuning = spec.tuning if spec.tuning >= 0 else cfg.tuning
-        d.disable_cta_pairs = 0 if cfg.gemm_cta_pairs else 1
+        pairs = cfg.gemm_cta_pairs if spec.cta_pairs is None else (spec.cta_pairs and cfg.gemm_cta_pairs)
+        d.disable_cta_pairs = 0 if pairs else 1
         d.dynamic_tiles = 1 if cfg.dynamic_tiles else 0
         d.wait_budget_ns = spec.wait_budget_ns
         d.entry_local = spec.entry_local

@@ -598,7 +598,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
 # --------------------------------------------------------------------------
 def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
                 col_begin: int, col_end: int, b_is_nk: bool = False,
-                push_mode: Optional[int] = None, wait: bool = True) -> None:
+                push_mode: Optional[int] = None, wait: bool = True, grid: int = 0) -> None:
     _require_2d("A", A, ctx)
     _require_2d("B", B, ctx)
     _require_2d("C", C, ctx)
@@ -609,7 +609,7 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
         raise ValueError("C must be allocated from the symmetric heap (ctx.zeros / ctx.empty)")
     push_mode = default_push_mode(ctx) if push_mode is None else push_mode
     key = ("all_scatter", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
-           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, push_mode)
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, push_mode, grid)
     st = op_state(ctx, key)
     m_tiles = -(-M // fg.BLOCK_M)
     gm = default_group_m_tiles(m_tiles, -(-N // fg.BLOCK_N), A.element_size())
@@ -630,7 +630,7 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
             out_cols=N, b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws,
             out_mc_ptr=mc, group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride,
             sig_stride=MAX_GROUPS, scatter_col_begin=col_begin, scatter_col_end=col_end,
-            entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0,
+            entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0, grid=grid,
             status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
         plan = st["plan"]
         if ws > 1:
@@ -666,7 +666,8 @@ def _comm_stream(ctx) -> torch.cuda.Stream:
 
 def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, *,
                    col_begin: int, col_end: int, overlapped: bool, b_is_nk: bool = False,
-                   use_multimem: Optional[bool] = None) -> None:
+                   use_multimem: Optional[bool] = None, gemm_grid: int = 0,
+                   push_grid: int = 0) -> None:
     """All-scatter as two kernels: ``C = A @ B`` locally, then columns
     ``[col_begin, col_end)`` of ``C`` are copied to every peer.
 
@@ -687,7 +688,7 @@ def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     if ws > 1 and (width <= 0 or (width * C.element_size()) % 16 or (col_begin * C.element_size()) % 16):
         raise ValueError("the pushed column slice must start and end on 16-byte boundaries")
     key = ("gemm_then_push", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
-           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, overlapped)
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, col_begin, col_end, overlapped, gemm_grid)
     st = op_state(ctx, key)
     m_tiles = -(-M // fg.BLOCK_M)
     shared = op_state(ctx, ("gemm_then_push:sig", name, M, N, K, overlapped))
@@ -702,7 +703,7 @@ def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             mode=fg.MODE_GEMM, dtype=A.dtype, a_ptr=A.data_ptr(), a_rows=M, lda=A.stride(0),
             b_ptr=B.data_ptr(), b_cols=N, ldb=B.stride(0), k=K, sub_m=M, sub_n=N,
             out_ptrs=[C.data_ptr()], ldo=C.stride(0), out_rows=M, out_cols=N, b_kmajor=b_is_nk,
-            rank=rank, world_size=ws, group_m_tiles=1,
+            rank=rank, world_size=ws, group_m_tiles=1, grid=gemm_grid,
             sig_local=bands.data_ptr() if (bands is not None and ws > 1) else 0,
             sig_stride=m_tiles, status_ptr=status_block(ctx).data_ptr(),
             wait_budget_ns=wait_budget_ns()))
@@ -719,7 +720,7 @@ def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     bands = shared.get("bands")
     band_ready = bands.data_ptr() if bands is not None else 0
     per_band = plan.n_tiles_local * fg.EPILOGUE_SLABS
-    grid = max(1, min(m_tiles, 32))
+    grid = max(1, min(m_tiles, push_grid or 32))
     counters = shared["counters"].data_ptr()
     status = status_block(ctx).data_ptr()
 

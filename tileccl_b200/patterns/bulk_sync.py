@@ -9,6 +9,8 @@ from ._impl import run_two_kernel
 
 class BulkSyncPattern(Pattern):
     name = "bulk_sync"
+    split = "kernels"
 
     def _run(self, A, B, C, spec) -> None:
-        run_two_kernel(self.ctx, self.name, A, B, C, spec, overlapped=False)
+        run_two_kernel(self.ctx, self.name, A, B, C, spec, overlapped=False,
+                       shape=self.launch_shape())

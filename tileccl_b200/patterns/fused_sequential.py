@@ -11,4 +11,5 @@ class FusedSequentialPattern(Pattern):
     name = "fused_sequential"
 
     def _run(self, A, B, C, spec) -> None:
-        run_fused(self.ctx, self.name, A, B, C, spec, pick_push_mode(self.ctx, fg.PUSH_STORES))
+        run_fused(self.ctx, self.name, A, B, C, spec, pick_push_mode(self.ctx, fg.PUSH_STORES),
+                  shape=self.launch_shape())

@@ -9,6 +9,8 @@ from ._impl import run_two_kernel
 
 class ProducerConsumerPattern(Pattern):
     name = "producer_consumer"
+    split = "kernels"
 
     def _run(self, A, B, C, spec) -> None:
-        run_two_kernel(self.ctx, self.name, A, B, C, spec, overlapped=True)
+        run_two_kernel(self.ctx, self.name, A, B, C, spec, overlapped=True,
+                       shape=self.launch_shape())

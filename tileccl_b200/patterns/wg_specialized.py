@@ -14,4 +14,5 @@ class WGSpecializedPattern(Pattern):
     name = "wg_specialized"
 
     def _run(self, A, B, C, spec) -> None:
-        run_fused(self.ctx, self.name, A, B, C, spec, pick_push_mode(self.ctx, fg.PUSH_TMA))
+        run_fused(self.ctx, self.name, A, B, C, spec, pick_push_mode(self.ctx, fg.PUSH_TMA),
+                  shape=self.launch_shape())

@@ -229,3 +229,26 @@ def test_fused_kernel_abort_path_then_normal_call(ctxs, monkeypatch):
     run_all()
     for r in range(ws):
         assert _rel(C[r].cpu(), full[r * M // ws:(r + 1) * M // ws]) < TOL[dtype]
+
+
+def test_call_stats_count_bytes_signals_and_tiles(ctxs):
+    """Per-call counters of the fused kernel: bytes stored into peers, signals, tiles."""
+    from tileccl_b200 import ops
+
+    ws, dtype = len(ctxs), torch.float16
+    M, N, K = 256 * ws, 512, 128
+    A = [_randn(c, M // ws, K, dtype, K ** -0.5) for c in ctxs]
+    B = [_randn(c, K, N, dtype) for c in ctxs]
+    C = [c.zeros(M, N, dtype=dtype) for c in ctxs]
+    for c in ctxs:
+        ops.call_stats(c)                                  # clear
+    for r, c in enumerate(ctxs):
+        ops.gemm_allgather_rows(A[r], B[r], C[r], ctx=c)
+    for c in ctxs:
+        ops.check_status(c)
+    for c in ctxs:
+        st = ops.call_stats(c)
+        assert st["bytes_pushed"] == (ws - 1) * (M // ws) * N * 2
+        assert st["tiles"] == 2 * (N // 256)               # 256 rows per rank = 2 tile rows
+        assert st["signals_sent"] == (ws - 1) * st["tiles"] * 4   # one per 32-row slab and peer
+        assert ops.call_stats(c)["bytes_pushed"] == 0      # reading resets

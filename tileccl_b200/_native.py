@@ -107,6 +107,7 @@ class GemmDesc(C.Structure):
         ("scatter_col_begin", C.c_int32),
         ("scatter_col_end", C.c_int32),
         ("grid", C.c_int32),
+        ("stats", C.c_uint64),
         ("status", C.c_uint64),
         ("trace", C.c_uint64),
         ("wait_budget_ns", C.c_uint64),

@@ -36,7 +36,12 @@ struct GemmPlan {
   std::vector<cudaEvent_t> events;   // streamed launches: one per run of tiles, + 1
   cudaEvent_t done_event = nullptr;  // end of the last streamed call on its launch stream
   bool streamed_before = false;
-  uint32_t* sched = nullptr;         // dynamic tile scheduler: {next position, exited CTAs}
+  // Dynamic tile scheduler: {next position, exited CTAs}.  Allocated at the first
+  // whole-order launch, on the device that launch runs on (a plan may be built while another
+  // device is current, e.g. one process driving several GPUs).
+  bool want_sched = false;
+  uint32_t* sched = nullptr;
+  int sched_device = -1;
   ~GemmPlan() {
     if (sched != nullptr) cudaFree(sched);
     for (cudaEvent_t e : events) cudaEventDestroy(e);
@@ -193,6 +198,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
   p.scatter_col_begin = d.scatter_col_begin;
   p.scatter_col_end = d.scatter_col_end;
   p.status = d.status;
+  p.stats = d.stats;
   p.trace = d.trace;
   p.tuning = d.tuning;
   TCCL_CHECK_ARG(d.rs_own_lag >= 0, "rs_own_lag must be >= 0");
@@ -240,11 +246,7 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     plan->pair_grid = 2 * pairs;
     plan->pair_push_grid = grid & ~1;
   }
-  if (d.dynamic_tiles != 0) {
-    // Two counters that every whole-order launch finds, and leaves, at zero.
-    TCCL_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&plan->sched), 2 * sizeof(uint32_t)));
-    TCCL_CHECK_CUDA(cudaMemset(plan->sched, 0, 2 * sizeof(uint32_t)));
-  }
+  plan->want_sched = d.dynamic_tiles != 0;
   info.pair_kernel = plan->pair_kernel ? 1 : 0;
   info.pair_grid = plan->pair_grid;
   // uint64 words a trace buffer must hold: tile slots of the larger form + per-CTA stamps
@@ -298,9 +300,21 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   p.announce_entry = (flags & 8) ? 1 : 0;
   // Whole-order launches hand tiles out dynamically; tile-range launches (several launches
   // share one order) keep the fixed round-robin assignment.
-  p.sched_counter = (plan->sched != nullptr && tile_begin == 0 && tile_end == total && total > 0)
-                        ? reinterpret_cast<uint64_t>(plan->sched)
-                        : 0;
+  p.sched_counter = 0;
+  if (plan->want_sched && tile_begin == 0 && tile_end == total && total > 0) {
+    int dev = -1;
+    TCCL_CHECK_CUDA(cudaGetDevice(&dev));
+    if (plan->sched == nullptr) {
+      // Two counters that every whole-order launch finds, and leaves, at zero.
+      TCCL_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&plan->sched), 2 * sizeof(uint32_t)));
+      TCCL_CHECK_CUDA(cudaMemset(plan->sched, 0, 2 * sizeof(uint32_t)));
+      plan->sched_device = dev;
+    }
+    TCCL_CHECK_ARG(dev == plan->sched_device,
+                   "this plan was first launched on device " << plan->sched_device
+                                                             << " and cannot move to device " << dev);
+    p.sched_counter = reinterpret_cast<uint64_t>(plan->sched);
+  }
   int grid = plan->info.grid;
   if (ag_push) {
     // Every CTA contributes one arrival to the peers' gate counters, so the grid of a

@@ -269,6 +269,14 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
   const bool comm_push = p.world_size > 1 && p.push_mode != kPushTma &&
                          (p.mode == kModePushAll || p.mode == kModeAllScatter);
 
+  // Per-call counters (FusedGemmParams::stats): each role keeps its own sums in registers and
+  // adds them once, when it is done.
+  auto stat_add = [&](int word, uint64_t v) {
+    if (p.stats != 0 && v != 0)
+      atomicAdd(reinterpret_cast<unsigned long long*>(p.stats) + word,
+                static_cast<unsigned long long>(v));
+  };
+
   // ---------------------------- dynamic tile scheduling ----------------------------
   // SMs do not get equal shares of the link, so with a fixed round-robin assignment the
   // slowest SMs finish long after the others (and a reduce-scatter owner waits for the
@@ -515,6 +523,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       tma_prefetch_desc(&p.tma_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      uint64_t peer_wait_ns = 0, n_tiles_done = 0;
       for (uint32_t n_seq = 0; ok; ++n_seq) {
         int t;
         if (dyn) {
@@ -534,13 +543,17 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           if (t >= tile_end) break;
         }
         const TileCoord c = decode_tile<kPair>(p, t, cta);
+        n_tiles_done += kPair ? 2 : 1;
         if (p.a_gate != 0 && c.valid) {
           // Rows of A written by a peer: wait for that peer's arrival counter.
           int src = c.a_row0 / p.a_gate_rows_per_rank;
           if (src != p.rank) {
             uint32_t seen = 0;
-            if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.a_gate) + src, p.a_gate_target,
-                              wb, &seen)) {
+            const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+            const bool arrived = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.a_gate) + src,
+                                              p.a_gate_target, wb, &seen);
+            if (p.stats != 0) peer_wait_ns += globaltimer_ns() - w0;
+            if (!arrived) {
               report_status(status, kStatusTimeoutSignal, 10, p.a_gate_target, seen, p.rank, t);
               *abort_flag = 1;
               ok = false;
@@ -601,8 +614,11 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
                 p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
                                                 p.n_tiles_local * kEpiWarps);
             uint32_t seen = 0;
-            if (!tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group, target, wb,
-                              &seen)) {
+            const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+            const bool arrived = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group,
+                                              target, wb, &seen);
+            if (p.stats != 0) peer_wait_ns += globaltimer_ns() - w0;
+            if (!arrived) {
               report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
               *abort_flag = 1;
               ok = false;
@@ -645,6 +661,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           }
         }
       }
+      stat_add(2, peer_wait_ns);
+      stat_add(3, leader ? n_tiles_done : 0);
       if (!ok) {
         // Let loads that are still in flight land before the CTA retires.
         for (int s = 0; s < kNS; ++s)
@@ -741,7 +759,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         const uint32_t target =
             p.epoch * static_cast<uint32_t>(group_m_count(p, g) * p.n_tiles_local * kEpiWarps);
         uint32_t seen = 0;
-        if (!tile_wait_ge(sig + src * p.sig_stride + g, target, wb, &seen)) {
+        const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+        const bool arrived = tile_wait_ge(sig + src * p.sig_stride + g, target, wb, &seen);
+        if (p.stats != 0) stat_add(2, globaltimer_ns() - w0);
+        if (!arrived) {
           report_status(status, kStatusTimeoutSignal, 30, target, seen, p.rank, i);
           break;
         }
@@ -761,6 +782,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     bool ok = true;
     // Peer copies issued by this warp (bulk stores) must not start before the peers have
     // entered this call; checked once, right before the first of them.
+    uint64_t bytes_pushed = 0, signals_sent = 0;     // lane 0 only
     bool peers_entered = !(p.world_size > 1 && p.push_mode == kPushTma && p.entry_local != 0 &&
                            (p.mode == kModePushAll || p.mode == kModeAllScatter));
     // lane 0: the last kPend tiles whose signals have not been sent yet ([0] = oldest)
@@ -777,6 +799,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
     auto send_signal = [&](int owner, int g, bool after_bulk) {
       const bool relaxed = after_bulk && (p.tuning & kTuneRelaxedSignalAfterBulk) != 0;
       auto add = [&](uint32_t* ctr) {
+        ++signals_sent;
         if (relaxed)
           asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(ctr), "r"(1u) : "memory");
         else
@@ -888,7 +911,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           // Partial tile -> owner's staging slot for (parity, this rank).
           const int z = p.stage_parity * p.world_size + p.rank;
           if (p.push_mode == kPushTma) {
-            if (lane == 0) tma_store_3d(&p.tma_out[c.owner], col0, y, z, sbuf);
+            if (lane == 0) {
+              tma_store_3d(&p.tma_out[c.owner], col0, y, z, sbuf);
+              bytes_pushed += kEpiBufBytes;
+            }
           } else {
             char* dst = reinterpret_cast<char*>(p.out_ptr[c.owner]) +
                         static_cast<int64_t>(z) * p.out_slot_bytes;
@@ -918,9 +944,11 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
               }
               peers_entered = true;
             }
-            if (lane == 0)
+            if (lane == 0) {
               for (int d = 1; d < p.world_size; ++d)
                 tma_store_3d(&p.tma_out[(p.rank + d) % p.world_size], col0, y, 0, sbuf);
+              bytes_pushed += static_cast<uint64_t>(p.world_size - 1) * kEpiBufBytes;
+            }
           }
         }
         if (lane == 0) tma_store_commit();
@@ -1000,6 +1028,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       for (int i = 0; i < kPend; ++i)
         if (pend_valid[i]) send_signal(pend_owner[i], pend_group[i], true);
       if (trace_cta != nullptr) trace_cta[4 + q] = globaltimer_ns();
+      stat_add(0, bytes_pushed);
+      stat_add(1, signals_sent);
     }
   }
 

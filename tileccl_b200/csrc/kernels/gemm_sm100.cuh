@@ -29,6 +29,7 @@ static constexpr int kSmemCtl = 512;
 static constexpr int kSmemTotal = kSmemPipe + kSmemEpi + kSmemCtl + 1024;  // + alignment slack
 
 static constexpr int kMaxRanks = 8;
+static constexpr int kStatWords = 8;
 
 enum GemmMode : int {
   kModeGemm = 0,       // out[0] = A @ B
@@ -116,6 +117,10 @@ struct alignas(64) FusedGemmParams {
   // between launches (the last CTA to exit resets them).  0 = static round-robin.
   uint64_t sched_counter;
   // diagnostics
+  // optional uint64[kStatWords] counters, added to by every launch (host reads and clears):
+  // [0] bytes stored into peers' memory  [1] TileGroup signals sent  [2] ns spent waiting for
+  // peers (TileGroup / gate / entry counters, summed over waiting threads)  [3] tiles computed
+  uint64_t stats;
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;
   // optional uint64[trace_tile_slots][4 epilogue warps][4] (accumulator ready / stores

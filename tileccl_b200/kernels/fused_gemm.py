@@ -37,6 +37,7 @@ EPILOGUE_SLABS = 4  # one signal increment per 32-row slab of a tile
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
 STATUS_WORDS = 8
+STAT_WORDS = 8
 
 # Kernel launches issued through this module since import (benchmarks report it).
 LAUNCH_COUNT = 0
@@ -124,6 +125,7 @@ class FusedGemmSpec:
     scatter_col_end: int = 0
     grid: int = 0
     status_ptr: int = 0
+    stats_ptr: int = 0          # uint64[8] per-call counters (see ops.call_stats), 0 = off
     trace_ptr: int = 0
     tuning: int = -1            # -1: TILECCL_TUNING from the environment (default 1)
     rs_own_lag: int = 0         # reduce-scatter: rounds the own tile rows trail (0 = all last)
@@ -185,6 +187,7 @@ class FusedGemmPlan:
         d.scatter_col_begin, d.scatter_col_end = spec.scatter_col_begin, spec.scatter_col_end
         d.grid = spec.grid
         d.status = spec.status_ptr
+        d.stats = spec.stats_ptr if _config().call_stats else 0
         d.trace = spec.trace_ptr
         d.rs_own_lag = spec.rs_own_lag
         d.ident_ptr = spec.ident_ptr

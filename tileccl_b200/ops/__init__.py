@@ -26,7 +26,7 @@ from typing import Any, Optional
 import torch
 
 from . import _fused
-from ._fused import check_status, recover
+from ._fused import call_stats, check_status, recover
 from ..kernels.fused_gemm import TileCCLTimeoutError
 
 __all__ = [
@@ -41,7 +41,7 @@ __all__ = [
     "ReduceScatterPlan",
     "GemmAllScatterContract", "GemmAllGatherContract", "GemmReduceScatterContract",
     "AllGatherGemmReduceScatterContract",
-    "check_status", "recover", "TileCCLTimeoutError",
+    "check_status", "recover", "call_stats", "TileCCLTimeoutError",
 ]
 
 _STORAGE_KINDS = ("symmetric",)

@@ -52,6 +52,29 @@ def status_block(ctx) -> torch.Tensor:
     return st
 
 
+def stats_block(ctx) -> torch.Tensor:
+    """uint64[8] device words every fused launch of this context adds its counters to."""
+    st = ctx._state.get("stats")
+    if st is None:
+        st = torch.zeros(fg.STAT_WORDS, dtype=torch.int64, device=ctx.torch_device)
+        ctx._state["stats"] = st
+    return st
+
+
+def call_stats(ctx, reset: bool = True) -> dict:
+    """Counters accumulated by the fused kernels of this context since the last reset
+    (synchronises the device): bytes stored into peers' memory, TileGroup signals sent,
+    nanoseconds spent waiting for peers (summed over the waiting threads) and tiles computed."""
+    st = ctx._state.get("stats")
+    if st is None:
+        return {"bytes_pushed": 0, "signals_sent": 0, "peer_wait_ns": 0, "tiles": 0}
+    torch.cuda.synchronize(ctx.torch_device)
+    w = st.cpu().tolist()
+    if reset:
+        st.zero_()
+    return {"bytes_pushed": w[0], "signals_sent": w[1], "peer_wait_ns": w[2], "tiles": w[3]}
+
+
 def check_status(ctx) -> None:
     """Synchronise and raise :class:`TileCCLTimeoutError` if any kernel gave up waiting."""
     st = ctx._state.get("status")
@@ -442,7 +465,7 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
             b_kmajor=b_is_nk, push_mode=push_mode, rank=rank, world_size=ws, out_mc_ptr=mc,
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
             entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0,
-            status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
+            status_ptr=status_block(ctx).data_ptr(), stats_ptr=stats_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
         plan = st["plan"]
         if ws > 1:
             per_epoch = [plan.group_m_count(g) * plan.n_tiles_local * fg.EPILOGUE_SLABS
@@ -565,7 +588,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             rs_own_lag=(default_rs_own_lag(ws, m_tiles, -(-sub_n // fg.BLOCK_N))
                         if ws > 1 and _in_kernel_waits_ok(ctx) else 0),
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
-            stage_local=stage_ptr, status_ptr=status_block(ctx).data_ptr(),
+            stage_local=stage_ptr, status_ptr=status_block(ctx).data_ptr(), stats_ptr=stats_block(ctx).data_ptr(),
             wait_budget_ns=wait_budget_ns()))
     plan = st["plan"]
     if ctx.local_group is None and "fast" not in st:
@@ -631,7 +654,7 @@ def all_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tenso
             out_mc_ptr=mc, group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride,
             sig_stride=MAX_GROUPS, scatter_col_begin=col_begin, scatter_col_end=col_end,
             entry_local=entry_ptr(ctx, sigst) if ws > 1 else 0, grid=grid,
-            status_ptr=status_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
+            status_ptr=status_block(ctx).data_ptr(), stats_ptr=stats_block(ctx).data_ptr(), wait_budget_ns=wait_budget_ns()))
         plan = st["plan"]
         if ws > 1:
             # A tile signals once per slab whether or not it overlaps the pushed slice, so the
@@ -705,7 +728,7 @@ def gemm_then_push(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             out_ptrs=[C.data_ptr()], ldo=C.stride(0), out_rows=M, out_cols=N, b_kmajor=b_is_nk,
             rank=rank, world_size=ws, group_m_tiles=1, grid=gemm_grid,
             sig_local=bands.data_ptr() if (bands is not None and ws > 1) else 0,
-            sig_stride=m_tiles, status_ptr=status_block(ctx).data_ptr(),
+            sig_stride=m_tiles, status_ptr=status_block(ctx).data_ptr(), stats_ptr=stats_block(ctx).data_ptr(),
             wait_budget_ns=wait_budget_ns()))
     plan = st["plan"]
     if ws == 1:

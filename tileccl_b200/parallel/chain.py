@@ -82,7 +82,8 @@ def rows_allgather_gemm(ctx, name: str, x_full: torch.Tensor, W: torch.Tensor,
             sub_n=N, out_ptrs=[out.data_ptr()], ldo=out.stride(0), out_rows=M, out_cols=n_out,
             b_kmajor=b_is_nk, epi_op=epi, rank=rank, world_size=ws,
             rot_m_tiles=(rank * mloc) // fg.BLOCK_M if ws > 1 else 0,
-            status_ptr=_fused.status_block(ctx).data_ptr(), wait_budget_ns=_fused.wait_budget_ns())
+            status_ptr=_fused.status_block(ctx).data_ptr(),
+            stats_ptr=_fused.stats_block(ctx).data_ptr(), wait_budget_ns=_fused.wait_budget_ns())
         if ws > 1:
             spec.heap_stride = ctx.heap.stride
             spec.a_gate = gate["gate"].data_ptr()

@@ -31,6 +31,7 @@ class RuntimeConfig:
     push_mode: str = "tma"                 # TILECCL_PUSH_MODE: tma | stores | multimem
     tuning: int = 1                        # TILECCL_TUNING: bit 0 = relaxed signal after a completed bulk store
     gemm_cta_pairs: bool = True            # TILECCL_GEMM_2SM: whole-order launches on CTA pairs
+    call_stats: bool = True                # TILECCL_STATS: fused kernels add per-call counters (ops.call_stats)
     dynamic_tiles: bool = True             # TILECCL_DYNAMIC_TILES: tiles handed to CTAs from a global counter
     rs_own_lag: Optional[int] = None       # TILECCL_RS_OWN_LAG: rounds the own rows trail (None = heuristic)
     wait_budget_us: Optional[float] = None  # TILECCL_WAIT_BUDGET_US: budget of every device wait (None = 2 s)
@@ -61,6 +62,7 @@ class RuntimeConfig:
             push_mode=push,
             tuning=int(e.get("TILECCL_TUNING") or 1),
             gemm_cta_pairs=_flag(e, "TILECCL_GEMM_2SM", True),
+            call_stats=_flag(e, "TILECCL_STATS", True),
             dynamic_tiles=_flag(e, "TILECCL_DYNAMIC_TILES", True),
             rs_own_lag=_opt_int(e, "TILECCL_RS_OWN_LAG"),
             wait_budget_us=float(budget) if budget not in (None, "") else None,

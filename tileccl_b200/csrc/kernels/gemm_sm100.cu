@@ -523,7 +523,8 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       tma_prefetch_desc(&p.tma_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      uint64_t peer_wait_ns = 0, n_tiles_done = 0;
+      uint64_t peer_wait_clk = 0, n_tiles_done = 0;   // (the SM cycle counter: a %globaltimer
+                                                      // read costs about a microsecond)
       for (uint32_t n_seq = 0; ok; ++n_seq) {
         int t;
         if (dyn) {
@@ -549,10 +550,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           int src = c.a_row0 / p.a_gate_rows_per_rank;
           if (src != p.rank) {
             uint32_t seen = 0;
-            const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+            const long long w0 = clock64();
             const bool arrived = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.a_gate) + src,
                                               p.a_gate_target, wb, &seen);
-            if (p.stats != 0) peer_wait_ns += globaltimer_ns() - w0;
+            peer_wait_clk += static_cast<uint64_t>(clock64() - w0);
             if (!arrived) {
               report_status(status, kStatusTimeoutSignal, 10, p.a_gate_target, seen, p.rank, t);
               *abort_flag = 1;
@@ -614,10 +615,10 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
                 p.epoch * static_cast<uint32_t>((p.world_size - 1) * group_m_count(p, group) *
                                                 p.n_tiles_local * kEpiWarps);
             uint32_t seen = 0;
-            const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+            const long long w0 = clock64();
             const bool arrived = tile_wait_ge(reinterpret_cast<const uint32_t*>(p.sig_local) + group,
                                               target, wb, &seen);
-            if (p.stats != 0) peer_wait_ns += globaltimer_ns() - w0;
+            peer_wait_clk += static_cast<uint64_t>(clock64() - w0);
             if (!arrived) {
               report_status(status, kStatusTimeoutSignal, 40, target, seen, p.rank, group);
               *abort_flag = 1;
@@ -661,7 +662,7 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
           }
         }
       }
-      stat_add(2, peer_wait_ns);
+      stat_add(2, peer_wait_clk);
       stat_add(3, leader ? n_tiles_done : 0);
       if (!ok) {
         // Let loads that are still in flight land before the CTA retires.
@@ -759,9 +760,9 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
         const uint32_t target =
             p.epoch * static_cast<uint32_t>(group_m_count(p, g) * p.n_tiles_local * kEpiWarps);
         uint32_t seen = 0;
-        const uint64_t w0 = p.stats != 0 ? globaltimer_ns() : 0;
+        const long long w0 = clock64();
         const bool arrived = tile_wait_ge(sig + src * p.sig_stride + g, target, wb, &seen);
-        if (p.stats != 0) stat_add(2, globaltimer_ns() - w0);
+        stat_add(2, static_cast<uint64_t>(clock64() - w0));
         if (!arrived) {
           report_status(status, kStatusTimeoutSignal, 30, target, seen, p.rank, i);
           break;

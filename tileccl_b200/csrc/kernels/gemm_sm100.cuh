@@ -118,8 +118,8 @@ struct alignas(64) FusedGemmParams {
   uint64_t sched_counter;
   // diagnostics
   // optional uint64[kStatWords] counters, added to by every launch (host reads and clears):
-  // [0] bytes stored into peers' memory  [1] TileGroup signals sent  [2] ns spent waiting for
-  // peers (TileGroup / gate / entry counters, summed over waiting threads)  [3] tiles computed
+  // [0] bytes stored into peers' memory  [1] TileGroup signals sent  [2] SM cycles spent waiting for
+  // peers (TileGroup / gate counters, summed over waiting threads)  [3] tiles computed
   uint64_t stats;
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;

@@ -297,9 +297,16 @@ class SymmetricHeap:
         after the reset can never alias a live counter.
         """
         self._check_alive()
+        used = self.bytes_allocated
         _native.call("tccl_heap_reset", self._native.handle)
         self._ledger.reset()
-        self._dirty = True
+        # Everything handed out so far goes back to zero right here, while no rank is using
+        # the heap, so that counters carved from it later need no memset of their own (a late
+        # memset by the owner could wipe a signal that a faster peer has already sent).
+        if used:
+            self._buffer[:used].zero_()
+        self._dirty = False
+        self.barrier()
         self._state.clear()
         for ref in list(self._reset_hooks):
             hook = ref()

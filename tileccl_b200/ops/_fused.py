@@ -64,15 +64,15 @@ def stats_block(ctx) -> torch.Tensor:
 def call_stats(ctx, reset: bool = True) -> dict:
     """Counters accumulated by the fused kernels of this context since the last reset
     (synchronises the device): bytes stored into peers' memory, TileGroup signals sent,
-    nanoseconds spent waiting for peers (summed over the waiting threads) and tiles computed."""
+    SM cycles spent waiting for peers (summed over the waiting threads) and tiles computed."""
     st = ctx._state.get("stats")
     if st is None:
-        return {"bytes_pushed": 0, "signals_sent": 0, "peer_wait_ns": 0, "tiles": 0}
+        return {"bytes_pushed": 0, "signals_sent": 0, "peer_wait_cycles": 0, "tiles": 0}
     torch.cuda.synchronize(ctx.torch_device)
     w = st.cpu().tolist()
     if reset:
         st.zero_()
-    return {"bytes_pushed": w[0], "signals_sent": w[1], "peer_wait_ns": w[2], "tiles": w[3]}
+    return {"bytes_pushed": w[0], "signals_sent": w[1], "peer_wait_cycles": w[2], "tiles": w[3]}
 
 
 def check_status(ctx) -> None:

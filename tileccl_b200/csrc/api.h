@@ -112,8 +112,9 @@ typedef struct TcclGemmDesc {
   uint64_t ag_src, ag_dst, ag_mc_dst, ag_bytes;
   int32_t scatter_col_begin, scatter_col_end;
   int32_t grid;                  // 0 = one CTA per SM
-  uint64_t stats;                // uint64[8] in device memory, may be 0: per-call counters every launch
-                                 // adds to (bytes stored to peers, signals sent, SM cycles waited for peers, tiles)
+  uint64_t stats;                // uint64[256][4] in device memory, may be 0: CTA b of every launch adds its
+                                 // counters to row b (bytes stored to peers, signals sent, SM cycles waited
+                                 // for peers, tiles)
   uint64_t status;               // uint32[8] in device memory, may be 0
   uint64_t trace;                // uint64[TcclGemmPlanInfo::trace_words] in device memory, may be 0: 4 stamps per
                                  // epilogue warp and 128-row tile, then 4 stamps per CTA

@@ -72,7 +72,13 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code, u
                                               uint32_t expected, uint32_t observed, uint32_t rank,
                                               uint32_t item) {
   if (status == nullptr) return;
-  if (atomicCAS(status, 0u, code) == 0u) {
+  // The first report wins, except that a peer-signal time-out (the root cause) replaces a
+  // pipeline-barrier time-out that another role of the same kernel reported a moment earlier.
+  const uint32_t old = atomicCAS(status, 0u, code);
+  bool take = old == 0u;
+  if (!take && code == kStatusTimeoutSignal && old == kStatusTimeoutMbarrier)
+    take = atomicCAS(status, old, code) == old;
+  if (take) {
     status[1] = where;
     status[2] = expected;
     status[3] = observed;

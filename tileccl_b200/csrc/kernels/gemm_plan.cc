@@ -323,6 +323,7 @@ extern "C" int tccl_gemm_plan_launch(void* plan_, uint32_t epoch, uint32_t a_gat
   } else
   if (grid > tile_end - tile_begin) grid = tile_end - tile_begin;
   if (grid < 1) grid = 1;
+  if (grid > kStatMaxCtas || plan->pair_push_grid > kStatMaxCtas) p.stats = 0;   // table has one row per CTA
   if (plan->pair_kernel && tile_begin == 0 && tile_end == total) {
     p.trace_tile_slots = 2 * ((p.m_tiles_local + 1) / 2) * p.n_tiles_local * p.owners;
     // (an all-gather-pushing launch has a fixed grid: the consumers count its CTAs)

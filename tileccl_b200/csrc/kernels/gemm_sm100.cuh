@@ -29,7 +29,8 @@ static constexpr int kSmemCtl = 512;
 static constexpr int kSmemTotal = kSmemPipe + kSmemEpi + kSmemCtl + 1024;  // + alignment slack
 
 static constexpr int kMaxRanks = 8;
-static constexpr int kStatWords = 8;
+static constexpr int kStatPerCta = 4;      // counters per CTA row of the statistics table
+static constexpr int kStatMaxCtas = 256;   // rows of the table (>= any grid of the kernel)
 
 enum GemmMode : int {
   kModeGemm = 0,       // out[0] = A @ B
@@ -117,9 +118,10 @@ struct alignas(64) FusedGemmParams {
   // between launches (the last CTA to exit resets them).  0 = static round-robin.
   uint64_t sched_counter;
   // diagnostics
-  // optional uint64[kStatWords] counters, added to by every launch (host reads and clears):
-  // [0] bytes stored into peers' memory  [1] TileGroup signals sent  [2] SM cycles spent waiting for
-  // peers (TileGroup / gate counters, summed over waiting threads)  [3] tiles computed
+  // optional uint64[kStatMaxCtas][kStatPerCta] table; CTA b of every launch adds its sums to
+  // row b (the host adds up the rows and clears them): [0] bytes stored into peers' memory
+  // [1] TileGroup signals sent  [2] SM cycles spent waiting for peers (TileGroup / gate
+  // counters, summed over waiting threads)  [3] tiles computed
   uint64_t stats;
   uint64_t status;                    // uint32[kStatusWords]
   uint64_t wait_budget_ns;

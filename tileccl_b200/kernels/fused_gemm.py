@@ -37,7 +37,7 @@ EPILOGUE_SLABS = 4  # one signal increment per 32-row slab of a tile
 
 _DTYPE_CODE = {torch.float16: 0, torch.bfloat16: 1}
 STATUS_WORDS = 8
-STAT_WORDS = 8
+STAT_WORDS = 256 * 4       # one row of four counters per CTA
 
 # Kernel launches issued through this module since import (benchmarks report it).
 LAUNCH_COUNT = 0

@@ -53,7 +53,7 @@ def status_block(ctx) -> torch.Tensor:
 
 
 def stats_block(ctx) -> torch.Tensor:
-    """uint64[8] device words every fused launch of this context adds its counters to."""
+    """uint64[256][4] device table: CTA b of every fused launch adds its counters to row b."""
     st = ctx._state.get("stats")
     if st is None:
         st = torch.zeros(fg.STAT_WORDS, dtype=torch.int64, device=ctx.torch_device)
@@ -69,7 +69,7 @@ def call_stats(ctx, reset: bool = True) -> dict:
     if st is None:
         return {"bytes_pushed": 0, "signals_sent": 0, "peer_wait_cycles": 0, "tiles": 0}
     torch.cuda.synchronize(ctx.torch_device)
-    w = st.cpu().tolist()
+    w = st.view(-1, 4).sum(0).cpu().tolist()
     if reset:
         st.zero_()
     return {"bytes_pushed": w[0], "signals_sent": w[1], "peer_wait_cycles": w[2], "tiles": w[3]}

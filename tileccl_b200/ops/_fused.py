@@ -156,6 +156,17 @@ def default_rs_own_lag(ws: int, m_tiles: int, n_tiles: int) -> int:
     return lag if 1 <= lag < m_tiles else 0
 
 
+def rs_uses_cta_pairs(ws: int) -> bool:
+    """Kernel form of a reduce-scatter.  With peers the one-CTA form measured faster at 2, 4
+    and 8 GPUs (its owner-side reduction multiplies a 128 x 128 identity, the CTA-pair form a
+    256 x 256 one of which half is zero blocks, and an own pair-tile waits for two tile rows
+    of every peer instead of one); a single rank runs a plain GEMM, where pairs win."""
+    forced = _config().rs_cta_pairs
+    if forced is not None:
+        return forced
+    return ws <= 1
+
+
 def default_group_m_tiles(m_tiles: int, n_tiles: Optional[int] = None, elem_bytes: int = 2) -> int:
     """Tile rows per TileGroup: the planner's P0 rule (a group carries at least tau_min bytes,
     tileccl_v2/tile_group.py:116-117 in the reference) with tau_min taken from the calibration
@@ -587,6 +598,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
             ident_ptr=fg.identity_operand(A.dtype, A.device).data_ptr() if ws > 1 else 0,
             rs_own_lag=(default_rs_own_lag(ws, m_tiles, -(-sub_n // fg.BLOCK_N))
                         if ws > 1 and _in_kernel_waits_ok(ctx) else 0),
+            cta_pairs=rs_uses_cta_pairs(ws),
             group_m_tiles=gm, sig_local=sig_ptr, heap_stride=stride, sig_stride=MAX_GROUPS,
             stage_local=stage_ptr, status_ptr=status_block(ctx).data_ptr(), stats_ptr=stats_block(ctx).data_ptr(),
             wait_budget_ns=wait_budget_ns()))

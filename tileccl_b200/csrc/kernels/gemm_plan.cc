@@ -246,7 +246,9 @@ int build_plan(const TcclGemmDesc& d, GemmPlan* plan) {
     plan->pair_grid = 2 * pairs;
     plan->pair_push_grid = grid & ~1;
   }
-  plan->want_sched = d.dynamic_tiles != 0;
+  // Dynamic tile scheduling evens out unequal shares of the link; a single rank has no link
+  // and keeps the fixed order (best L2 reuse, no scheduling traffic).
+  plan->want_sched = d.dynamic_tiles != 0 && d.world_size > 1;
   info.pair_kernel = plan->pair_kernel ? 1 : 0;
   info.pair_grid = plan->pair_grid;
   // uint64 words a trace buffer must hold: tile slots of the larger form + per-CTA stamps

@@ -529,18 +529,22 @@ fused_gemm_sm100_kernel(const __grid_constant__ FusedGemmParams p) {
       tma_prefetch_desc(&p.tma_b);
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      // The position for the next tile is fetched one tile ahead: the atomic's round trip
+      // (about a microsecond) then hides behind this tile's K loop instead of delaying it.
+      int t_next = (dyn && leader) ? sched_fetch() : -1;
       uint64_t peer_wait_clk = 0, n_tiles_done = 0;   // (the SM cycle counter: a %globaltimer
                                                       // read costs about a microsecond)
       for (uint32_t n_seq = 0; ok; ++n_seq) {
         int t;
         if (dyn) {
           if (leader) {
-            t = sched_fetch();
+            t = t_next;
             if (!sched_publish(n_seq, t)) {
               report_status(status, kStatusTimeoutMbarrier, 14, 0, 0, p.rank, n_seq);
               ok = false;
               break;
             }
+            if (t >= 0) t_next = sched_fetch();
           } else {
             t = sched_consume(n_seq);
           }

@@ -289,10 +289,11 @@ def visit_rows(m_tiles: int, owners: int, rank: int, world_size: int, own_lag: i
     return rows
 
 
-# Shares of the rank's tile rows given to successive runs of a host-streamed launch.  Few
-# runs keep the number of copies (each costs a gap on the copy engine) and launches low;
-# the falling sizes leave only a tenth of the math behind the last byte of the transfer.
-STREAM_RUN_SHARES = (0.40, 0.30, 0.20, 0.10)
+# Shares of the rank's tile rows given to successive runs of a host-streamed launch.  Every
+# extra cudaMemcpyAsync costs several microseconds of copy-engine set-up (measured: 24 copies
+# instead of 6 per step added about 0.2 ms), so there are few runs; the falling sizes leave
+# little math behind the last byte of the transfer.
+STREAM_RUN_SHARES = (0.50, 0.35, 0.15)
 
 
 def _tile_row_chunks(plan, min_tiles: int = 148, shares: Sequence[float] = STREAM_RUN_SHARES) -> list:

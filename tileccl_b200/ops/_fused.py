@@ -377,7 +377,7 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
     key = (A.data_ptr(), a_host.data_ptr(), A.stride(0))
     prepared = getattr(plan, "_stream_chunks", None)
     if prepared is None or prepared[0] != key:
-        chunks = _tile_row_chunks(plan)
+        chunks = _tile_row_chunks(plan, shares=_config().stream_run_shares or STREAM_RUN_SHARES)
         if not A.is_contiguous() or any(len(r) > _native.STREAM_MAX_RANGES for _, _, r in chunks):
             prepared = (key, None, chunks)
         else:
@@ -398,6 +398,22 @@ def launch_streamed(ctx, plan, A: torch.Tensor, a_host: torch.Tensor, *,
         # Copies, events and launches are issued by the native runtime: a few microseconds
         # of host time per run instead of a Python round trip each.
         fg.count_launches(len(chunks))
+        if getattr(plan, "_stream_fast", None) is None or plan._stream_fast[0] != (key, order):
+            fn = getattr(_native.load(), "tccl_gemm_plan_launch_streamed")
+            handle, n_chunks, side_ptr = plan._handle, len(chunks), side.cuda_stream
+            side2_ptr = st["stream2"].cuda_stream if _config().stream_copy_streams == 2 else 0
+            order_bit = 4 if order == "plan" else 0
+
+            def stream_fast(epoch, a_gate_target, flags, _arr=arr):
+                """Repeat of this streamed launch on the same buffers: one native call."""
+                fg.count_launches(n_chunks)
+                rc = fn(handle, epoch & 0xFFFFFFFF, a_gate_target & 0xFFFFFFFF,
+                        flags | order_bit | 8, _arr, n_chunks, side_ptr, side2_ptr,
+                        torch.cuda.current_stream().cuda_stream)
+                if rc != 0:
+                    _native.check("tccl_gemm_plan_launch_streamed", rc)
+
+            plan._stream_fast = ((key, order), stream_fast)
         _native.call("tccl_gemm_plan_launch_streamed", plan._handle,
                      launch_kw.get("epoch", 1) & 0xFFFFFFFF,
                      launch_kw.get("a_gate_target", 0) & 0xFFFFFFFF,
@@ -455,6 +471,11 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
     if fast is not None and a_host is None:
         fast(wait)              # repeated call on the same buffers: epoch + launch only
         return
+    if a_host is not None:
+        fh = st.get("fast_host")
+        if fh is not None and fh[0] == (a_host.data_ptr(), a_host_order):
+            fh[1](wait)         # the same, with the operand streamed from the same host buffer
+            return
     m_tiles = -(-Mloc // fg.BLOCK_M)
     gm = group_m_tiles or default_group_m_tiles(m_tiles, -(-N // fg.BLOCK_N), A.element_size())
     sigst = _signal_state(ctx, f"push_all:{name}:{Mloc}x{N}x{K}:g{gm}") if ws > 1 else st
@@ -499,9 +520,25 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
         st["fast"] = fast
     sigst["epoch"] += 1
     epoch = sigst["epoch"]
+    def remember_streamed(in_kernel_wait: bool) -> None:
+        """After a streamed call went through the checked path once, later calls with the
+        same host buffer take one native call (host time matters: the first copy of a step
+        cannot start before the host has issued it)."""
+        sf = getattr(plan, "_stream_fast", None)
+        if sf is None or ctx.local_group is not None:
+            return
+        launcher = sf[1]
+
+        def fast_host(wait_flag, _sig=sigst):
+            _sig["epoch"] += 1
+            launcher(_sig["epoch"], 0, 1 if (wait_flag and in_kernel_wait) else 0)
+
+        st["fast_host"] = ((a_host.data_ptr(), a_host_order), fast_host)
+
     if ws == 1:
         if a_host is not None:
             launch_streamed(ctx, plan, A, a_host, order=a_host_order)
+            remember_streamed(False)
         else:
             plan.launch()
         return
@@ -518,6 +555,8 @@ def push_all(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, 
         phases.append(_on_device(ctx, lambda: wait_groups(ctx, st["sig"], plan.groups,
                                                           st["per_epoch"], epoch)))
     run_phases(ctx, ("push_all", name, Mloc, N, K, epoch), phases)
+    if a_host is not None and not ctx.is_single_process:
+        remember_streamed(True)
 
 
 def wait_groups(ctx, sig: torch.Tensor, n_groups: int, per_epoch: torch.Tensor, epoch: int) -> None:
@@ -572,6 +611,11 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     if fast is not None and a_host is None:
         fast()
         return
+    if a_host is not None:
+        fh = st.get("fast_host")
+        if fh is not None and fh[0] == (a_host.data_ptr(), a_host_order):
+            fh[1]()
+            return
     m_tiles = -(-sub_m // fg.BLOCK_M)
     gm = group_m_tiles or default_group_m_tiles(m_tiles, -(-sub_n // fg.BLOCK_N), A.element_size())
     sigst = (_signal_state(ctx, f"reduce_scatter:{name}:{M}x{N}x{K}:a{split_axis}:g{gm}:{A.dtype}")
@@ -627,6 +671,16 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
         phases = [_on_device(ctx, lambda: plan.launch(epoch=epoch, tile_begin=0, tile_end=n_remote)),
                   _on_device(ctx, lambda: plan.launch(epoch=epoch, tile_begin=n_remote))]
     run_phases(ctx, ("reduce_scatter", name, M, N, K, split_axis, epoch), phases)
+    sf = getattr(plan, "_stream_fast", None)
+    if (a_host is not None and sf is not None and ctx.local_group is None
+            and (ws == 1 or _in_kernel_waits_ok(ctx))):
+        launcher = sf[1]
+
+        def fast_host(_sig=sigst):
+            _sig["epoch"] += 1
+            launcher(_sig["epoch"], 0, 0)
+
+        st["fast_host"] = ((a_host.data_ptr(), a_host_order), fast_host)
 
 
 # --------------------------------------------------------------------------

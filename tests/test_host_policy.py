@@ -270,3 +270,17 @@ def test_pattern_options_select_the_launch_shape_or_are_rejected():
         WGSpecializedPattern(ctx, BLOCK_M=64, BLOCK_N=64, BLOCK_K=32)
     with pytest.raises(TypeError):
         WGSpecializedPattern(ctx, FANCY=1)
+
+
+def test_runtime_config_covers_the_measured_choices():
+    from tileccl_b200.utils import RuntimeConfig
+
+    cfg = RuntimeConfig.from_env({})
+    assert not cfg.dynamic_tiles and cfg.call_stats and cfg.rs_cta_pairs is None
+    assert cfg.ll_max_bytes == 65536 and cfg.stream_run_shares is None and cfg.stream_copy_streams == 1
+    cfg = RuntimeConfig.from_env({"TILECCL_DYNAMIC_TILES": "1", "TILECCL_STATS": "0",
+                                  "TILECCL_RS_CTA_PAIRS": "1", "TILECCL_LL_MAX_BYTES": "4096",
+                                  "TILECCL_STREAM_SHARES": "0.85,0.15"})
+    assert cfg.dynamic_tiles and not cfg.call_stats and cfg.rs_cta_pairs is True
+    assert cfg.ll_max_bytes == 4096 and cfg.stream_run_shares == (0.85, 0.15)
+    assert cfg.wait_budget_ns == 0 and RuntimeConfig.from_env({"TILECCL_WAIT_BUDGET_US": "3"}).wait_budget_ns == 3000

@@ -169,6 +169,13 @@ def describe_runtime_support(ctx: Any = None) -> RuntimeSupportMatrix:
     collectives["collectives.nvls"] = (coll if nvls else SupportStatus(
         PARTIAL if coll.state == SUPPORTED else coll.state, "NVLS not bound: peer load/store paths are used"))
     collectives["collectives.ops_other_than_sum"] = SupportStatus(UNSUPPORTED, "only op='sum'")
+    collectives["collectives.device_functions"] = SupportStatus(
+        SUPPORTED, "tile_allreduce / tile_allgather / tile_reduce_scatter / tile_broadcast / "
+                   "tile_scatter are __device__ functions (csrc/device/tile_collectives.cuh); user "
+                   "kernels are built and launched with tileccl_b200.userkernel")
+    collectives["collectives.low_latency_copies"] = SupportStatus(
+        coll.state, "all-gather / broadcast / scatter up to 64 KiB per peer travel as "
+                    "flag-in-data lines (csrc/device/tile_ll.cuh)")
     mem_ok = SupportStatus(SUPPORTED if has_heap else UNSUPPORTED,
                            f"cuMem VMM heap, mode {heap_mode}, transport {transport}" if has_heap
                            else "no heap attached")

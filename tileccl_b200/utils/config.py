@@ -32,7 +32,7 @@ class RuntimeConfig:
     tuning: int = 1                        # TILECCL_TUNING: bit 0 = relaxed signal after a completed bulk store
     gemm_cta_pairs: bool = True            # TILECCL_GEMM_2SM: whole-order launches on CTA pairs
     call_stats: bool = True                # TILECCL_STATS: fused kernels add per-call counters (ops.call_stats)
-    dynamic_tiles: bool = True             # TILECCL_DYNAMIC_TILES: tiles handed to CTAs from a global counter
+    dynamic_tiles: bool = False            # TILECCL_DYNAMIC_TILES: tiles handed to CTAs from a global counter
     rs_cta_pairs: Optional[bool] = None    # TILECCL_RS_CTA_PAIRS: kernel form of a multi-rank reduce-scatter (None = measured choice)
     rs_own_lag: Optional[int] = None       # TILECCL_RS_OWN_LAG: rounds the own rows trail (None = heuristic)
     wait_budget_us: Optional[float] = None  # TILECCL_WAIT_BUDGET_US: budget of every device wait (None = 2 s)
@@ -65,7 +65,7 @@ class RuntimeConfig:
             tuning=int(e.get("TILECCL_TUNING") or 1),
             gemm_cta_pairs=_flag(e, "TILECCL_GEMM_2SM", True),
             call_stats=_flag(e, "TILECCL_STATS", True),
-            dynamic_tiles=_flag(e, "TILECCL_DYNAMIC_TILES", True),
+            dynamic_tiles=_flag(e, "TILECCL_DYNAMIC_TILES", False),
             rs_cta_pairs=(None if e.get("TILECCL_RS_CTA_PAIRS") in (None, "")
                           else _flag(e, "TILECCL_RS_CTA_PAIRS")),
             rs_own_lag=_opt_int(e, "TILECCL_RS_OWN_LAG"),

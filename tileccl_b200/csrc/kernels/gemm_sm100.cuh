@@ -65,7 +65,7 @@ struct alignas(64) FusedGemmParams {
   // B operand next to a 128 x 128 identity as A operand, so acc += I * P = P in fp32.
   CUtensorMap tma_stage;              // this rank's staging {cols, rows, slots}, box {64, 64, 1}
   CUtensorMap tma_ident;              // identity [128, 128], box {64, 128}
-  // CTA-pair kernel (gemm2sm_sm100.cu): B with a box that covers 128 of a tile's 256 columns
+  // CTA-pair form of the kernel (gemm_sm100.cu, kPair): B with a box that covers 128 of a tile's 256 columns
   CUtensorMap tma_b_half;
   // raw views of the same destinations for the non-TMA push modes
   uint64_t out_ptr[kMaxRanks];

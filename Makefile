@@ -1,4 +1,4 @@
-.PHONY: help build rebuild ptxas test-cpu test-gpu bench bench-reference example lint clean
+.PHONY: help build build-debug rebuild ptxas test-cpu test-gpu sanitize bench bench-reference example lint clean
 
 PYTHON ?= python
 NGPU ?= 1
@@ -11,16 +11,22 @@ help:  ## Show this help
 build:  ## Compile csrc/ for sm_100a into tileccl_b200/lib/libtileccl_b200.so (no GPU needed)
 	$(PYTHON) -m tileccl_b200._build
 
-rebuild:  ## Recompile everything
-	$(PYTHON) -m tileccl_b200._build --force
+build-debug:  ## The same sources with recorded bounds checks (-DTILECCL_DEBUG_CHECKS; TILECCL_DEBUG=1 loads it)
+	$(PYTHON) -m tileccl_b200._build --debug
+
+rebuild:  ## Recompile everything (release and debug libraries)
+	$(PYTHON) -m tileccl_b200._build --all --force
+
+sanitize:  ## CPU emulation of the signalling protocol under ThreadSanitizer and ASan/UBSan
+	$(PYTHON) -m pytest tests/test_emulator_sanitizers.py -q
 
 ptxas:  ## Print registers / spills / shared memory of every kernel
 	$(PYTHON) -m tileccl_b200._build --ptxas-v
 
-test-cpu: build  ## Tests that need no GPU (planning, emulator, bootstrap, build checks)
+test-cpu: build build-debug  ## Tests that need no GPU (planning, emulator, bootstrap, build checks)
 	$(PYTHON) -m pytest tests -x -q -m "not gpu"
 
-test-gpu: build  ## Tests that need a B200
+test-gpu: build build-debug  ## Tests that need a B200
 	$(PYTHON) -m pytest tests -x -q -m gpu
 
 bench: build  ## Headline benchmark on NGPU GPUs (make bench NGPU=8)
@@ -44,5 +50,5 @@ lint:  ## ruff, when installed
 	ruff check tileccl_b200 tileccl tileccl_v2 tests examples benchmarks bench.py
 
 clean:  ## Remove build artefacts
-	rm -rf build/ dist/ *.egg-info .pytest_cache .ruff_cache tileccl_b200/lib/libtileccl_b200.so
+	rm -rf build/ dist/ *.egg-info .pytest_cache .ruff_cache tileccl_b200/lib/libtileccl_b200.so tileccl_b200/lib/libtileccl_b200_debug.so
 	find . -type d -name __pycache__ -prune -exec rm -rf {} + 2>/dev/null || true

@@ -22,8 +22,11 @@ from tileccl_b200 import userkernel  # noqa: E402
 SOURCE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "custom_kernel.cu")
 
 
-def run(world_size: int = 4, n: int = 4096, real: bool = False, calls: int = 3) -> None:
-    mod = userkernel.compile(SOURCE)
+def run(world_size: int = 4, n: int = 4096, real: bool = False, calls: int = 3,
+        debug: bool = False) -> None:
+    """``debug=True`` compiles the kernel with the recorded bounds checks and verifies at the
+    end that none of them fired."""
+    mod = userkernel.compile(SOURCE, debug=debug)
     devices = list(range(world_size)) if real else [0] * world_size
     ctxs = tccl.init_local(world_size, 64 << 20, devices=devices)
     try:
@@ -49,7 +52,13 @@ def run(world_size: int = 4, n: int = 4096, real: bool = False, calls: int = 3) 
                 assert torch.equal(data[r].cpu(), want), f"rank {r}: wrong all-reduce result"
                 left = (r - 1) % world_size
                 assert int(token[r][0]) == 1000 * epoch + left, f"rank {r}: wrong token"
-        print(f"custom kernel ok: world_size={world_size} real_gpus={real} calls={calls}")
+        if debug:
+            for c in ctxs:
+                with torch.cuda.device(c.torch_device):
+                    rec = mod.debug_record()
+                    assert rec.enabled == 1 and rec.count == 0, rec.to_dict("custom_kernel")
+        print(f"custom kernel ok: world_size={world_size} real_gpus={real} calls={calls}"
+              + (" (bounds checks on)" if debug else ""))
     finally:
         for c in ctxs:
             torch.cuda.synchronize(c.torch_device)
@@ -61,5 +70,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--real", type=int, default=0, help="run on this many real GPUs")
     ap.add_argument("--ranks", type=int, default=4)
+    ap.add_argument("--debug", action="store_true", help="compile with recorded bounds checks")
     args = ap.parse_args()
-    run(args.real or args.ranks, real=bool(args.real))
+    run(args.real or args.ranks, real=bool(args.real), debug=args.debug)

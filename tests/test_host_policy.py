@@ -284,3 +284,32 @@ def test_runtime_config_covers_the_measured_choices():
     assert cfg.dynamic_tiles and not cfg.call_stats and cfg.rs_cta_pairs is True
     assert cfg.ll_max_bytes == 4096 and cfg.stream_run_shares == (0.85, 0.15)
     assert cfg.wait_budget_ns == 0 and RuntimeConfig.from_env({"TILECCL_WAIT_BUDGET_US": "3"}).wait_budget_ns == 3000
+
+
+def test_op_state_table_is_bounded_and_keeps_signal_blocks():
+    """Plan entries are evicted oldest-first beyond the bound; signal blocks (epochs) never."""
+    from types import SimpleNamespace
+
+    from tileccl_b200.ops import _fused
+
+    closed = []
+
+    class FakePlan:
+        def __init__(self, i):
+            self.i = i
+
+        def close(self):
+            closed.append(self.i)
+
+    ctx = SimpleNamespace(_state={})
+    sig = _fused.op_state(ctx, ("sig", "gemm_allgather"))
+    sig["epoch"] = 7
+    for i in range(_fused.MAX_OP_STATES + 5):
+        _fused.op_state(ctx, ("push_all", "x", i))["plan"] = FakePlan(i)
+    table = ctx._state["ops"]
+    assert len(table) <= _fused.MAX_OP_STATES
+    assert table[("sig", "gemm_allgather")] is sig and sig["epoch"] == 7
+    assert closed == list(range(len(closed))) and len(closed) >= 5
+    # the same key gives the same state back
+    last = ("push_all", "x", _fused.MAX_OP_STATES + 4)
+    assert _fused.op_state(ctx, last) is table[last]

@@ -28,3 +28,14 @@ def test_device_api_names_point_at_real_functions():
         assert f" {name}(" in text, name
     with pytest.raises(RuntimeError, match="userkernel"):
         d.tile_allreduce()
+
+
+@pytest.mark.skipif(shutil.which("nvcc") is None and not os.path.exists("/usr/local/cuda/bin/nvcc"),
+                    reason="nvcc not installed")
+def test_example_kernel_compiles_with_the_recorded_bounds_checks():
+    from tileccl_b200 import userkernel
+
+    rel = userkernel.compile(os.path.join(ROOT, "examples", "custom_kernel.cu"))
+    dbg = userkernel.compile(os.path.join(ROOT, "examples", "custom_kernel.cu"), debug=True)
+    assert dbg.path != rel.path and dbg.path.exists()
+    assert dbg._debug_read is not None and rel._debug_read is not None

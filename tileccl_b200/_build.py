@@ -22,7 +22,10 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libtileccl_b200.so"
+DEBUG_LIB_PATH = LIB_DIR / "libtileccl_b200_debug.so"     # -DTILECCL_DEBUG_CHECKS
 BUILD_DIR = PKG_DIR.parent / "build" / "tileccl_b200"
+DEBUG_BUILD_DIR = PKG_DIR.parent / "build" / "tileccl_b200_debug"
+DEBUG_FLAGS = ["-DTILECCL_DEBUG_CHECKS=1"]
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON_FLAGS = [
@@ -69,18 +72,26 @@ def _compile_one(nvcc: str, src: Path, obj: Path, extra: list[str]) -> tuple[Pat
     return src, proc.stdout + proc.stderr
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> Path:
-    """Compile every translation unit under ``csrc/`` and link the shared object."""
+def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False,
+          debug: bool = False) -> Path:
+    """Compile every translation unit under ``csrc/`` and link the shared object.
+
+    ``debug=True`` builds the second library, ``libtileccl_b200_debug.so``: the same sources
+    with ``-DTILECCL_DEBUG_CHECKS``, in which pointer translations and the symmetric tiles
+    the verbs and collectives touch are bounds-checked on the device and violations are
+    recorded instead of faulting (``tileccl_b200.debug``; ``TILECCL_DEBUG=1`` loads it)."""
     nvcc = _nvcc()
-    BUILD_DIR.mkdir(parents=True, exist_ok=True)
+    build_dir = DEBUG_BUILD_DIR if debug else BUILD_DIR
+    lib_path = DEBUG_LIB_PATH if debug else LIB_PATH
+    build_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     hdr_mtime = _headers_mtime()
-    extra = ["-Xptxas", "-v"] if ptxas_v else []
+    extra = (["-Xptxas", "-v"] if ptxas_v else []) + (DEBUG_FLAGS if debug else [])
     jobs = []
     objs = []
     for src in sources():
         rel = src.relative_to(CSRC)
-        obj = BUILD_DIR / (str(rel).replace(os.sep, "__") + ".o")
+        obj = build_dir / (str(rel).replace(os.sep, "__") + ".o")
         objs.append(obj)
         stale = (
             force
@@ -100,17 +111,27 @@ def build(force: bool = False, verbose: bool = False, ptxas_v: bool = False) -> 
                     print(f"[tileccl_b200 build] {src.relative_to(CSRC)}")
                     if log.strip():
                         print(log)
-    need_link = bool(jobs) or not LIB_PATH.exists()
+    need_link = bool(jobs) or not lib_path.exists()
     if need_link:
-        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lpthread", "-ldl"]
+        cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", str(lib_path), *map(str, objs), "-lpthread", "-ldl"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{' '.join(cmd)}\n{proc.stdout}\n{proc.stderr}")
         if verbose:
-            print(f"[tileccl_b200 build] linked {LIB_PATH}")
-    return LIB_PATH
+            print(f"[tileccl_b200 build] linked {lib_path}")
+    return lib_path
+
+
+def build_all(force: bool = False, verbose: bool = False) -> list[Path]:
+    """The release library and the debug library."""
+    return [build(force=force, verbose=verbose), build(force=force, verbose=verbose, debug=True)]
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose=True, ptxas_v="--ptxas-v" in sys.argv)
-    print(path)
+    if "--all" in sys.argv:
+        for p in build_all(force="--force" in sys.argv, verbose=True):
+            print(p)
+    else:
+        path = build(force="--force" in sys.argv, verbose=True, ptxas_v="--ptxas-v" in sys.argv,
+                     debug="--debug" in sys.argv)
+        print(path)

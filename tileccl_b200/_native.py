@@ -159,11 +159,14 @@ _lib_lock = threading.Lock()
 
 
 def lib_path() -> Path:
-    """The shared object to load; ``TILECCL_NATIVE_LIB`` names another build of it."""
+    """The shared object to load: ``TILECCL_NATIVE_LIB`` names another build of it,
+    ``TILECCL_DEBUG=1`` selects the build with recorded bounds checks."""
     from .utils.config import current
 
-    override = current().native_lib
-    return Path(override) if override else _build.LIB_PATH
+    cfg = current()
+    if cfg.native_lib:
+        return Path(cfg.native_lib)
+    return _build.DEBUG_LIB_PATH if cfg.debug else _build.LIB_PATH
 
 
 def _declare(lib: C.CDLL) -> None:
@@ -195,6 +198,8 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_collective_ll_launch": [i32, i32, i32, i32, i32, u32, u64, u64, u64, u64, C.c_int64, u64,
                                       i32, u64, u64, u64],
         "tccl_p2p_copy": [i32, i32, i32, i32, u64, u64, u64, u64, u64, i32, u64],
+        "tccl_debug_read_primitives": [vp, i32],
+        "tccl_debug_read_collectives": [vp, i32],
         "tccl_push_region": [u64, u64, C.c_int64, i32, i32, i32, i32, i32, C.c_int64, u64, u32, u64,
                              u32, i32, i32, u64, u64, u64],
         "tccl_plan_tile_groups": [C.c_int64, C.c_int64, C.c_int64, C.c_int64, i32, i32, i32, i32,
@@ -236,7 +241,7 @@ def load(build_if_missing: bool = True) -> C.CDLL:
 
             if not build_if_missing or current().no_build:
                 raise NativeError("load", -1, f"{path} is missing; run `python -m tileccl_b200._build`")
-            _build.build()
+            _build.build(debug=(path == _build.DEBUG_LIB_PATH))
         lib = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
         _declare(lib)
         _lib = lib

@@ -285,6 +285,16 @@ int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t world_size,
                    uint64_t n, uint32_t value, uint32_t value2, uint64_t result, uint64_t budget_ns,
                    uint64_t stream);
 
+// --------------------------------------------------------------------------
+// Debug build (-DTILECCL_DEBUG_CHECKS, libtileccl_b200_debug.so): the record of bounds
+// violations of the current device (tileccl::DebugRecord in device/symm_ptr.cuh, 40 bytes:
+// count, code, rank, from_rank, to_rank, enabled, addr, bytes), one per translation unit
+// that uses the device primitives.  `enabled` is 0 in a release build.  `clear` != 0
+// zeroes the record after reading.  Call after synchronising the streams of interest.
+// --------------------------------------------------------------------------
+int tccl_debug_read_primitives(void* out_record, int32_t clear);   // prim_test.cu kernels
+int tccl_debug_read_collectives(void* out_record, int32_t clear);  // collectives.cu kernels
+
 #ifdef __cplusplus
 }
 #endif

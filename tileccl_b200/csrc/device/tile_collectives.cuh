@@ -288,6 +288,7 @@ __device__ __forceinline__ void tile_allgather(const SymmWindow& w, const void* 
                                                const TileCoop& c) {
   const char* s = static_cast<const char*>(src);
   char* d = static_cast<char*>(sym_dst);
+  if (!symm_span_ok(w, d, bytes * w.world_size, w.rank)) return;   // debug build only
   if (use_mc && (bytes & 15u) == 0) {
     coll_detail::copy_vec_mc(mc_ptr(w, d) + w.rank * bytes, s, bytes, c);
   } else {
@@ -304,6 +305,7 @@ __device__ __forceinline__ void tile_broadcast(const SymmWindow& w, void* sym_bu
                                                const TileCoop& c) {
   if (w.rank != root) return;
   char* b = static_cast<char*>(sym_buf);
+  if (!symm_span_ok(w, b, bytes, w.rank)) return;                  // debug build only
   if (use_mc && (bytes & 15u) == 0) {
     coll_detail::copy_vec_mc(mc_ptr(w, b), b, bytes, c);
   } else {
@@ -320,6 +322,7 @@ __device__ __forceinline__ void tile_scatter(const SymmWindow& w, const void* sr
   if (w.rank != root) return;
   const char* s = static_cast<const char*>(src);
   char* d = static_cast<char*>(sym_dst);
+  if (!symm_span_ok(w, d, bytes, w.rank)) return;                  // debug build only
   for (int k = 0; k < w.world_size; ++k) {
     const int r = (w.rank + k) % w.world_size;
     coll_detail::copy_vec(coll_detail::peer_of(w, d, r), s + r * bytes, bytes, elem_size, c);
@@ -330,6 +333,7 @@ __device__ __forceinline__ void tile_scatter(const SymmWindow& w, const void* sr
 __device__ __forceinline__ void tile_reduce_scatter(const SymmWindow& w, const void* sym_src,
                                                     void* dst, uint64_t bytes, int dtype,
                                                     bool use_mc, const TileCoop& c) {
+  if (!symm_span_ok(w, static_cast<const char*>(sym_src), bytes * w.world_size, w.rank)) return;
   coll_detail::reduce_chunk<false>(w, static_cast<const char*>(sym_src), static_cast<char*>(dst),
                                    nullptr, w.rank * bytes, bytes, dtype, use_mc, c);
 }
@@ -345,6 +349,7 @@ __device__ __forceinline__ void tile_allreduce_chunk(const SymmWindow& w, void* 
   const uint64_t off = w.rank * chunk;
   const uint64_t mine = off >= bytes ? 0 : (bytes - off < chunk ? bytes - off : chunk);
   char* b = static_cast<char*>(sym_buf);
+  if (!symm_span_ok(w, b, bytes, w.rank)) return;                  // debug build only
   coll_detail::reduce_chunk<true>(w, b, nullptr, b, off, mine, dtype, use_mc, c);
 }
 

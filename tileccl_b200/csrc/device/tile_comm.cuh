@@ -6,7 +6,9 @@
 //   tile_put_mc      - one multimem.st lands the tile in every rank's heap
 //   tile_get_reduce  - multimem.ld_reduce returns the sum over all ranks
 // A pointer argument named `sym_*` points into the CALLER's heap; the peer's
-// copy of the object is found by translate_ptr.
+// copy of the object is found by translate_ptr.  In a debug build
+// (-DTILECCL_DEBUG_CHECKS) a verb whose symmetric tile is not inside the caller's
+// heap records the violation and moves nothing.
 #pragma once
 #include "tile_mem.cuh"
 
@@ -16,6 +18,7 @@ template <int kMaxVec>
 __device__ __forceinline__ int tile_remote_load(const SymmWindow& w, const TileView& sym_src,
                                                 int from_rank, uint4 (&frag)[kMaxVec], int tid,
                                                 int nthreads) {
+  if (!symm_tile_ok(w, sym_src)) return 0;
   TileView s = sym_src;
   s.ptr = translate_ptr(w, sym_src.ptr, w.rank, from_rank);
   return tile_load(s, frag, tid, nthreads);
@@ -25,6 +28,7 @@ template <int kMaxVec>
 __device__ __forceinline__ void tile_remote_store(const SymmWindow& w, const TileView& sym_dst,
                                                   int to_rank, const uint4 (&frag)[kMaxVec],
                                                   int tid, int nthreads) {
+  if (!symm_tile_ok(w, sym_dst)) return;
   TileView d = sym_dst;
   d.ptr = translate_ptr(w, sym_dst.ptr, w.rank, to_rank);
   tile_store(d, frag, tid, nthreads);
@@ -34,6 +38,7 @@ __device__ __forceinline__ void tile_remote_store(const SymmWindow& w, const Til
 __device__ __forceinline__ void tile_put(const SymmWindow& w, const TileView& src,
                                          const TileView& sym_dst, int to_rank, int tid,
                                          int nthreads) {
+  if (!symm_tile_ok(w, sym_dst)) return;
   TileView d = sym_dst;
   d.ptr = translate_ptr(w, sym_dst.ptr, w.rank, to_rank);
   tile_copy<false>(d, src, tid, nthreads);
@@ -43,6 +48,7 @@ __device__ __forceinline__ void tile_put(const SymmWindow& w, const TileView& sr
 __device__ __forceinline__ void tile_get(const SymmWindow& w, const TileView& sym_src,
                                          const TileView& dst, int from_rank, int tid,
                                          int nthreads) {
+  if (!symm_tile_ok(w, sym_src)) return;
   TileView s = sym_src;
   s.ptr = translate_ptr(w, sym_src.ptr, w.rank, from_rank);
   tile_copy<true>(dst, s, tid, nthreads);
@@ -52,6 +58,7 @@ __device__ __forceinline__ void tile_get(const SymmWindow& w, const TileView& sy
 // Requires w.mc_base != 0 and 16-byte aligned rows.
 __device__ __forceinline__ void tile_put_mc(const SymmWindow& w, const TileView& src,
                                             const TileView& sym_dst, int tid, int nthreads) {
+  if (!mc_span_ok(w, sym_dst.ptr, tile_span_bytes(sym_dst))) return;
   char* mc = mc_ptr(w, sym_dst.ptr);
   const int vec_per_row = src.row_bytes >> 4;
   const int total = src.rows * vec_per_row;
@@ -67,6 +74,7 @@ __device__ __forceinline__ void tile_put_mc(const SymmWindow& w, const TileView&
 __device__ __forceinline__ void tile_get_reduce(const SymmWindow& w, const TileView& sym_src,
                                                 const TileView& dst, int kind, int tid,
                                                 int nthreads) {
+  if (!mc_span_ok(w, sym_src.ptr, tile_span_bytes(sym_src))) return;
   const char* mc = mc_ptr(w, sym_src.ptr);
   const int vec_per_row = sym_src.row_bytes >> 4;
   const int total = sym_src.rows * vec_per_row;

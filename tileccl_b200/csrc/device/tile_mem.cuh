@@ -30,6 +30,17 @@ __host__ __device__ __forceinline__ TileView make_tile_view(void* base, int64_t 
   return t;
 }
 
+// Bytes from the first to one past the last byte of the tile.
+__host__ __device__ __forceinline__ uint64_t tile_span_bytes(const TileView& t) {
+  if (t.rows <= 0 || t.row_bytes <= 0) return 0;
+  return static_cast<uint64_t>(t.rows - 1) * static_cast<uint64_t>(t.ld_bytes) +
+         static_cast<uint64_t>(t.row_bytes);
+}
+// Debug-build guard (see symm_ptr.cuh): the tile lies inside the CALLER's heap.
+__host__ __device__ __forceinline__ bool symm_tile_ok(const SymmWindow& w, const TileView& t) {
+  return symm_span_ok(w, t.ptr, tile_span_bytes(t), w.rank);
+}
+
 // Copies `src` to `dst` with `nthreads` cooperating threads (thread id `tid`).
 // Rows whose start and length are 16-byte aligned move as uint4; the rest byte-wise.
 template <bool kRemoteSrc = false>

@@ -31,7 +31,11 @@ __device__ __forceinline__ T* user_ptr(const UserArgs& a, int i) {
 
 }  // namespace tileccl
 
+// The entry macros also define `tileccl_user_debug_read(void* record, int clear)`: the
+// record of bounds violations of this object when it was compiled with
+// -DTILECCL_DEBUG_CHECKS (userkernel.compile(..., debug=True)), an empty record otherwise.
 #define TILECCL_USER_KERNEL_ENTRY_(KERNEL, COOPERATIVE)                                       \
+  TILECCL_DEFINE_DEBUG_READER(tileccl_user_debug_read)                                        \
   extern "C" int tileccl_user_launch(const tileccl::SymmWindow* w, const uint64_t* args,      \
                                      int n_args, int grid, int block, void* stream) {         \
     tileccl::UserArgs a = {};                                                                 \

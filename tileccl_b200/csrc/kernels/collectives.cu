@@ -430,6 +430,8 @@ extern "C" int tccl_allreduce_sum_noalloc(const uint64_t* buffers, int32_t n_ran
   return kOk;
 }
 
+TILECCL_DEFINE_DEBUG_READER(tccl_debug_read_collectives)
+
 namespace tileccl {
 cudaError_t preload_collective_kernels() {
   cudaFuncAttributes a;

@@ -182,6 +182,8 @@ extern "C" int tccl_prim_test(int32_t op, int32_t sub_op, int32_t rank, int32_t 
   return kOk;
 }
 
+TILECCL_DEFINE_DEBUG_READER(tccl_debug_read_primitives)
+
 namespace tileccl {
 cudaError_t preload_prim_kernels() {
   cudaFuncAttributes a;

@@ -33,11 +33,31 @@ _DEFAULT_PUSH = {"stores": fg.PUSH_STORES, "tma": fg.PUSH_TMA, "multimem": fg.PU
 # --------------------------------------------------------------------------
 # per-context state
 # --------------------------------------------------------------------------
+MAX_OP_STATES = 512
+_PINNED_STATE_KINDS = ("sig", "h2d_stream")   # signal blocks carry epochs: never evicted
+
+
 def op_state(ctx, key) -> dict:
-    """Mutable state of one (operator, shapes, buffers) combination on one rank."""
+    """Mutable state of one (operator, shapes, buffers) combination on one rank.
+
+    A plan bakes addresses, extents, strides and the dtype into its tensor maps, and all of
+    those are part of its key, so an equal key always means equal descriptors (a freed
+    tensor whose address is reused by one of the same geometry gets the same plan, which is
+    then also the right one).  The table is bounded: beyond ``MAX_OP_STATES`` entries the
+    oldest plan entry is dropped (its native plan is destroyed with it; the signal blocks
+    and their epochs stay)."""
     table = ctx._state.setdefault("ops", {})
     st = table.get(key)
     if st is None:
+        if len(table) >= MAX_OP_STATES:
+            for old in table:
+                if old[0] not in _PINNED_STATE_KINDS:
+                    dropped = table.pop(old)
+                    plan = dropped.get("plan")
+                    dropped.clear()
+                    if plan is not None and hasattr(plan, "close"):
+                        plan.close()
+                    break
         st = {"epoch": 0}
         table[key] = st
     return st
@@ -605,7 +625,7 @@ def reduce_scatter(ctx, name: str, A: torch.Tensor, B: torch.Tensor, C: torch.Te
     if push_mode == fg.PUSH_MULTIMEM:
         push_mode = fg.PUSH_STORES  # partials go to one owner, not to everyone
     key = ("reduce_scatter", name, A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K, A.stride(0),
-           B.stride(0), A.dtype, b_is_nk, split_axis, push_mode)
+           B.stride(0), C.stride(0), A.dtype, b_is_nk, split_axis, push_mode)
     st = op_state(ctx, key)
     fast = st.get("fast")
     if fast is not None and a_host is None:

@@ -181,6 +181,11 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
                       st["budget_ns"], torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_collective_launch", rc)
+        if _config().debug and op != OP_ALLREDUCE_ONE_SHOT:
+            from .. import debug as _debug
+
+            _debug.after_collective(heap, st, epoch,
+                                    root=root if op in (OP_BROADCAST, OP_SCATTER) else None)
         return
 
     def make(mask: int):

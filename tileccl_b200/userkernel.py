@@ -76,6 +76,23 @@ class UserKernelModule:
                        C.c_void_p]
         fn.restype = C.c_int
         self._fn = fn
+        self._debug_read = getattr(self._lib, "tileccl_user_debug_read", None)
+        if self._debug_read is not None:
+            self._debug_read.argtypes = [C.c_void_p, C.c_int]
+            self._debug_read.restype = C.c_int
+
+    def debug_record(self, *, clear: bool = True):
+        """The bounds-violation record of this object on the current device (see
+        ``tileccl_b200.debug``); None if the object was built without the entry macros."""
+        if self._debug_read is None:
+            return None
+        from .debug import DebugRecord
+
+        rec = DebugRecord()
+        rc = self._debug_read(C.byref(rec), 1 if clear else 0)
+        if rc != 0:
+            raise RuntimeError(f"reading the debug record failed with CUDA error {rc}")
+        return rec
 
     def launch(self, ctx_or_heap, args: Sequence[int], *, grid: int = 1, block: int = 256,
                rank: Optional[int] = None, stream=None) -> None:
@@ -101,12 +118,17 @@ class UserKernelModule:
 
 
 def compile(source, *, extra_flags: Sequence[str] = (), force: bool = False,
-            entry: str = "tileccl_user_launch") -> UserKernelModule:
+            entry: str = "tileccl_user_launch", debug: bool = False) -> UserKernelModule:
     """Compile ``source`` (a ``.cu`` path) for sm_100a against the device headers and load it.
+
+    ``debug=True`` adds ``-DTILECCL_DEBUG_CHECKS``: translations and symmetric tiles are
+    bounds-checked on the device and violations recorded (``module.debug_record()``).
 
     The shared object is cached under ``build/user_kernels/`` keyed by the source text, the
     headers' time stamps and the flags, so repeated calls cost nothing.
     """
+    if debug:
+        extra_flags = tuple(extra_flags) + tuple(_build.DEBUG_FLAGS)
     src = Path(source).resolve()
     text = src.read_bytes()
     stamp = max((h.stat().st_mtime_ns for h in INCLUDE_DIR.glob("*.cuh")), default=0)

@@ -44,6 +44,7 @@ class RuntimeConfig:
     bootstrap_timeout_ms: Optional[int] = None  # TILECCL_BOOTSTRAP_TIMEOUT_MS
     native_lib: Optional[str] = None       # TILECCL_NATIVE_LIB: another build of the shared object
     no_build: bool = False                 # TILECCL_NO_BUILD: never compile the shared object on import
+    debug: bool = False                    # TILECCL_DEBUG: load the build with recorded bounds checks and check every collective call
     stream_run_shares: Optional[tuple] = None  # TILECCL_STREAM_SHARES: "0.85,0.15" - runs of a host-streamed operand
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
     ll_max_bytes: int = 65536              # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency copy collectives (0 = off)
@@ -76,6 +77,7 @@ class RuntimeConfig:
             bootstrap_timeout_ms=_opt_int(e, "TILECCL_BOOTSTRAP_TIMEOUT_MS"),
             native_lib=e.get("TILECCL_NATIVE_LIB") or None,
             no_build=_flag(e, "TILECCL_NO_BUILD"),
+            debug=_flag(e, "TILECCL_DEBUG"),
             stream_run_shares=(tuple(float(x) for x in e["TILECCL_STREAM_SHARES"].split(","))
                                if e.get("TILECCL_STREAM_SHARES") else None),
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,

@@ -187,6 +187,19 @@ def main() -> int:
     coll.check_status(ctx.heap)
     os.environ["TILECCL_DISABLE_NVLS"] = "0"
     os.environ["TILECCL_FORCE_NVLS"] = "0"
+    # large broadcast: pipelined relay from three ranks on (root sends every piece once, the
+    # others forward theirs); sizes repeat and roots alternate so several epochs are covered
+    if ws >= 3:
+        big = ctx.zeros((12 << 20) // 4 + 4096, dtype=torch.float32)
+        assert coll._relay_ok(ctx.heap, big.numel() * 4, big.data_ptr())
+        for call, root in enumerate([0, ws - 1, 1, 0, 2]):
+            gen = torch.Generator(device=dev).manual_seed(1000 + 10 * call + rank)
+            big.copy_(torch.rand(big.numel(), device=dev, generator=gen))
+            want = gather(big)[root]
+            ops.broadcast(big, ctx=ctx, root=root)
+            check(f"relay broadcast call {call} root {root}", big, want, 1e-7)
+        dist.barrier()
+        coll.check_status(ctx.heap)
 
     tokens, hidden, ffn = 128 * ws * 2, 512, 256 * ws
     mlp = TPMLP(ctx, tokens=tokens, hidden=hidden, ffn=ffn, dtype=torch.bfloat16, seed=3)

@@ -97,6 +97,43 @@ def test_rooted_collectives_with_alternating_roots(ctxs):
         coll.check_status(c.heap)
 
 
+@pytest.mark.parametrize("nbytes, threshold", [(1 << 20, 65536), ((12 << 20) + 4096 * 16, None)])
+def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, monkeypatch):
+    """Three or more ranks, large message: the root sends every piece once and the other
+    ranks forward theirs.  Roots alternate and sizes repeat, so flags and counters of
+    several calls are exercised; a guard region after the buffer must stay untouched."""
+    from tileccl_b200 import ops
+    from tileccl_b200.primitives import collectives as coll
+
+    ws = len(ctxs)
+    if ws < 3:
+        pytest.skip("the relay needs three ranks")
+    if threshold is not None:
+        monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", str(threshold))
+    n = nbytes // 4
+    bufs = [c.zeros(n, dtype=torch.float32) for c in ctxs]
+    guards = [c.zeros(4096, dtype=torch.int32) for c in ctxs]
+    for g in guards:
+        g.fill_(0x5A5A5A5A)
+    assert coll._relay_ok(ctxs[0].heap, nbytes, bufs[0].data_ptr())
+    for call, root in enumerate([0, ws - 1, 1, 0]):
+        want = None
+        for r in range(ws):
+            gen = torch.Generator(device=bufs[r].device).manual_seed(100 * call + r)
+            bufs[r].copy_(torch.rand(n, device=bufs[r].device, generator=gen))
+            if r == root:
+                want = bufs[r].cpu().clone()
+        for r, c in enumerate(ctxs):
+            ops.broadcast(bufs[r], ctx=c, root=root)
+        for r in range(ws):
+            assert torch.equal(bufs[r].cpu(), want), (call, root, r)
+    for c in ctxs:
+        coll.check_status(c.heap)
+    assert ("coll_relay", "broadcast_relay:0") in ctxs[0].heap._state
+    for g in guards:
+        assert int((g != 0x5A5A5A5A).sum()) == 0
+
+
 def test_reset_allocator_drops_internal_workspaces(ctxs):
     """reset -> allocate -> all-reduce and fused op: library counters and staging are re-created
     instead of aliasing the tensors allocated after the reset."""

@@ -39,3 +39,18 @@ def test_stress_thousands_of_calls_with_changing_inputs(ws):
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker, "--calls", "2000"]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert out.returncode == 0 and "MP_STRESS_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])
+
+
+@pytest.mark.parametrize("ws", [2, 4])
+def test_debug_mode_checks_every_collective_call(ws):
+    """TILECCL_DEBUG=1: the library with recorded bounds checks, and after every collective
+    call the status words, the bounds record and the epoch invariants of its counters."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < ws:
+        pytest.skip(f"needs {ws} GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_debug_worker.py")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker]
+    env = dict(os.environ, TILECCL_DEBUG="1")
+    env.pop("TILECCL_NATIVE_LIB", None)
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0 and "MP_DEBUG_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])

@@ -313,3 +313,23 @@ def test_op_state_table_is_bounded_and_keeps_signal_blocks():
     # the same key gives the same state back
     last = ("push_all", "x", _fused.MAX_OP_STATES + 4)
     assert _fused.op_state(ctx, last) is table[last]
+
+
+def test_relay_broadcast_policy_and_piece_size(monkeypatch):
+    from types import SimpleNamespace
+
+    from tileccl_b200.primitives import collectives as coll
+
+    for nbytes in (8 << 20, (8 << 20) + 16, 256 << 20, 1 << 30, 3 << 30):
+        piece = coll.relay_piece_bytes(nbytes)
+        assert piece % 8192 == 0 and piece >= coll.RELAY_MIN_PIECE
+        assert -(-nbytes // piece) <= coll.RELAY_MAX_PIECES
+    assert coll.relay_piece_bytes(256 << 20) == 128 << 10
+    heap3, heap2 = SimpleNamespace(world_size=3), SimpleNamespace(world_size=2)
+    monkeypatch.delenv("TILECCL_BCAST_RELAY_MIN_BYTES", raising=False)
+    assert coll._relay_ok(heap3, 8 << 20, 4096)
+    assert not coll._relay_ok(heap3, (8 << 20) - 16, 4096)      # below the threshold
+    assert not coll._relay_ok(heap2, 64 << 20, 4096)            # one relay only: nothing to gain
+    assert not coll._relay_ok(heap3, (8 << 20) + 8, 4096)       # not a multiple of 16
+    monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", "0")
+    assert not coll._relay_ok(heap3, 64 << 20, 4096)            # switched off

@@ -210,6 +210,17 @@ int tccl_collective_ll_launch(int32_t op, int32_t rank, int32_t world_size, int3
                               uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
                               uint64_t stream);
 
+// Pipelined relay broadcast for large messages on 3..8 ranks: the root sends piece p of
+// `buf` (pieces of `piece_bytes`, at most 4096 of them) once, to the non-root ranks in turn,
+// with a flag; each of those forwards its pieces to the other non-root ranks.  `flags`:
+// 4096 zeroed uint32 on the heap, `counters`: 32 zeroed uint32 on the heap, both per root.
+// phase_mask: 1 announce, 2 root push, 8 relay forwarding, 4 final wait (15 = whole call).
+int tccl_broadcast_relay_launch(int32_t rank, int32_t world_size, int32_t root,
+                                int32_t phase_mask, uint32_t epoch, uint64_t buf, uint64_t bytes,
+                                uint64_t piece_bytes, uint64_t flags, uint64_t counters,
+                                uint64_t heap_base, int64_t heap_stride, int32_t grid,
+                                uint64_t status, uint64_t budget_ns, uint64_t stream);
+
 // --------------------------------------------------------------------------
 // Region push (csrc/kernels/push_region.cu): copies rows x row_bytes (pitch
 // ld_bytes) of this rank's heap to the same place in every peer's heap, band by

@@ -433,6 +433,104 @@ __device__ __forceinline__ bool tile_coll_wait_done(const SymmWindow& w, const T
 }
 
 // ---------------------------------------------------------------------------
+// pipelined relay broadcast (large messages, three or more ranks)
+// ---------------------------------------------------------------------------
+// A multimem.st broadcast is bounded by what ONE source can multicast, and a root that
+// unicasts to n - 1 peers sends every byte n - 1 times.  Here the root sends every byte
+// ONCE: the buffer is cut into pieces, piece p goes to relay rank relay_rank_of(p) (the
+// non-root ranks in turn) together with a flag, and that rank forwards the piece to the
+// other non-root ranks as soon as the flag shows the current call.  Root egress is B,
+// every other rank receives B and sends (n - 2) / (n - 1) B: all links run at the unicast
+// rate and the transfer is pipelined piece by piece.
+//
+// `flags` is a symmetric uint32[kTileRelayMaxPieces] that only ever holds call numbers
+// (epoch = 1, 2, 3 ... per call on this flag block; zero before first use).  Both functions
+// are CTA-collective; CTA `cta` of `n_ctas` takes every n_ctas-th piece.  `bytes` and
+// `piece_bytes` are multiples of 16.
+static constexpr uint32_t kTileRelayMaxPieces = 4096;
+
+__device__ __forceinline__ int relay_rank_of(uint32_t piece, int root, int world_size) {
+  const int k = static_cast<int>(piece % static_cast<uint32_t>(world_size - 1));
+  return k < root ? k : k + 1;                       // k-th rank that is not the root
+}
+
+// Root: piece p -> the same place in relay_rank_of(p)'s heap, then flag[p] = epoch there.
+__device__ __forceinline__ void tile_relay_push(const SymmWindow& w, void* sym_buf, uint64_t bytes,
+                                                uint64_t piece_bytes, uint32_t* sym_flags,
+                                                uint32_t epoch, uint32_t cta, uint32_t n_ctas) {
+  char* b = static_cast<char*>(sym_buf);
+  if (!symm_span_ok(w, b, bytes, w.rank)) return;                  // debug build only
+  const uint32_t n_pieces = static_cast<uint32_t>((bytes + piece_bytes - 1) / piece_bytes);
+  const TileCoop coop = tile_coop_cta();
+  for (uint32_t p = cta; p < n_pieces; p += n_ctas) {
+    const uint64_t off = static_cast<uint64_t>(p) * piece_bytes;
+    const uint64_t len = bytes - off < piece_bytes ? bytes - off : piece_bytes;
+    const int to = relay_rank_of(p, w.rank, w.world_size);
+    coll_detail::copy_vec(coll_detail::peer_of(w, b, to) + off, b + off, len, 16, coop);
+    __syncthreads();                                 // every thread's stores are issued ...
+    if (threadIdx.x == 0) {
+      __threadfence_system();                        // ... and ordered before the flag
+      st_release_sys(coll_detail::peer_of(w, sym_flags, to) + p, epoch);
+    }
+  }
+}
+
+// Relay (every rank but the root): wait for each of its pieces, copy it from the local
+// buffer to the other non-root ranks.  Returns false when a piece never arrived within the
+// budget (the status words then name the piece).
+__device__ __forceinline__ bool tile_relay_forward(const SymmWindow& w, void* sym_buf,
+                                                   uint64_t bytes, uint64_t piece_bytes, int root,
+                                                   const uint32_t* sym_flags, uint32_t epoch,
+                                                   uint32_t cta, uint32_t n_ctas,
+                                                   const WaitBudget& wb, uint32_t* status) {
+  __shared__ int arrived;
+  char* b = static_cast<char*>(sym_buf);
+  if (!symm_span_ok(w, b, bytes, w.rank)) return true;             // debug build only
+  const int ws = w.world_size;
+  const uint32_t n_pieces = static_cast<uint32_t>((bytes + piece_bytes - 1) / piece_bytes);
+  const uint32_t mine = static_cast<uint32_t>(w.rank < root ? w.rank : w.rank - 1);
+  // destination k = 1 .. ws - 1 is rank (rank + k) % ws (peers staggered), the root left out
+  auto dest = [&](int k) -> char* {
+    const int r = (w.rank + k) % ws;
+    return r == root ? nullptr : coll_detail::peer_of(w, b, r);
+  };
+  for (uint32_t p = cta * static_cast<uint32_t>(ws - 1) + mine; p < n_pieces;
+       p += n_ctas * static_cast<uint32_t>(ws - 1)) {
+    if (threadIdx.x == 0) {
+      uint32_t seen = 0;
+      arrived = tile_wait_ge(sym_flags + p, epoch, wb, &seen) ? 1 : 0;
+      if (!arrived) report_status(status, kStatusTimeoutSignal, 65, epoch, seen, w.rank, p);
+    }
+    __syncthreads();
+    if (!arrived) return false;
+    const uint64_t off = static_cast<uint64_t>(p) * piece_bytes;
+    const uint64_t n = (bytes - off < piece_bytes ? bytes - off : piece_bytes) >> 4;
+    constexpr int kU = 4;
+    uint64_t i = threadIdx.x;
+    for (; i + (kU - 1) * blockDim.x < n; i += kU * blockDim.x) {
+      uint4 v[kU];
+#pragma unroll
+      for (int j = 0; j < kU; ++j) v[j] = ld_remote_v4(b + off + ((i + j * blockDim.x) << 4));
+      for (int k = 1; k < ws; ++k) {
+        char* d = dest(k);
+        if (d == nullptr) continue;
+#pragma unroll
+        for (int j = 0; j < kU; ++j) st_remote_v4(d + off + ((i + j * blockDim.x) << 4), v[j]);
+      }
+    }
+    for (; i < n; i += blockDim.x) {
+      const uint4 v = ld_remote_v4(b + off + (i << 4));
+      for (int k = 1; k < ws; ++k) {
+        char* d = dest(k);
+        if (d != nullptr) st_remote_v4(d + off + (i << 4), v);
+      }
+    }
+    __syncthreads();                                 // `arrived` is rewritten for the next piece
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------------------
 // whole calls from inside a user kernel: ONE CTA per rank runs announce -> wait ->
 // move -> publish -> wait.  Every rank must make the same call with the same epoch.
 // Returns false when a wait ran out of its budget (the status words then say where).

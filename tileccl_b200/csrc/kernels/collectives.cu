@@ -174,6 +174,63 @@ __global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const CollParams
 }
 
 // ---------------------------------------------------------------------------
+// Pipelined relay broadcast for large messages on three or more ranks
+// (device/tile_collectives.cuh: tile_relay_push / tile_relay_forward).  The handshake is
+// the all-to-all one: every rank's buffer is written by the root and by the relays.
+// phase_mask: 1 announce, 2 the root's push, 8 the relays' forwarding, 4 final wait; a
+// launch normally runs all of them (15).  With ranks emulated on one GPU the host issues
+// them one by one, the root's push before the relays' forwarding, so no launch waits for
+// a later one.
+// ---------------------------------------------------------------------------
+struct RelayParams {
+  int32_t rank, world_size, root, phase_mask;
+  uint32_t epoch;
+  uint64_t buf;          // local address of the tensor (same offset in every heap)
+  uint64_t bytes;        // multiple of 16
+  uint64_t piece_bytes;  // multiple of 16; ceil(bytes / piece_bytes) <= kTileRelayMaxPieces
+  uint64_t flags;        // local address of the piece flags (uint32[kTileRelayMaxPieces])
+  uint64_t counters;     // local address of the counter block
+  uint64_t heap_base;
+  int64_t heap_stride;
+  uint64_t status, budget_ns;
+};
+
+__global__ void __launch_bounds__(512) broadcast_relay_kernel(const RelayParams p) {
+  __shared__ uint32_t abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  WaitBudget wb;
+  wb.start(p.budget_ns, &abort_word);
+  SymmWindow w;
+  w.base = p.heap_base - static_cast<uint64_t>(p.rank) * static_cast<uint64_t>(p.heap_stride);
+  w.stride = static_cast<uint64_t>(p.heap_stride);
+  w.mc_base = 0;
+  w.rank = p.rank;
+  w.world_size = p.world_size;
+  TileCollSync sync;
+  sync.counters = reinterpret_cast<uint32_t*>(p.counters);
+  sync.epoch = p.epoch;
+  sync.status = reinterpret_cast<uint32_t*>(p.status);
+  sync.root = -1;                                    // all-to-all announcements and completions
+  const bool is_root = p.rank == p.root;
+
+  if ((p.phase_mask & 1) && blockIdx.x == 0) tile_coll_announce(w, sync);
+  if (p.phase_mask & (is_root ? 2 : 8)) {
+    if (tile_coll_wait_ready(w, sync, wb)) {
+      void* buf = reinterpret_cast<void*>(p.buf);
+      uint32_t* flags = reinterpret_cast<uint32_t*>(p.flags);
+      if (is_root)
+        tile_relay_push(w, buf, p.bytes, p.piece_bytes, flags, p.epoch, blockIdx.x, gridDim.x);
+      else
+        tile_relay_forward(w, buf, p.bytes, p.piece_bytes, p.root, flags, p.epoch, blockIdx.x,
+                           gridDim.x, wb, sync.status);
+    }
+    tile_coll_publish(w, sync, gridDim.x);
+  }
+  if ((p.phase_mask & 4) && blockIdx.x == 0) tile_coll_wait_done(w, sync, wb);
+}
+
+// ---------------------------------------------------------------------------
 // Low-latency copy collectives (all-gather, broadcast, scatter) for small messages:
 // data and flag travel in the same 16-byte store (device/tile_ll.cuh), so a call is one
 // NVLink write latency plus one poll instead of announce / move / publish / wait.
@@ -303,6 +360,31 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t rank, int32_t world
   p.counters = counters; p.heap_stride = heap_stride; p.bytes = static_cast<uint32_t>(bytes);
   p.status = status; p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
   ll_copy_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  TCCL_CHECK_CUDA(cudaGetLastError());
+  return kOk;
+}
+
+extern "C" int tccl_broadcast_relay_launch(int32_t rank, int32_t world_size, int32_t root,
+                                           int32_t phase_mask, uint32_t epoch, uint64_t buf,
+                                           uint64_t bytes, uint64_t piece_bytes, uint64_t flags,
+                                           uint64_t counters, uint64_t heap_base,
+                                           int64_t heap_stride, int32_t grid, uint64_t status,
+                                           uint64_t budget_ns, uint64_t stream) {
+  TCCL_CHECK_ARG(world_size >= 3 && world_size <= kMaxRanks, "the relay broadcast needs 3..8 ranks");
+  TCCL_CHECK_ARG(rank >= 0 && rank < world_size && root >= 0 && root < world_size, "bad rank/root");
+  TCCL_CHECK_ARG(buf != 0 && buf % 16 == 0 && bytes > 0 && bytes % 16 == 0,
+                 "buffer and size must be multiples of 16 bytes");
+  TCCL_CHECK_ARG(piece_bytes >= 16 && piece_bytes % 16 == 0, "piece size must be a multiple of 16");
+  TCCL_CHECK_ARG((bytes + piece_bytes - 1) / piece_bytes <= kTileRelayMaxPieces,
+                 "at most " << kTileRelayMaxPieces << " pieces per call");
+  TCCL_CHECK_ARG(flags != 0 && counters != 0 && epoch != 0, "flags, counters and an epoch >= 1");
+  TCCL_CHECK_ARG(grid >= 1, "grid must be >= 1");
+  RelayParams p;
+  p.rank = rank; p.world_size = world_size; p.root = root; p.phase_mask = phase_mask;
+  p.epoch = epoch; p.buf = buf; p.bytes = bytes; p.piece_bytes = piece_bytes; p.flags = flags;
+  p.counters = counters; p.heap_base = heap_base; p.heap_stride = heap_stride; p.status = status;
+  p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
+  broadcast_relay_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   TCCL_CHECK_CUDA(cudaGetLastError());
   return kOk;
 }
@@ -438,6 +520,7 @@ cudaError_t preload_collective_kernels() {
   cudaError_t e = cudaFuncGetAttributes(&a, collective_kernel);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, allreduce_oneshot_kernel);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, ll_copy_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&a, broadcast_relay_kernel);
   return e;
 }
 }  // namespace tileccl

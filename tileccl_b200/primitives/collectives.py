@@ -13,7 +13,9 @@ reduce-scatter  pull own chunk from every rank and sum in fp32
                 (multimem.ld_reduce if NVLS)
 all-reduce      <= 256 KiB: one-shot through a double-buffered staging copy;
                 larger: pull-reduce own chunk, push it to every rank
-broadcast       root pushes to everyone
+broadcast       root pushes to everyone (multimem.st if NVLS); from 8 MiB on three or
+                more ranks: pipelined relay (root sends every byte once, to the other
+                ranks in turn, and each forwards its pieces to the rest)
 scatter         root pushes chunk r to rank r
 =============== =========================================================
 """
@@ -255,6 +257,68 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
     _run(heap, ("ll:" + kind, per_peer_bytes, epoch, root), phases)
 
 
+RELAY_MAX_PIECES = 4096
+RELAY_MIN_PIECE = 16 * 1024
+
+
+def relay_piece_bytes(nbytes: int) -> int:
+    """Piece size of the relay broadcast: about 2048 pieces per message (a piece is the unit
+    of pipelining: the relays start one piece time after the root), at least 16 KiB, in
+    multiples of 8 KiB (one 16-byte access for each of a CTA's 512 threads)."""
+    piece = max(RELAY_MIN_PIECE, -(-nbytes // 2048))
+    return -(-piece // 8192) * 8192
+
+
+def _relay_ok(heap, nbytes: int, ptr: int) -> bool:
+    limit = _config().bcast_relay_min_bytes
+    return (heap.world_size >= 3 and limit > 0 and nbytes >= limit and nbytes % 16 == 0
+            and ptr % 16 == 0)
+
+
+def _launch_relay(heap, root: int, ptr: int, nbytes: int) -> None:
+    """Large broadcast as a pipelined relay (``broadcast_relay_kernel``)."""
+    kind = f"broadcast_relay:{root}"
+    st = heap._state.get(("coll_relay", kind))
+    if st is None:
+        st = {"flags": heap.allocate_signal_buffer(RELAY_MAX_PIECES),
+              "counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0,
+              "status_ptr": _status(heap).data_ptr(),
+              "fn": getattr(_native.load(), "tccl_broadcast_relay_launch")}
+        st["flags_ptr"], st["counters_ptr"] = st["flags"].data_ptr(), st["counters"].data_ptr()
+        heap._state[("coll_relay", kind)] = st
+    st["epoch"] += 1
+    epoch = st["epoch"]
+    piece = relay_piece_bytes(nbytes)
+    n_pieces = -(-nbytes // piece)
+    # the root's CTAs take pieces in turn; a relay owns every (ws - 1)-th piece
+    own = n_pieces if heap.rank == root else -(-n_pieces // (heap.world_size - 1))
+    grid = max(1, min(_sm_count(heap.device), own))
+
+    def go(mask: int):
+        rc = st["fn"](heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, ptr, nbytes,
+                      piece, st["flags_ptr"], st["counters_ptr"], heap.local_base, heap.stride,
+                      grid, st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            _native.check("tccl_broadcast_relay_launch", rc)
+
+    if not heap.emulated and heap.local_group is None:
+        go(15)
+        if _config().debug:
+            from .. import debug as _debug
+
+            _debug.after_collective(heap, st, epoch)
+        return
+
+    def on_dev(mask):
+        def run():
+            with torch.cuda.device(heap.device):
+                go(mask)
+        return run
+
+    phases = [on_dev(1), on_dev(2), on_dev(8), on_dev(4)] if heap.emulated else [on_dev(15)]
+    _run(heap, (kind, nbytes, epoch, root), phases)
+
+
 def _heap_of(heap, ctx):
     if heap is None and ctx is not None:
         heap = ctx.heap
@@ -378,6 +442,9 @@ def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> to
     if _ll_ok(heap, nbytes, tensor.data_ptr()):
         _launch_ll(heap, f"broadcast:{root}", OP_BROADCAST, tensor.data_ptr(), tensor.data_ptr(),
                    nbytes, root=root)
+        return tensor
+    if _relay_ok(heap, nbytes, tensor.data_ptr()):
+        _launch_relay(heap, root, tensor.data_ptr(), nbytes)
         return tensor
     # The rooted handshake only advances the counters between the root and the others, so
     # every root has its own counter block and epoch (roots may alternate call by call).

@@ -48,6 +48,7 @@ class RuntimeConfig:
     stream_run_shares: Optional[tuple] = None  # TILECCL_STREAM_SHARES: "0.85,0.15" - runs of a host-streamed operand
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
     ll_max_bytes: int = 65536              # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency copy collectives (0 = off)
+    bcast_relay_min_bytes: int = 8 << 20   # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never)
     comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
     push_mode_explicit: bool = False       # TILECCL_PUSH_MODE was set (it then overrides a pattern's own choice)
     # feature gates kept from the reference
@@ -82,6 +83,7 @@ class RuntimeConfig:
                                if e.get("TILECCL_STREAM_SHARES") else None),
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
             ll_max_bytes=min(65536, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or 65536))),
+            bcast_relay_min_bytes=max(0, int(e.get("TILECCL_BCAST_RELAY_MIN_BYTES") or (8 << 20))),
             comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
             push_mode_explicit=bool(e.get("TILECCL_PUSH_MODE")),
             experimental_multiprocess_device_collectives=(

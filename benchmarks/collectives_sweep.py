@@ -67,7 +67,7 @@ def sweep_ours(args, rank, ws, dev):
     ctx = tccl.init(heap_size=int(2.5 * args.max_bytes) + (64 << 20))
     rows = []
     for nbytes in sizes(args.min_bytes, args.max_bytes, args.step):
-        for dtype in (torch.float16, torch.float32):
+        for dtype in args.dtype_list:
             es = torch.empty((), dtype=dtype).element_size()
             n = max(ws, nbytes // es // ws * ws)
             ctx.barrier()
@@ -103,6 +103,8 @@ def sweep_ours(args, rank, ws, dev):
                             None),
             }
             for name, (ours, nccl, factor, check) in cases.items():
+                if name not in args.op_list:
+                    continue
                 fill()
                 ctx.barrier()
                 ours()
@@ -127,8 +129,14 @@ def sweep_ours(args, rank, ws, dev):
                     row.update(nccl_ms=ms_n, nccl_bus_gbps=n * es * factor / ms_n / 1e6)
                 rows.append(row)
             coll.check_status(ctx.heap)
+    from tileccl_b200.utils.config import current
+
+    cfg = current()
     payload = {"suite": "collectives_sweep", "impl": "ours", "world_size": ws,
-               "nvls": ctx.heap.has_multicast, "rows": rows}
+               "nvls": ctx.heap.has_multicast and not cfg.disable_nvls,
+               "switches": {"disable_nvls": cfg.disable_nvls, "ll_max_bytes": cfg.ll_max_bytes,
+                            "bcast_relay_min_bytes": cfg.bcast_relay_min_bytes},
+               "rows": rows}
     ctx.barrier()
     ctx.heap.cleanup()
     return payload
@@ -146,7 +154,7 @@ def sweep_reference(args, rank, ws, dev):
     ctx = tileccl.init(backend="cuda", heap_size=8 * args.max_bytes + (64 << 20))
     rows, t_start = [], time.time()
     for nbytes in sizes(args.min_bytes, args.max_bytes, args.step):
-        for dtype in (torch.float16, torch.float32):
+        for dtype in args.dtype_list:
             es = torch.empty((), dtype=dtype).element_size()
             n = max(ws, nbytes // es // ws * ws)
             full = ctx.zeros(n, dtype=dtype)
@@ -162,6 +170,8 @@ def sweep_reference(args, rank, ws, dev):
                 "scatter": (lambda: rcoll.scatter(full, part, ctx.heap, root=0), (ws - 1) / ws),
             }
             for name, (fn, factor) in cases.items():
+                if name not in args.op_list:
+                    continue
                 row = {"collective": name, "bytes": n * es, "dtype": str(dtype).split(".")[-1],
                        "world_size": ws}
                 flag = torch.tensor([1.0 if time.time() - t_start > args.time_budget_s else 0.0],
@@ -187,8 +197,13 @@ def main() -> None:
     ap.add_argument("--step", type=int, default=2, help="ratio between consecutive sizes")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--time-budget-s", type=float, default=240.0, help="reference sweep only")
+    ap.add_argument("--ops", default="allreduce,allgather,reduce_scatter,broadcast,scatter",
+                    help="comma-separated subset of the five collectives")
+    ap.add_argument("--dtypes", default="float16,float32")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
+    args.op_list = [o.strip() for o in args.ops.split(",") if o.strip()]
+    args.dtype_list = [getattr(torch, d.strip()) for d in args.dtypes.split(",") if d.strip()]
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)

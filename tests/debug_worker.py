@@ -60,7 +60,7 @@ def main() -> None:
 
         # 4. collectives of the debug library: right answers, no record
         xs = [c.randn(300_000, dtype=torch.float16) for c in ctxs]
-        want = (xs[0].float() + xs[1].float()).cpu()
+        want = xs[0].float().cpu() + xs[1].float().cpu()
         for c, x in zip(ctxs, xs):
             ops.allreduce(x, ctx=c)
         for c in ctxs:

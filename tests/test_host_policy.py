@@ -333,3 +333,23 @@ def test_relay_broadcast_policy_and_piece_size(monkeypatch):
     assert not coll._relay_ok(heap3, (8 << 20) + 8, 4096)       # not a multiple of 16
     monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", "0")
     assert not coll._relay_ok(heap3, 64 << 20, 4096)            # switched off
+
+
+def test_cached_config_follows_the_environment(monkeypatch):
+    """current() re-parses only when one of the variables it depends on changed, and the list
+    of those variables covers every name from_env() reads."""
+    import re
+
+    from tileccl_b200.utils import config
+
+    src = open(config.__file__).read()
+    read = set(re.findall(r'"(T[iI][lL][eE]CCL_[A-Za-z_0-9]+)"', src))
+    assert read == set(config.ENV_NAMES)
+    monkeypatch.delenv("TILECCL_LL_MAX_BYTES", raising=False)
+    a = config.current()
+    assert config.current() is a                       # unchanged environment: same snapshot
+    monkeypatch.setenv("TILECCL_LL_MAX_BYTES", "4096")
+    b = config.current()
+    assert b is not a and b.ll_max_bytes == 4096
+    monkeypatch.delenv("TILECCL_LL_MAX_BYTES")
+    assert config.current().ll_max_bytes == 65536

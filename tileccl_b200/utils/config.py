@@ -105,9 +105,41 @@ class RuntimeConfig:
         return not self.disable_nvls
 
 
+# Every variable from_env() looks at.  current() compares their raw values with those of the
+# last snapshot, so a launch pays a couple of microseconds instead of a full parse.
+ENV_NAMES = (
+    "TILECCL_PUSH_MODE", "TILECCL_TUNING", "TILECCL_GEMM_2SM", "TILECCL_STATS",
+    "TILECCL_DYNAMIC_TILES", "TILECCL_RS_CTA_PAIRS", "TILECCL_RS_OWN_LAG",
+    "TILECCL_WAIT_BUDGET_US", "TILECCL_DISABLE_NVLS", "TILECCL_FORCE_NVLS", "TILECCL_CALIBRATION",
+    "TILECCL_BOOTSTRAP_TIMEOUT_MS", "TILECCL_NATIVE_LIB", "TILECCL_NO_BUILD", "TILECCL_DEBUG",
+    "TILECCL_STREAM_SHARES", "TILECCL_STREAM_COPY_STREAMS", "TILECCL_LL_MAX_BYTES",
+    "TILECCL_BCAST_RELAY_MIN_BYTES", "TILECCL_COMM_SMS",
+    "TileCCL_ENABLE_EXPERIMENTAL_MULTIPROCESS_DEVICE_COLLECTIVES",
+    "TileCCL_FORCE_MULTIPROCESS_TRANSPORT",
+)
+_ENV_KEYS_RAW = tuple(os.fsencode(n) for n in ENV_NAMES)
+_cached: Optional[tuple] = None      # (fingerprint, RuntimeConfig)
+
+
+def _fingerprint() -> tuple:
+    raw = getattr(os.environ, "_data", None)      # CPython on POSIX: bytes -> bytes
+    if isinstance(raw, dict):
+        get = raw.get
+        return tuple(get(k) for k in _ENV_KEYS_RAW)
+    get = os.environ.get
+    return tuple(get(n) for n in ENV_NAMES)
+
+
 def current() -> RuntimeConfig:
     """The configuration in force right now.  Every module of the library that depends on an
-    environment switch asks here (nothing else reads ``TILECCL_*`` variables); the environment
-    is read afresh on every call, so a variable set mid-program takes effect at the next plan
-    or launch that consults it."""
-    return RuntimeConfig.from_env()
+    environment switch asks here (nothing else reads ``TILECCL_*`` variables).  A variable
+    set mid-program takes effect at the next plan or launch that consults it: the snapshot is
+    re-parsed whenever the raw value of one of ``ENV_NAMES`` differs from the last call's."""
+    global _cached
+    fp = _fingerprint()
+    c = _cached
+    if c is not None and c[0] == fp:
+        return c[1]
+    cfg = RuntimeConfig.from_env()
+    _cached = (fp, cfg)
+    return cfg

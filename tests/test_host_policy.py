@@ -353,3 +353,54 @@ def test_cached_config_follows_the_environment(monkeypatch):
     assert b is not a and b.ll_max_bytes == 4096
     monkeypatch.delenv("TILECCL_LL_MAX_BYTES")
     assert config.current().ll_max_bytes == 65536
+
+
+def test_repeat_collective_calls_reuse_the_resolved_launch(monkeypatch):
+    """Second call on the same buffers: no validation, no policy, next epoch, same arguments;
+    a changed configuration or other buffers take the full path again."""
+    from types import SimpleNamespace
+
+    import torch
+
+    from tileccl_b200 import _native
+    from tileccl_b200.primitives import collectives as coll
+
+    calls = []
+
+    def fake_launch(*args):
+        calls.append(args)
+        return 0
+
+    monkeypatch.setattr(_native, "load", lambda *a, **k: SimpleNamespace(
+        tccl_collective_launch=fake_launch, tccl_collective_ll_launch=fake_launch))
+    monkeypatch.setattr(coll, "_stream_ptr", lambda idx: 0)
+    monkeypatch.delenv("TILECCL_DEBUG", raising=False)
+    monkeypatch.delenv("TILECCL_DISABLE_NVLS", raising=False)
+    dev = torch.device("cpu")
+    monkeypatch.setitem(coll._SM_COUNT, dev, 148)
+    heap = SimpleNamespace(rank=1, world_size=4, emulated=False, local_group=None, device=dev,
+                           multicast_base=0, local_base=1 << 30, stride=1 << 28, has_multicast=False,
+                           _state={}, owns_tensor=lambda t: True,
+                           allocate_signal_buffer=lambda n: torch.zeros(n, dtype=torch.int32))
+    validated = []
+    real_validate = coll._validate
+    monkeypatch.setattr(coll, "_validate", lambda name, t, h: (validated.append(name),
+                                                               real_validate(name, t, h)))
+    src = torch.zeros(4 * 65536, dtype=torch.float32)
+    out = torch.zeros(65536, dtype=torch.float32)
+    coll.reduce_scatter(src, out, heap)
+    assert len(calls) == 1 and len(validated) == 2
+    coll.reduce_scatter(src, out, heap)
+    coll.reduce_scatter(src, out, heap)
+    assert len(calls) == 3 and len(validated) == 2              # repeat calls skipped validation
+    epochs = [c[8] for c in calls]
+    assert epochs == [1, 2, 3]
+    assert all(c[:8] == calls[0][:8] and c[9:] == calls[0][9:] for c in calls)
+    other = torch.zeros(65536, dtype=torch.float32)
+    coll.reduce_scatter(src, other, heap)                       # other buffers: full path
+    assert len(validated) == 4 and calls[-1][8] == 4            # same kind, same counter block
+    monkeypatch.setenv("TILECCL_WAIT_BUDGET_US", "5000")
+    coll.reduce_scatter(src, out, heap)                         # new configuration: full path
+    assert len(validated) == 6 and calls[-1][-2] == 5_000_000 and calls[-1][8] == 5
+    monkeypatch.setenv("TILECCL_DEBUG", "1")                    # debug mode never remembers
+    assert coll._config().debug

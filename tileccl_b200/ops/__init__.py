@@ -28,6 +28,7 @@ import torch
 from . import _fused
 from ._fused import call_stats, check_status, recover
 from ..kernels.fused_gemm import TileCCLTimeoutError
+from ..primitives import collectives as _coll
 
 __all__ = [
     "gemm_allscatter", "gemm_allscatter_sharded", "gemm_allgather", "gemm_reducescatter",
@@ -662,6 +663,8 @@ def build_allgather_plan(src, output, *, ctx=None, storage_kind="symmetric") -> 
 def allgather(src, output, *, ctx=None, storage_kind="symmetric"):
     """Rank-major concatenation of every rank's ``src`` into ``output`` on every rank."""
     ctx = _ctx_or_current(ctx)
+    if _coll.try_fast(ctx.heap, "allgather", src, output):
+        return output
     key = ("allgather", src.data_ptr(), output.data_ptr(), src.numel(), src.dtype, storage_kind)
     return _cached_plan(ctx, key, lambda: build_allgather_plan(
         src, output, ctx=ctx, storage_kind=storage_kind)).execute(src, output, validate=False)
@@ -721,6 +724,8 @@ def build_allreduce_plan(tensor, *, ctx=None, op="sum", storage_kind="symmetric"
 def allreduce(tensor, *, ctx=None, op="sum", storage_kind="symmetric"):
     """In-place sum over ranks."""
     ctx = _ctx_or_current(ctx)
+    if op == "sum" and _coll.try_fast(ctx.heap, "allreduce", tensor):
+        return tensor
     key = ("allreduce", tensor.data_ptr(), tensor.numel(), tensor.dtype, op, storage_kind)
     return _cached_plan(ctx, key, lambda: build_allreduce_plan(
         tensor, ctx=ctx, op=op, storage_kind=storage_kind)).execute(tensor, validate=False)
@@ -770,6 +775,8 @@ def build_reduce_scatter_plan(src, output, *, ctx=None, implementation="auto",
 def reduce_scatter(src, output, *, ctx=None, implementation="auto", storage_kind="symmetric"):
     """``output = sum over ranks of src[rank * n:(rank + 1) * n]`` (rank-major chunks)."""
     ctx = _ctx_or_current(ctx)
+    if _coll.try_fast(ctx.heap, "reduce_scatter", src, output):
+        return output
     key = ("reduce_scatter", src.data_ptr(), output.data_ptr(), src.numel(), src.dtype,
            implementation, storage_kind)
     return _cached_plan(ctx, key, lambda: build_reduce_scatter_plan(
@@ -780,19 +787,19 @@ def reduce_scatter(src, output, *, ctx=None, implementation="auto", storage_kind
 def broadcast(tensor, *, ctx=None, root: int = 0):
     """Every rank's ``tensor`` becomes ``root``'s."""
     ctx = _ctx_or_current(ctx)
+    if _coll.try_fast(ctx.heap, "broadcast", tensor, None, root):
+        return tensor
     _vector_contract("tensor", tensor, ctx)
-    from ..primitives import collectives
-
-    collectives.broadcast(tensor, ctx.heap, root=root, ctx=ctx)
+    _coll.broadcast(tensor, ctx.heap, root=root, ctx=ctx)
     return tensor
 
 
 def scatter(src, output, *, ctx=None, root: int = 0):
     """Rank ``r`` receives chunk ``r`` of ``root``'s ``src``."""
     ctx = _ctx_or_current(ctx)
+    if _coll.try_fast(ctx.heap, "scatter", src, output, root):
+        return output
     _vector_contract("src", src, ctx)
     _vector_contract("output", output, ctx)
-    from ..primitives import collectives
-
-    collectives.scatter(src, output, ctx.heap, root=root, ctx=ctx)
+    _coll.scatter(src, output, ctx.heap, root=root, ctx=ctx)
     return output

@@ -29,6 +29,7 @@ import torch
 
 from .. import _native
 from ..utils.config import current as _config
+from ..utils.config import generation as _config_generation
 from ..kernels.fused_gemm import STATUS_WORDS, raise_on_status
 
 OP_ALLGATHER = 0
@@ -75,8 +76,64 @@ class AllReduceExecutionSpec:
 # --------------------------------------------------------------------------
 # per-heap state
 # --------------------------------------------------------------------------
+_SM_COUNT: dict = {}
+
+
 def _sm_count(device: torch.device) -> int:
-    return torch.cuda.get_device_properties(device).multi_processor_count
+    n = _SM_COUNT.get(device)
+    if n is None:
+        n = _SM_COUNT[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream_ptr(device_index: int) -> int:
+    """Handle of the current stream of ``device_index`` (the cheap way when torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(device_index)
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+# --------------------------------------------------------------------------
+# Repeat calls.  A call on buffers that were seen before (same addresses, sizes, dtype,
+# root, and the same configuration snapshot) skips validation and policy and re-issues the
+# launch through a closure that has everything resolved: for small messages the host side of
+# a call is as long as the device side.  One-process-per-GPU heaps only (emulated ranks
+# replay phases through `_run`), never in debug mode (which checks every call).
+# --------------------------------------------------------------------------
+_FAST_MAX = 4096
+
+
+def _fast_key(kind: str, a: torch.Tensor, b: Optional[torch.Tensor], root: int) -> tuple:
+    if b is None:
+        return (kind, a.data_ptr(), a.numel(), a.dtype, a.is_contiguous(), root,
+                _config_generation())
+    return (kind, a.data_ptr(), b.data_ptr(), a.numel(), b.numel(), a.dtype, b.dtype,
+            a.is_contiguous() and b.is_contiguous(), root, _config_generation())
+
+
+def try_fast(heap, kind: str, a: torch.Tensor, b: Optional[torch.Tensor] = None,
+             root: int = 0) -> bool:
+    """Re-issue a remembered launch; False when this call has to take the full path."""
+    table = heap._state.get("coll_fast")
+    if not table:
+        return False
+    fn = table.get(_fast_key(kind, a, b, root))
+    if fn is None:
+        return False
+    fn()
+    return True
+
+
+def _remember(heap, kind: str, a, b, root: int, relaunch) -> None:
+    if relaunch is None:
+        return
+    table = heap._state.setdefault("coll_fast", {})
+    if len(table) >= _FAST_MAX:
+        table.clear()
+    table[_fast_key(kind, a, b, root)] = relaunch
 
 
 def _counters(heap, kind: str) -> dict:
@@ -162,33 +219,44 @@ def _run(heap, key, phases) -> None:
 
 def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbytes: int, *,
             elem_size: int, root: int = 0, staging: int = 0, stage_slot: int = 0,
-            use_multimem: bool = False, grid: Optional[int] = None, rv_extra=()) -> None:
+            use_multimem: bool = False, grid: Optional[int] = None, rv_extra=()):
+    """Launch one call; returns a closure that repeats it (next epoch, same arguments) on a
+    one-process-per-GPU heap, else None."""
     st = _counters(heap, kind)
-    st["epoch"] += 1
-    epoch = st["epoch"]
     grid = grid or _grid_for(nbytes, heap.device)
     if "status_ptr" not in st:
         st["status_ptr"] = _status(heap).data_ptr()
         st["counters_ptr"] = st["counters"].data_ptr()
-        st["budget_ns"] = _budget_ns()
         st["fn"] = getattr(_native.load(), "tccl_collective_launch")
     status, counters = st["status_ptr"], st["counters_ptr"]
     if not heap.emulated and heap.local_group is None:
         # One process per GPU: a single launch with all three phases, on the current stream
-        # of the current device (the heap's device).  This is the latency path: no closures,
-        # no device switch.
-        rc = st["fn"](op, dtype_code, heap.rank, heap.world_size, root, 1 if use_multimem else 0,
-                      7, elem_size, epoch & 0xFFFFFFFF, src, dst, staging, stage_slot, counters,
-                      heap.multicast_base, heap.local_base, heap.stride, nbytes, grid, status,
-                      st["budget_ns"], torch.cuda.current_stream().cuda_stream)
-        if rc != 0:
-            _native.check("tccl_collective_launch", rc)
-        if _config().debug and op != OP_ALLREDUCE_ONE_SHOT:
-            from .. import debug as _debug
+        # of the current device (the heap's device).  This is the latency path: no device
+        # switch, everything but the epoch and the stream resolved once.
+        fn, rank, ws, mc = st["fn"], heap.rank, heap.world_size, 1 if use_multimem else 0
+        mc_base, local_base, stride = heap.multicast_base, heap.local_base, heap.stride
+        budget, dev_index = _budget_ns(), heap.device.index
 
-            _debug.after_collective(heap, st, epoch,
-                                    root=root if op in (OP_BROADCAST, OP_SCATTER) else None)
-        return
+        def relaunch():
+            st["epoch"] = e = st["epoch"] + 1
+            rc = fn(op, dtype_code, rank, ws, root, mc, 7, elem_size, e & 0xFFFFFFFF, src, dst,
+                    staging, stage_slot, counters, mc_base, local_base, stride, nbytes, grid,
+                    status, budget, _stream_ptr(dev_index))
+            if rc != 0:
+                _native.check("tccl_collective_launch", rc)
+
+        relaunch()
+        if _config().debug:
+            if op != OP_ALLREDUCE_ONE_SHOT:
+                from .. import debug as _debug
+
+                _debug.after_collective(heap, st, st["epoch"],
+                                        root=root if op in (OP_BROADCAST, OP_SCATTER) else None)
+            return None
+        return relaunch
+
+    st["epoch"] += 1
+    epoch = st["epoch"]
 
     def make(mask: int):
         def go():
@@ -206,6 +274,7 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
     else:
         phases = [make(7)]
     _run(heap, (kind, nbytes, epoch) + tuple(rv_extra), phases)
+    return None
 
 
 LL_SLOT_BYTES = 128 * 1024      # staging per (parity, source): 64 KiB of payload as 16-byte lines
@@ -220,8 +289,9 @@ def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
 
 
 def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int, *,
-               root: int = 0) -> None:
-    """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store."""
+               root: int = 0):
+    """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store.
+    Returns a closure that repeats the call (see ``_launch``) or None."""
     st = heap._state.get(("coll_ll", kind))
     if st is None:
         slots = heap.world_size if op == OP_ALLGATHER else 1
@@ -231,10 +301,25 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
                                                                    "tccl_collective_ll_launch")}
         st["stage_ptr"], st["counters_ptr"] = st["stage"].data_ptr(), st["counters"].data_ptr()
         heap._state[("coll_ll", kind)] = st
-    st["epoch"] += 1
-    epoch = st["epoch"]
     lines = per_peer_bytes // 8 * (heap.world_size - 1)      # lines this rank sends or receives
     grid = max(1, min(8, lines // 2048))
+    if not heap.emulated and heap.local_group is None:
+        fn, rank, ws, stride = st["fn"], heap.rank, heap.world_size, heap.stride
+        stage_ptr, counters_ptr, status = st["stage_ptr"], st["counters_ptr"], st["status_ptr"]
+        budget, dev_index = _budget_ns(), heap.device.index
+
+        def relaunch():
+            st["epoch"] = e = st["epoch"] + 1
+            rc = fn(op, rank, ws, root, 3, e & 0xFFFFFFFF, src, dst, stage_ptr, counters_ptr,
+                    stride, per_peer_bytes, grid, status, budget, _stream_ptr(dev_index))
+            if rc != 0:
+                _native.check("tccl_collective_ll_launch", rc)
+
+        relaunch()
+        return None if _config().debug else relaunch
+
+    st["epoch"] += 1
+    epoch = st["epoch"]
 
     def go(mask: int):
         rc = st["fn"](op, heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, src, dst,
@@ -242,10 +327,6 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
                       st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_collective_ll_launch", rc)
-
-    if not heap.emulated and heap.local_group is None:
-        go(3)
-        return
 
     def on_dev(mask):
         def run():
@@ -255,6 +336,7 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
 
     phases = [on_dev(1), on_dev(2)] if heap.emulated else [on_dev(3)]
     _run(heap, ("ll:" + kind, per_peer_bytes, epoch, root), phases)
+    return None
 
 
 RELAY_MAX_PIECES = 4096
@@ -275,8 +357,9 @@ def _relay_ok(heap, nbytes: int, ptr: int) -> bool:
             and ptr % 16 == 0)
 
 
-def _launch_relay(heap, root: int, ptr: int, nbytes: int) -> None:
-    """Large broadcast as a pipelined relay (``broadcast_relay_kernel``)."""
+def _launch_relay(heap, root: int, ptr: int, nbytes: int):
+    """Large broadcast as a pipelined relay (``broadcast_relay_kernel``).  Returns a closure
+    that repeats the call (see ``_launch``) or None."""
     kind = f"broadcast_relay:{root}"
     st = heap._state.get(("coll_relay", kind))
     if st is None:
@@ -286,13 +369,35 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int) -> None:
               "fn": getattr(_native.load(), "tccl_broadcast_relay_launch")}
         st["flags_ptr"], st["counters_ptr"] = st["flags"].data_ptr(), st["counters"].data_ptr()
         heap._state[("coll_relay", kind)] = st
-    st["epoch"] += 1
-    epoch = st["epoch"]
     piece = relay_piece_bytes(nbytes)
     n_pieces = -(-nbytes // piece)
     # the root's CTAs take pieces in turn; a relay owns every (ws - 1)-th piece
     own = n_pieces if heap.rank == root else -(-n_pieces // (heap.world_size - 1))
     grid = max(1, min(_sm_count(heap.device), own))
+    if not heap.emulated and heap.local_group is None:
+        fn, rank, ws = st["fn"], heap.rank, heap.world_size
+        flags_ptr, counters_ptr, status = st["flags_ptr"], st["counters_ptr"], st["status_ptr"]
+        local_base, stride = heap.local_base, heap.stride
+        budget, dev_index = _budget_ns(), heap.device.index
+
+        def relaunch():
+            st["epoch"] = e = st["epoch"] + 1
+            rc = fn(rank, ws, root, 15, e & 0xFFFFFFFF, ptr, nbytes, piece, flags_ptr,
+                    counters_ptr, local_base, stride, grid, status, budget,
+                    _stream_ptr(dev_index))
+            if rc != 0:
+                _native.check("tccl_broadcast_relay_launch", rc)
+
+        relaunch()
+        if _config().debug:
+            from .. import debug as _debug
+
+            _debug.after_collective(heap, st, st["epoch"])
+            return None
+        return relaunch
+
+    st["epoch"] += 1
+    epoch = st["epoch"]
 
     def go(mask: int):
         rc = st["fn"](heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, ptr, nbytes,
@@ -300,14 +405,6 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int) -> None:
                       grid, st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_broadcast_relay_launch", rc)
-
-    if not heap.emulated and heap.local_group is None:
-        go(15)
-        if _config().debug:
-            from .. import debug as _debug
-
-            _debug.after_collective(heap, st, epoch)
-        return
 
     def on_dev(mask):
         def run():
@@ -317,6 +414,7 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int) -> None:
 
     phases = [on_dev(1), on_dev(2), on_dev(8), on_dev(4)] if heap.emulated else [on_dev(15)]
     _run(heap, (kind, nbytes, epoch, root), phases)
+    return None
 
 
 def _heap_of(heap, ctx):
@@ -363,6 +461,8 @@ def allreduce(tensor: torch.Tensor, heap=None, op: str = "sum", *, ctx=None,
               _execution: Optional[AllReduceExecutionSpec] = None) -> torch.Tensor:
     """In-place sum of ``tensor`` over all ranks."""
     heap = _heap_of(heap, ctx)
+    if op == "sum" and try_fast(heap, "allreduce", tensor):
+        return tensor
     _validate("tensor", tensor, heap)
     ex = _execution or resolve_allreduce_execution(tensor, heap=heap, op=op)
     if ex.implementation == "noop":
@@ -378,18 +478,22 @@ def allreduce(tensor: torch.Tensor, heap=None, op: str = "sum", *, ctx=None,
         if stage is None:
             stage = heap.allocate_tensor((2 * ONE_SHOT_MAX_BYTES,), torch.uint8)
             heap._state["coll_stage"] = stage
-        _launch(heap, "allreduce1", OP_ALLREDUCE_ONE_SHOT, code, ptr, ptr, nbytes,
-                staging=stage.data_ptr(), stage_slot=ONE_SHOT_MAX_BYTES, grid=ex.grid_size,
-                elem_size=tensor.element_size())
+        again = _launch(heap, "allreduce1", OP_ALLREDUCE_ONE_SHOT, code, ptr, ptr, nbytes,
+                        staging=stage.data_ptr(), stage_slot=ONE_SHOT_MAX_BYTES,
+                        grid=ex.grid_size, elem_size=tensor.element_size())
     else:
-        _launch(heap, "allreduce2", OP_ALLREDUCE_TWO_SHOT, code, ptr, ptr, nbytes,
-                use_multimem=ex.use_multimem, grid=ex.grid_size, elem_size=tensor.element_size())
+        again = _launch(heap, "allreduce2", OP_ALLREDUCE_TWO_SHOT, code, ptr, ptr, nbytes,
+                        use_multimem=ex.use_multimem, grid=ex.grid_size,
+                        elem_size=tensor.element_size())
+    _remember(heap, "allreduce", tensor, None, 0, again)
     return tensor
 
 
 def allgather(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, ctx=None) -> torch.Tensor:
     """``output[r * n:(r + 1) * n] = rank r's tensor`` on every rank."""
     heap = _heap_of(heap, ctx)
+    if try_fast(heap, "allgather", tensor, output):
+        return output
     _validate("tensor", tensor, heap)
     _validate("output", output, heap)
     if output.numel() != tensor.numel() * heap.world_size or output.dtype != tensor.dtype:
@@ -399,10 +503,13 @@ def allgather(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, ctx=None
         output.view(-1).copy_(tensor.view(-1))
         return output
     if _ll_ok(heap, nbytes, tensor.data_ptr(), output.data_ptr()):
-        _launch_ll(heap, "allgather", OP_ALLGATHER, tensor.data_ptr(), output.data_ptr(), nbytes)
-        return output
-    _launch(heap, "allgather", OP_ALLGATHER, 3, tensor.data_ptr(), output.data_ptr(), nbytes,
-            use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
+        again = _launch_ll(heap, "allgather", OP_ALLGATHER, tensor.data_ptr(), output.data_ptr(),
+                           nbytes)
+    else:
+        again = _launch(heap, "allgather", OP_ALLGATHER, 3, tensor.data_ptr(), output.data_ptr(),
+                        nbytes, use_multimem=_use_multimem(heap, nbytes),
+                        elem_size=tensor.element_size())
+    _remember(heap, "allgather", tensor, output, 0, again)
     return output
 
 
@@ -414,6 +521,8 @@ def reduce_scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, op: st
         raise ValueError(f"only op='sum' is supported, got {op!r}")
     if implementation not in ("auto", "device"):
         raise ValueError("implementation must be 'auto' or 'device' (there is no host reference path)")
+    if try_fast(heap, "reduce_scatter", tensor, output):
+        return output
     _validate("tensor", tensor, heap)
     _validate("output", output, heap)
     if tensor.dtype not in _DTYPE_CODE:
@@ -424,15 +533,18 @@ def reduce_scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, op: st
     if heap.world_size == 1:
         output.view(-1).copy_(tensor.view(-1))
         return output
-    _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype], tensor.data_ptr(),
-            output.data_ptr(), nbytes, use_multimem=_use_multimem(heap, nbytes),
-            elem_size=tensor.element_size())
+    again = _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype],
+                    tensor.data_ptr(), output.data_ptr(), nbytes,
+                    use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
+    _remember(heap, "reduce_scatter", tensor, output, 0, again)
     return output
 
 
 def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> torch.Tensor:
     """Every rank's ``tensor`` becomes ``root``'s (in place)."""
     heap = _heap_of(heap, ctx)
+    if try_fast(heap, "broadcast", tensor, None, root):
+        return tensor
     _validate("tensor", tensor, heap)
     if not 0 <= root < heap.world_size:
         raise ValueError(f"root={root} out of range for world_size={heap.world_size}")
@@ -440,17 +552,18 @@ def broadcast(tensor: torch.Tensor, heap=None, root: int = 0, *, ctx=None) -> to
         return tensor
     nbytes = tensor.numel() * tensor.element_size()
     if _ll_ok(heap, nbytes, tensor.data_ptr()):
-        _launch_ll(heap, f"broadcast:{root}", OP_BROADCAST, tensor.data_ptr(), tensor.data_ptr(),
-                   nbytes, root=root)
-        return tensor
-    if _relay_ok(heap, nbytes, tensor.data_ptr()):
-        _launch_relay(heap, root, tensor.data_ptr(), nbytes)
-        return tensor
-    # The rooted handshake only advances the counters between the root and the others, so
-    # every root has its own counter block and epoch (roots may alternate call by call).
-    _launch(heap, f"broadcast:{root}", OP_BROADCAST, 3, tensor.data_ptr(), tensor.data_ptr(), nbytes,
-            root=root, use_multimem=_use_multimem(heap, nbytes), rv_extra=(root,),
-            elem_size=tensor.element_size())
+        again = _launch_ll(heap, f"broadcast:{root}", OP_BROADCAST, tensor.data_ptr(),
+                           tensor.data_ptr(), nbytes, root=root)
+    elif _relay_ok(heap, nbytes, tensor.data_ptr()):
+        again = _launch_relay(heap, root, tensor.data_ptr(), nbytes)
+    else:
+        # The rooted handshake only advances the counters between the root and the others, so
+        # every root has its own counter block and epoch (roots may alternate call by call).
+        again = _launch(heap, f"broadcast:{root}", OP_BROADCAST, 3, tensor.data_ptr(),
+                        tensor.data_ptr(), nbytes, root=root,
+                        use_multimem=_use_multimem(heap, nbytes), rv_extra=(root,),
+                        elem_size=tensor.element_size())
+    _remember(heap, "broadcast", tensor, None, root, again)
     return tensor
 
 
@@ -458,6 +571,8 @@ def scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, root: int 
             ctx=None) -> torch.Tensor:
     """Rank ``r`` receives ``root``'s ``tensor[r * n:(r + 1) * n]`` in ``output``."""
     heap = _heap_of(heap, ctx)
+    if try_fast(heap, "scatter", tensor, output, root):
+        return output
     _validate("tensor", tensor, heap)
     _validate("output", output, heap)
     if not 0 <= root < heap.world_size:
@@ -469,9 +584,11 @@ def scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, root: int 
         output.view(-1).copy_(tensor.view(-1))
         return output
     if _ll_ok(heap, nbytes, tensor.data_ptr(), output.data_ptr()):
-        _launch_ll(heap, f"scatter:{root}", OP_SCATTER, tensor.data_ptr(), output.data_ptr(), nbytes,
-                   root=root)
-        return output
-    _launch(heap, f"scatter:{root}", OP_SCATTER, 3, tensor.data_ptr(), output.data_ptr(), nbytes, root=root,
-            rv_extra=(root,), elem_size=tensor.element_size())
+        again = _launch_ll(heap, f"scatter:{root}", OP_SCATTER, tensor.data_ptr(),
+                           output.data_ptr(), nbytes, root=root)
+    else:
+        again = _launch(heap, f"scatter:{root}", OP_SCATTER, 3, tensor.data_ptr(),
+                        output.data_ptr(), nbytes, root=root, rv_extra=(root,),
+                        elem_size=tensor.element_size())
+    _remember(heap, "scatter", tensor, output, root, again)
     return output

@@ -119,15 +119,14 @@ ENV_NAMES = (
 )
 _ENV_KEYS_RAW = tuple(os.fsencode(n) for n in ENV_NAMES)
 _cached: Optional[tuple] = None      # (fingerprint, RuntimeConfig)
+_generation = 0                      # how many times the snapshot has been re-parsed
 
 
 def _fingerprint() -> tuple:
     raw = getattr(os.environ, "_data", None)      # CPython on POSIX: bytes -> bytes
     if isinstance(raw, dict):
-        get = raw.get
-        return tuple(get(k) for k in _ENV_KEYS_RAW)
-    get = os.environ.get
-    return tuple(get(n) for n in ENV_NAMES)
+        return tuple(map(raw.get, _ENV_KEYS_RAW))
+    return tuple(map(os.environ.get, ENV_NAMES))
 
 
 def current() -> RuntimeConfig:
@@ -135,11 +134,19 @@ def current() -> RuntimeConfig:
     environment switch asks here (nothing else reads ``TILECCL_*`` variables).  A variable
     set mid-program takes effect at the next plan or launch that consults it: the snapshot is
     re-parsed whenever the raw value of one of ``ENV_NAMES`` differs from the last call's."""
-    global _cached
+    global _cached, _generation
     fp = _fingerprint()
     c = _cached
     if c is not None and c[0] == fp:
         return c[1]
     cfg = RuntimeConfig.from_env()
     _cached = (fp, cfg)
+    _generation += 1
     return cfg
+
+
+def generation() -> int:
+    """A number that changes whenever ``current()`` would return a different snapshot: part of
+    the key of launchers that bake configuration-dependent choices in."""
+    current()
+    return _generation

@@ -117,13 +117,27 @@ def sweep_ours(args, rank, ws, dev):
                     root_full = ref_full.clone()
                     dist.broadcast(root_full, src=0)
                     err = rel_err(part, root_full[rank * (n // ws):(rank + 1) * (n // ws)])
-                e = torch.tensor([err], dtype=torch.float64, device=dev)
+                # a device wait that gave up (status words) fails the row on every rank
+                # instead of being timed 20 more times
+                status = ctx.heap._state.get("status")
+                gave_up = 0.0 if status is None or int(status[0]) == 0 else 1.0
+                e = torch.tensor([err, gave_up], dtype=torch.float64, device=dev)
                 dist.all_reduce(e, op=dist.ReduceOp.MAX)
-                err = float(e.item())
-                ms = timed(ours, iters, dev)
+                err, gave_up = float(e[0].item()), float(e[1].item())
                 row = {"collective": name, "bytes": n * es, "dtype": str(dtype).split(".")[-1],
-                       "world_size": ws, "ms": ms, "bus_gbps": n * es * factor / ms / 1e6,
-                       "max_rel_err_vs_nccl": err, "correct": bool(err <= tol)}
+                       "world_size": ws, "max_rel_err_vs_nccl": err, "correct": bool(err <= tol)}
+                if gave_up:
+                    if status is not None:
+                        row["error"] = f"device wait timed out, status words {status.tolist()}"
+                        status.zero_()
+                    else:
+                        row["error"] = "device wait timed out on a peer"
+                    row["correct"] = False
+                    rows.append(row)
+                    ctx.barrier()
+                    continue
+                ms = timed(ours, iters, dev)
+                row.update(ms=ms, bus_gbps=n * es * factor / ms / 1e6)
                 if nccl is not None:
                     ms_n = timed(nccl, iters, dev)
                     row.update(nccl_ms=ms_n, nccl_bus_gbps=n * es * factor / ms_n / 1e6)

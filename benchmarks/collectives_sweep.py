@@ -11,7 +11,7 @@ run, ``--impl reference``) the reference's Triton collectives.  One process per 
 
 "bytes" is the size of the full buffer (allreduce / broadcast: the tensor; allgather: the
 gathered output; reduce_scatter / scatter: the input).  Device time (CUDA events around
-`iters` back-to-back calls), max over ranks; bus GB/s uses the usual factors (allreduce
+`iters` back-to-back calls, max over ranks, median of three batches); bus GB/s uses the usual factors (allreduce
 2(n-1)/n, allgather / reduce_scatter / scatter (n-1)/n, broadcast 1).  Every row of this
 library is checked once against NCCL's result on the same inputs before it is timed.
 """
@@ -30,21 +30,27 @@ import torch.distributed as dist
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def timed(fn, iters, dev):
+def timed(fn, iters, dev, batches=3):
+    """Per-call device time: `batches` batches of `iters` back-to-back calls, each between two
+    CUDA events; per batch the max over ranks, then the median over batches (one stalled
+    iteration on a shared host otherwise decides a whole row, for either library)."""
     for _ in range(3):
         fn()
-    torch.cuda.synchronize()
-    dist.barrier()
-    s = torch.cuda.Event(enable_timing=True)
-    e = torch.cuda.Event(enable_timing=True)
-    s.record()
-    for _ in range(iters):
-        fn()
-    e.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([s.elapsed_time(e) / iters], dtype=torch.float64, device=dev)
+    per_batch = []
+    for _ in range(batches):
+        torch.cuda.synchronize()
+        dist.barrier()
+        s = torch.cuda.Event(enable_timing=True)
+        e = torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        per_batch.append(s.elapsed_time(e) / iters)
+    t = torch.tensor(per_batch, dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    return float(t.median().item())
 
 
 def sizes(lo, hi, step):
@@ -85,7 +91,7 @@ def sweep_ours(args, rank, ws, dev):
                 ref_part.copy_(part)
 
             ctx.barrier()
-            iters = 20 if nbytes <= (16 << 20) else 5
+            iters = 20 if nbytes <= (16 << 20) else (5 if nbytes <= (256 << 20) else 3)
             tol = 2e-2 if dtype is torch.float16 else 1e-5
             cases = {
                 "allreduce": (lambda: ops.allreduce(full, ctx=ctx), lambda: dist.all_reduce(ref_full),

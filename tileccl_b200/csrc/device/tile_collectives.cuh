@@ -454,6 +454,28 @@ __device__ __forceinline__ int relay_rank_of(uint32_t piece, int root, int world
   return k < root ? k : k + 1;                       // k-th rank that is not the root
 }
 
+namespace coll_detail {
+// 16-byte copy of `n` vectors by one CTA with up to kU loads in flight per thread for ANY
+// n (the slots past the end are predicated off): pieces are a few vectors per thread, and
+// without the loads up front every store would wait for its own load.
+template <int kU>
+__device__ __forceinline__ void copy_piece(char* dst, const char* src, uint64_t n) {
+  for (uint64_t base = threadIdx.x; base < n; base += static_cast<uint64_t>(kU) * blockDim.x) {
+    uint4 v[kU];
+#pragma unroll
+    for (int j = 0; j < kU; ++j) {
+      const uint64_t i = base + static_cast<uint64_t>(j) * blockDim.x;
+      if (i < n) v[j] = ld_remote_v4(src + (i << 4));
+    }
+#pragma unroll
+    for (int j = 0; j < kU; ++j) {
+      const uint64_t i = base + static_cast<uint64_t>(j) * blockDim.x;
+      if (i < n) st_remote_v4(dst + (i << 4), v[j]);
+    }
+  }
+}
+}  // namespace coll_detail
+
 // Root: piece p -> the same place in relay_rank_of(p)'s heap, then flag[p] = epoch there.
 __device__ __forceinline__ void tile_relay_push(const SymmWindow& w, void* sym_buf, uint64_t bytes,
                                                 uint64_t piece_bytes, uint32_t* sym_flags,
@@ -461,12 +483,11 @@ __device__ __forceinline__ void tile_relay_push(const SymmWindow& w, void* sym_b
   char* b = static_cast<char*>(sym_buf);
   if (!symm_span_ok(w, b, bytes, w.rank)) return;                  // debug build only
   const uint32_t n_pieces = static_cast<uint32_t>((bytes + piece_bytes - 1) / piece_bytes);
-  const TileCoop coop = tile_coop_cta();
   for (uint32_t p = cta; p < n_pieces; p += n_ctas) {
     const uint64_t off = static_cast<uint64_t>(p) * piece_bytes;
     const uint64_t len = bytes - off < piece_bytes ? bytes - off : piece_bytes;
     const int to = relay_rank_of(p, w.rank, w.world_size);
-    coll_detail::copy_vec(coll_detail::peer_of(w, b, to) + off, b + off, len, 16, coop);
+    coll_detail::copy_piece<8>(coll_detail::peer_of(w, b, to) + off, b + off, len >> 4);
     __syncthreads();                                 // every thread's stores are issued ...
     if (threadIdx.x == 0) {
       __threadfence_system();                        // ... and ordered before the flag
@@ -505,24 +526,22 @@ __device__ __forceinline__ bool tile_relay_forward(const SymmWindow& w, void* sy
     if (!arrived) return false;
     const uint64_t off = static_cast<uint64_t>(p) * piece_bytes;
     const uint64_t n = (bytes - off < piece_bytes ? bytes - off : piece_bytes) >> 4;
-    constexpr int kU = 4;
-    uint64_t i = threadIdx.x;
-    for (; i + (kU - 1) * blockDim.x < n; i += kU * blockDim.x) {
+    constexpr int kU = 4;                            // loads in flight per thread, any n
+    for (uint64_t base = threadIdx.x; base < n; base += static_cast<uint64_t>(kU) * blockDim.x) {
       uint4 v[kU];
 #pragma unroll
-      for (int j = 0; j < kU; ++j) v[j] = ld_remote_v4(b + off + ((i + j * blockDim.x) << 4));
+      for (int j = 0; j < kU; ++j) {
+        const uint64_t i = base + static_cast<uint64_t>(j) * blockDim.x;
+        if (i < n) v[j] = ld_remote_v4(b + off + (i << 4));
+      }
       for (int k = 1; k < ws; ++k) {
         char* d = dest(k);
         if (d == nullptr) continue;
 #pragma unroll
-        for (int j = 0; j < kU; ++j) st_remote_v4(d + off + ((i + j * blockDim.x) << 4), v[j]);
-      }
-    }
-    for (; i < n; i += blockDim.x) {
-      const uint4 v = ld_remote_v4(b + off + (i << 4));
-      for (int k = 1; k < ws; ++k) {
-        char* d = dest(k);
-        if (d != nullptr) st_remote_v4(d + off + (i << 4), v);
+        for (int j = 0; j < kU; ++j) {
+          const uint64_t i = base + static_cast<uint64_t>(j) * blockDim.x;
+          if (i < n) st_remote_v4(d + off + (i << 4), v[j]);
+        }
       }
     }
     __syncthreads();                                 // `arrived` is rewritten for the next piece

@@ -231,21 +231,59 @@ __global__ void __launch_bounds__(512) broadcast_relay_kernel(const RelayParams 
 }
 
 // ---------------------------------------------------------------------------
-// Low-latency copy collectives (all-gather, broadcast, scatter) for small messages:
-// data and flag travel in the same 16-byte store (device/tile_ll.cuh), so a call is one
-// NVLink write latency plus one poll instead of announce / move / publish / wait.
+// Low-latency collectives (all-gather, broadcast, scatter, reduce-scatter) for small
+// messages: data and flag travel in the same 16-byte store (device/tile_ll.cuh), so a call
+// is one NVLink write latency plus one poll instead of announce / move / publish / wait.
+// Reduce-scatter: every rank sends chunk d of its input to rank d and sums, in fp32 and in
+// rank order, the lines it receives with its own chunk.
 // ---------------------------------------------------------------------------
 struct LLParams {
-  int32_t op, rank, world_size, root, phase_mask;
+  int32_t op, dtype, rank, world_size, root, phase_mask;
   uint32_t epoch;        // 1, 2, 3 ... per call on this staging + counter block (also the flag)
   uint64_t src, dst;     // local addresses
   uint64_t stage;        // this rank's staging: [2 parities][n_slots][kLLSlotBytes]
-  int32_t n_slots;       // world_size (all-gather: one slot per source) or 1 (rooted ops)
+  int32_t n_slots;       // world_size (all-gather, reduce-scatter: one slot per source) or 1 (rooted ops)
   uint64_t counters;     // this rank's block: [0, 8) acknowledgements from rank d, [16] cta_done
   int64_t heap_stride;
   uint32_t bytes;        // payload per (source, destination), multiple of 8, <= kLLMaxBytes
   uint64_t status, budget_ns;
 };
+
+namespace {
+// acc (4 floats for 16-bit types, 2 for fp32) += the 8 payload bytes {d0, d1}
+__device__ __forceinline__ void ll_accumulate(int dtype, float* acc, uint32_t d0, uint32_t d1) {
+  if (dtype == kF32) {
+    acc[0] += __uint_as_float(d0);
+    acc[1] += __uint_as_float(d1);
+  } else if (dtype == kBF16) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d0));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&d1));
+    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  } else {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&d0));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&d1));
+    acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y;
+  }
+}
+__device__ __forceinline__ uint2 ll_finish(int dtype, const float* acc) {
+  uint2 o;
+  if (dtype == kF32) {
+    o.x = __float_as_uint(acc[0]);
+    o.y = __float_as_uint(acc[1]);
+  } else if (dtype == kBF16) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(acc[0], acc[1]);
+    const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2], acc[3]);
+    o.x = *reinterpret_cast<const uint32_t*>(&a);
+    o.y = *reinterpret_cast<const uint32_t*>(&b);
+  } else {
+    const __half2 a = __floats2half2_rn(acc[0], acc[1]);
+    const __half2 b = __floats2half2_rn(acc[2], acc[3]);
+    o.x = *reinterpret_cast<const uint32_t*>(&a);
+    o.y = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  return o;
+}
+}  // namespace
 
 __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
   __shared__ uint32_t abort_word;
@@ -257,7 +295,8 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
   uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
   uint32_t* counters = reinterpret_cast<uint32_t*>(p.counters);
   const int ws = p.world_size, rank = p.rank;
-  const bool rooted = p.op != kAllGather;
+  const bool rooted = p.op != kAllGather && p.op != kReduceScatter;
+  const bool per_dest_chunk = p.op == kScatter || p.op == kReduceScatter;
   const bool sender = !rooted || rank == p.root;
   const bool receiver = !rooted || rank != p.root;
   const uint32_t parity = p.epoch & 1u;
@@ -286,7 +325,7 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
       for (int k = 1; k < ws; ++k) {
         const int d = (rank + k) % ws;
         const char* src = reinterpret_cast<const char*>(p.src) +
-                          (p.op == kScatter ? static_cast<uint64_t>(d) * p.bytes : 0);
+                          (per_dest_chunk ? static_cast<uint64_t>(d) * p.bytes : 0);
         char* lines = reinterpret_cast<char*>(peer_addr(p.stage, d)) + parity_off +
                       static_cast<uint64_t>(slot) * kLLSlotBytes;
         ll_send(lines, src, p.bytes, p.epoch, tid, nthreads);
@@ -309,6 +348,27 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
     bool ok = true;
     if (rooted) {
       ok = ll_recv(reinterpret_cast<char*>(p.dst), stage, p.bytes, p.epoch, tid, nthreads, wb);
+    } else if (p.op == kReduceScatter) {
+      const char* own = reinterpret_cast<const char*>(p.src) + static_cast<uint64_t>(rank) * p.bytes;
+      const uint32_t lines = p.bytes >> 3;
+      for (uint32_t i = tid; i < lines && ok; i += nthreads) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < ws && ok; ++s) {          // rank order: same sum on every path
+          uint32_t d0, d1;
+          if (s == rank) {
+            const uint2 v = *reinterpret_cast<const uint2*>(own + (static_cast<uint64_t>(i) << 3));
+            d0 = v.x; d1 = v.y;
+          } else {
+            ok = ll_load_line(stage + static_cast<uint64_t>(s) * kLLSlotBytes +
+                                  static_cast<uint64_t>(i) * kLLLineBytes,
+                              p.epoch, d0, d1, wb);
+          }
+          if (ok) ll_accumulate(p.dtype, acc, d0, d1);
+        }
+        if (ok)
+          *reinterpret_cast<uint2*>(reinterpret_cast<char*>(p.dst) +
+                                    (static_cast<uint64_t>(i) << 3)) = ll_finish(p.dtype, acc);
+      }
     } else {
       for (int k = 1; k < ws && ok; ++k) {
         const int s = (rank + ws - k) % ws;
@@ -338,13 +398,16 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
 
 using namespace tileccl;
 
-extern "C" int tccl_collective_ll_launch(int32_t op, int32_t rank, int32_t world_size, int32_t root,
+extern "C" int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank,
+                                         int32_t world_size, int32_t root,
                                          int32_t phase_mask, uint32_t epoch, uint64_t src,
                                          uint64_t dst, uint64_t stage, uint64_t counters,
                                          int64_t heap_stride, uint64_t bytes, int32_t grid,
                                          uint64_t status, uint64_t budget_ns, uint64_t stream) {
-  TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter,
-                 "the low-latency path moves copies only (all-gather, broadcast, scatter)");
+  TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter || op == kReduceScatter,
+                 "the low-latency path serves all-gather, broadcast, scatter and reduce-scatter");
+  TCCL_CHECK_ARG(op != kReduceScatter || dtype == kF16 || dtype == kBF16 || dtype == kF32,
+                 "reduce-scatter needs a float dtype (0 fp16, 1 bf16, 2 fp32)");
   TCCL_CHECK_ARG(world_size >= 2 && world_size <= kMaxRanks, "world_size must be 2..8");
   TCCL_CHECK_ARG(rank >= 0 && rank < world_size && root >= 0 && root < world_size, "bad rank/root");
   TCCL_CHECK_ARG(bytes > 0 && bytes <= kLLMaxBytes && bytes % 8 == 0,
@@ -354,9 +417,10 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t rank, int32_t world
   TCCL_CHECK_ARG(epoch != 0, "epoch starts at 1");
   TCCL_CHECK_ARG(grid >= 1 && grid <= 32, "grid must be 1..32");
   LLParams p;
-  p.op = op; p.rank = rank; p.world_size = world_size; p.root = root; p.phase_mask = phase_mask;
+  p.op = op; p.dtype = dtype; p.rank = rank; p.world_size = world_size; p.root = root;
+  p.phase_mask = phase_mask;
   p.epoch = epoch; p.src = src; p.dst = dst; p.stage = stage;
-  p.n_slots = op == kAllGather ? world_size : 1;
+  p.n_slots = (op == kAllGather || op == kReduceScatter) ? world_size : 1;
   p.counters = counters; p.heap_stride = heap_stride; p.bytes = static_cast<uint32_t>(bytes);
   p.status = status; p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
   ll_copy_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);

@@ -10,7 +10,8 @@ Algorithms (all direct, one NVLink hop, any world size 1..8):
 =============== =========================================================
 all-gather      push own chunk into every rank's output (multimem.st if NVLS)
 reduce-scatter  pull own chunk from every rank and sum in fp32
-                (multimem.ld_reduce if NVLS)
+                (multimem.ld_reduce if NVLS); chunks up to 64 KiB: every rank
+                sends chunk d to rank d as flag-in-data lines, the owner sums
 all-reduce      <= 256 KiB: one-shot through a double-buffered staging copy;
                 larger: pull-reduce own chunk, push it to every rank
 broadcast       root pushes to everyone (multimem.st if NVLS); from 8 MiB on three or
@@ -289,12 +290,12 @@ def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
 
 
 def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int, *,
-               root: int = 0):
+               root: int = 0, dtype_code: int = 3):
     """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store.
     Returns a closure that repeats the call (see ``_launch``) or None."""
     st = heap._state.get(("coll_ll", kind))
     if st is None:
-        slots = heap.world_size if op == OP_ALLGATHER else 1
+        slots = heap.world_size if op in (OP_ALLGATHER, OP_REDUCE_SCATTER) else 1
         st = {"stage": heap.allocate_zeroed((2 * slots * LL_SLOT_BYTES,), torch.uint8),
               "counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0,
               "status_ptr": _status(heap).data_ptr(), "fn": getattr(_native.load(),
@@ -310,8 +311,9 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
 
         def relaunch():
             st["epoch"] = e = st["epoch"] + 1
-            rc = fn(op, rank, ws, root, 3, e & 0xFFFFFFFF, src, dst, stage_ptr, counters_ptr,
-                    stride, per_peer_bytes, grid, status, budget, _stream_ptr(dev_index))
+            rc = fn(op, dtype_code, rank, ws, root, 3, e & 0xFFFFFFFF, src, dst, stage_ptr,
+                    counters_ptr, stride, per_peer_bytes, grid, status, budget,
+                    _stream_ptr(dev_index))
             if rc != 0:
                 _native.check("tccl_collective_ll_launch", rc)
 
@@ -322,8 +324,8 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
     epoch = st["epoch"]
 
     def go(mask: int):
-        rc = st["fn"](op, heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, src, dst,
-                      st["stage_ptr"], st["counters_ptr"], heap.stride, per_peer_bytes, grid,
+        rc = st["fn"](op, dtype_code, heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF,
+                      src, dst, st["stage_ptr"], st["counters_ptr"], heap.stride, per_peer_bytes, grid,
                       st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_collective_ll_launch", rc)
@@ -343,11 +345,12 @@ RELAY_MAX_PIECES = 4096
 RELAY_MIN_PIECE = 16 * 1024
 
 
-def relay_piece_bytes(nbytes: int) -> int:
-    """Piece size of the relay broadcast: about 2048 pieces per message (a piece is the unit
-    of pipelining: the relays start one piece time after the root), at least 16 KiB, in
-    multiples of 8 KiB (one 16-byte access for each of a CTA's 512 threads)."""
-    piece = max(RELAY_MIN_PIECE, -(-nbytes // 2048))
+def relay_piece_bytes(nbytes: int, target_pieces: int = 2048) -> int:
+    """Piece size of the relay broadcast: about ``target_pieces`` pieces per message (a piece
+    is the unit of pipelining: the relays start one piece time after the root, and every
+    piece costs one flag and one fence), at least 16 KiB, in multiples of 8 KiB (one 16-byte
+    access for each of a CTA's 512 threads)."""
+    piece = max(RELAY_MIN_PIECE, -(-nbytes // max(16, min(RELAY_MAX_PIECES, target_pieces))))
     return -(-piece // 8192) * 8192
 
 
@@ -369,11 +372,14 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
               "fn": getattr(_native.load(), "tccl_broadcast_relay_launch")}
         st["flags_ptr"], st["counters_ptr"] = st["flags"].data_ptr(), st["counters"].data_ptr()
         heap._state[("coll_relay", kind)] = st
-    piece = relay_piece_bytes(nbytes)
+    cfg = _config()
+    piece = relay_piece_bytes(nbytes, cfg.bcast_relay_pieces)
     n_pieces = -(-nbytes // piece)
-    # the root's CTAs take pieces in turn; a relay owns every (ws - 1)-th piece
+    # the root's CTAs take pieces in turn; a relay owns every (ws - 1)-th piece.  Several
+    # CTAs per SM: while one waits for its stores to be acknowledged (the fence before a
+    # flag) the others keep the link busy.
     own = n_pieces if heap.rank == root else -(-n_pieces // (heap.world_size - 1))
-    grid = max(1, min(_sm_count(heap.device), own))
+    grid = max(1, min(_sm_count(heap.device) * cfg.bcast_relay_ctas_per_sm, own))
     if not heap.emulated and heap.local_group is None:
         fn, rank, ws = st["fn"], heap.rank, heap.world_size
         flags_ptr, counters_ptr, status = st["flags_ptr"], st["counters_ptr"], st["status_ptr"]
@@ -533,9 +539,13 @@ def reduce_scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, op: st
     if heap.world_size == 1:
         output.view(-1).copy_(tensor.view(-1))
         return output
-    again = _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype],
-                    tensor.data_ptr(), output.data_ptr(), nbytes,
-                    use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
+    if _ll_ok(heap, nbytes, tensor.data_ptr(), output.data_ptr()):
+        again = _launch_ll(heap, "reduce_scatter", OP_REDUCE_SCATTER, tensor.data_ptr(),
+                           output.data_ptr(), nbytes, dtype_code=_DTYPE_CODE[tensor.dtype])
+    else:
+        again = _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype],
+                        tensor.data_ptr(), output.data_ptr(), nbytes,
+                        use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
     _remember(heap, "reduce_scatter", tensor, output, 0, again)
     return output
 

@@ -49,6 +49,8 @@ class RuntimeConfig:
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
     ll_max_bytes: int = 65536              # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency copy collectives (0 = off)
     bcast_relay_min_bytes: int = 8 << 20   # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never)
+    bcast_relay_pieces: int = 2048         # TILECCL_BCAST_RELAY_PIECES: pieces a relayed broadcast aims for (16 .. 4096)
+    bcast_relay_ctas_per_sm: int = 2       # TILECCL_BCAST_RELAY_CTAS_PER_SM: CTAs per SM of the relay kernel (1 .. 4)
     comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
     push_mode_explicit: bool = False       # TILECCL_PUSH_MODE was set (it then overrides a pattern's own choice)
     # feature gates kept from the reference
@@ -84,6 +86,8 @@ class RuntimeConfig:
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
             ll_max_bytes=min(65536, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or 65536))),
             bcast_relay_min_bytes=max(0, int(e.get("TILECCL_BCAST_RELAY_MIN_BYTES") or (8 << 20))),
+            bcast_relay_pieces=min(4096, max(16, int(e.get("TILECCL_BCAST_RELAY_PIECES") or 2048))),
+            bcast_relay_ctas_per_sm=min(4, max(1, int(e.get("TILECCL_BCAST_RELAY_CTAS_PER_SM") or 2))),
             comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
             push_mode_explicit=bool(e.get("TILECCL_PUSH_MODE")),
             experimental_multiprocess_device_collectives=(
@@ -113,7 +117,8 @@ ENV_NAMES = (
     "TILECCL_WAIT_BUDGET_US", "TILECCL_DISABLE_NVLS", "TILECCL_FORCE_NVLS", "TILECCL_CALIBRATION",
     "TILECCL_BOOTSTRAP_TIMEOUT_MS", "TILECCL_NATIVE_LIB", "TILECCL_NO_BUILD", "TILECCL_DEBUG",
     "TILECCL_STREAM_SHARES", "TILECCL_STREAM_COPY_STREAMS", "TILECCL_LL_MAX_BYTES",
-    "TILECCL_BCAST_RELAY_MIN_BYTES", "TILECCL_COMM_SMS",
+    "TILECCL_BCAST_RELAY_MIN_BYTES", "TILECCL_BCAST_RELAY_PIECES",
+    "TILECCL_BCAST_RELAY_CTAS_PER_SM", "TILECCL_COMM_SMS",
     "TileCCL_ENABLE_EXPERIMENTAL_MULTIPROCESS_DEVICE_COLLECTIVES",
     "TileCCL_FORCE_MULTIPROCESS_TRANSPORT",
 )

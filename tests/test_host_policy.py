@@ -404,3 +404,14 @@ def test_repeat_collective_calls_reuse_the_resolved_launch(monkeypatch):
     assert len(validated) == 6 and calls[-1][-2] == 5_000_000 and calls[-1][8] == 5
     monkeypatch.setenv("TILECCL_DEBUG", "1")                    # debug mode never remembers
     assert coll._config().debug
+
+
+def test_low_latency_staging_classes():
+    from tileccl_b200.primitives import collectives as coll
+
+    assert coll.ll_slot_bytes(8) == coll.LL_MIN_SLOT_BYTES == 128 * 1024
+    assert coll.ll_slot_bytes(65536) == 128 * 1024
+    assert coll.ll_slot_bytes(65544) == 256 * 1024
+    assert coll.ll_slot_bytes(1 << 20) == 2 << 20
+    for n in (8, 4096, 65536, 100_000, 1 << 20):
+        assert coll.ll_slot_bytes(n) >= 2 * n

@@ -196,7 +196,7 @@ def _declare(lib: C.CDLL) -> None:
         "tccl_prim_test": [i32, i32, i32, i32, i32, u64, u64, u64, u64, u64, u64, u32, u32, u64, u64,
                            u64],
         "tccl_collective_ll_launch": [i32, i32, i32, i32, i32, i32, u32, u64, u64, u64, u64,
-                                      C.c_int64, u64, i32, u64, u64, u64],
+                                      C.c_int64, u64, u64, i32, u64, u64, u64],
         "tccl_p2p_copy": [i32, i32, i32, i32, u64, u64, u64, u64, u64, i32, u64],
         "tccl_broadcast_relay_launch": [i32, i32, i32, i32, u32, u64, u64, u64, u64, u64, u64,
                                         C.c_int64, i32, u64, u64, u64],

@@ -200,17 +200,18 @@ int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t worl
                            uint64_t stream);
 
 // Low-latency form of all-gather, broadcast, scatter (op 0, 4, 5) and reduce-scatter (op 1,
-// `dtype` 0 fp16 / 1 bf16 / 2 fp32; ignored by the copies) for messages of at most 64 KiB
+// `dtype` 0 fp16 / 1 bf16 / 2 fp32; ignored by the copies) for messages of at most 1 MiB
 // per (source, destination): payload and flag travel in the same 16-byte store.  `stage`:
-// this rank's staging on the heap, 2 x slots x 128 KiB (slots = world_size for all-gather
-// and reduce-scatter, else 1); `counters`: 32 zeroed uint32 on the heap; both per collective
-// kind (and root).  phase_mask: bit 0 send, bit 1 receive (3 = whole call).
+// this rank's zeroed staging on the heap, 2 x slots x slot_bytes (slots = world_size for
+// all-gather and reduce-scatter, else 1; slot_bytes >= 2 x bytes, at least 128 KiB);
+// `counters`: 32 zeroed uint32 on the heap; both per collective kind, root and slot size.
+// phase_mask: bit 0 send, bit 1 receive (3 = whole call).
 int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,
                               int32_t root,
                               int32_t phase_mask, uint32_t epoch, uint64_t src, uint64_t dst,
                               uint64_t stage, uint64_t counters, int64_t heap_stride,
-                              uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
-                              uint64_t stream);
+                              uint64_t bytes, uint64_t slot_bytes, int32_t grid, uint64_t status,
+                              uint64_t budget_ns, uint64_t stream);
 
 // Pipelined relay broadcast for large messages on 3..8 ranks: the root sends piece p of
 // `buf` (pieces of `piece_bytes`, at most 4096 of them) once, to the non-root ranks in turn,

@@ -16,10 +16,12 @@
 
 namespace tileccl {
 
-static constexpr uint32_t kLLMaxBytes = 64 * 1024;          // payload per (source, destination)
-static constexpr uint32_t kLLLineBytes = 16;
-static constexpr uint32_t kLLMaxLines = kLLMaxBytes / 8;    // 8 payload bytes per line
-static constexpr uint64_t kLLSlotBytes = static_cast<uint64_t>(kLLMaxLines) * kLLLineBytes;
+static constexpr uint32_t kLLMaxBytes = 1024 * 1024;        // payload per (source, destination)
+static constexpr uint32_t kLLLineBytes = 16;                // 8 payload bytes per line
+// A staging slot holds the lines of one (source, destination) message: 2 bytes of staging
+// per payload byte.  The slot size is a launch parameter (the host sizes the staging for the
+// message class in use), at least kLLMinSlotBytes.
+static constexpr uint64_t kLLMinSlotBytes = 128 * 1024;
 
 __device__ __forceinline__ void ll_store_line(void* line, uint32_t d0, uint32_t d1, uint32_t flag) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(line), "r"(d0), "r"(flag),

@@ -241,7 +241,8 @@ struct LLParams {
   int32_t op, dtype, rank, world_size, root, phase_mask;
   uint32_t epoch;        // 1, 2, 3 ... per call on this staging + counter block (also the flag)
   uint64_t src, dst;     // local addresses
-  uint64_t stage;        // this rank's staging: [2 parities][n_slots][kLLSlotBytes]
+  uint64_t stage;        // this rank's staging: [2 parities][n_slots][slot_bytes]
+  uint64_t slot_bytes;   // staging per (parity, source): >= 2 * bytes
   int32_t n_slots;       // world_size (all-gather, reduce-scatter: one slot per source) or 1 (rooted ops)
   uint64_t counters;     // this rank's block: [0, 8) acknowledgements from rank d, [16] cta_done
   int64_t heap_stride;
@@ -300,7 +301,7 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
   const bool sender = !rooted || rank == p.root;
   const bool receiver = !rooted || rank != p.root;
   const uint32_t parity = p.epoch & 1u;
-  const uint64_t parity_off = static_cast<uint64_t>(parity) * p.n_slots * kLLSlotBytes;
+  const uint64_t parity_off = static_cast<uint64_t>(parity) * p.n_slots * p.slot_bytes;
   const uint32_t tid = blockIdx.x * blockDim.x + threadIdx.x, nthreads = gridDim.x * blockDim.x;
   auto peer_addr = [&](uint64_t local, int r) {
     return local + static_cast<uint64_t>(static_cast<int64_t>(r - rank) * p.heap_stride);
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
         const char* src = reinterpret_cast<const char*>(p.src) +
                           (per_dest_chunk ? static_cast<uint64_t>(d) * p.bytes : 0);
         char* lines = reinterpret_cast<char*>(peer_addr(p.stage, d)) + parity_off +
-                      static_cast<uint64_t>(slot) * kLLSlotBytes;
+                      static_cast<uint64_t>(slot) * p.slot_bytes;
         ll_send(lines, src, p.bytes, p.epoch, tid, nthreads);
       }
       // this rank's own part never leaves the GPU
@@ -359,7 +360,7 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
             const uint2 v = *reinterpret_cast<const uint2*>(own + (static_cast<uint64_t>(i) << 3));
             d0 = v.x; d1 = v.y;
           } else {
-            ok = ll_load_line(stage + static_cast<uint64_t>(s) * kLLSlotBytes +
+            ok = ll_load_line(stage + static_cast<uint64_t>(s) * p.slot_bytes +
                                   static_cast<uint64_t>(i) * kLLLineBytes,
                               p.epoch, d0, d1, wb);
           }
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
       for (int k = 1; k < ws && ok; ++k) {
         const int s = (rank + ws - k) % ws;
         ok = ll_recv(reinterpret_cast<char*>(p.dst) + static_cast<uint64_t>(s) * p.bytes,
-                     stage + static_cast<uint64_t>(s) * kLLSlotBytes, p.bytes, p.epoch, tid,
+                     stage + static_cast<uint64_t>(s) * p.slot_bytes, p.bytes, p.epoch, tid,
                      nthreads, wb);
       }
     }
@@ -402,7 +403,8 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank
                                          int32_t world_size, int32_t root,
                                          int32_t phase_mask, uint32_t epoch, uint64_t src,
                                          uint64_t dst, uint64_t stage, uint64_t counters,
-                                         int64_t heap_stride, uint64_t bytes, int32_t grid,
+                                         int64_t heap_stride, uint64_t bytes,
+                                         uint64_t slot_bytes, int32_t grid,
                                          uint64_t status, uint64_t budget_ns, uint64_t stream) {
   TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter || op == kReduceScatter,
                  "the low-latency path serves all-gather, broadcast, scatter and reduce-scatter");
@@ -415,11 +417,13 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank
   TCCL_CHECK_ARG(src % 8 == 0 && dst % 8 == 0 && stage % 16 == 0 && stage != 0 && counters != 0,
                  "buffers must be 8-byte aligned and staging / counters present");
   TCCL_CHECK_ARG(epoch != 0, "epoch starts at 1");
-  TCCL_CHECK_ARG(grid >= 1 && grid <= 32, "grid must be 1..32");
+  TCCL_CHECK_ARG(slot_bytes >= kLLMinSlotBytes && slot_bytes % 16 == 0 && slot_bytes >= 2 * bytes,
+                 "a staging slot holds 2 bytes per payload byte, at least " << kLLMinSlotBytes);
+  TCCL_CHECK_ARG(grid >= 1 && grid <= 64, "grid must be 1..64");
   LLParams p;
   p.op = op; p.dtype = dtype; p.rank = rank; p.world_size = world_size; p.root = root;
   p.phase_mask = phase_mask;
-  p.epoch = epoch; p.src = src; p.dst = dst; p.stage = stage;
+  p.epoch = epoch; p.src = src; p.dst = dst; p.stage = stage; p.slot_bytes = slot_bytes;
   p.n_slots = (op == kAllGather || op == kReduceScatter) ? world_size : 1;
   p.counters = counters; p.heap_stride = heap_stride; p.bytes = static_cast<uint32_t>(bytes);
   p.status = status; p.budget_ns = budget_ns ? budget_ns : 2000000000ull;

@@ -130,10 +130,13 @@ def recover(ctx) -> None:
     if heap is not None:
         # the stand-alone collectives keep their counter blocks and epochs on the heap object
         for key, st in heap._state.items():
-            if isinstance(key, tuple) and key and key[0] in ("coll", "coll_ll") and isinstance(st, dict):
+            if (isinstance(key, tuple) and key and key[0] in ("coll", "coll_ll", "coll_relay")
+                    and isinstance(st, dict)):
                 st["counters"].zero_()
                 if "stage" in st:
                     st["stage"].zero_()      # stale low-latency lines carry old flags
+                if "flags" in st:
+                    st["flags"].zero_()      # piece flags of the relay broadcast hold call numbers
                 st["epoch"] = 0
         hs = heap._state.get("status")
         if hs is not None:

@@ -278,8 +278,15 @@ def _launch(heap, kind: str, op: int, dtype_code: int, src: int, dst: int, nbyte
     return None
 
 
-LL_SLOT_BYTES = 128 * 1024      # staging per (parity, source): 64 KiB of payload as 16-byte lines
-LL_MAX_BYTES = 64 * 1024
+LL_MIN_SLOT_BYTES = 128 * 1024  # staging per (parity, source): 64 KiB of payload as 16-byte lines
+LL_MAX_BYTES = 1024 * 1024      # what the kernel accepts; the policy limit is RuntimeConfig.ll_max_bytes
+
+
+def ll_slot_bytes(per_peer_bytes: int) -> int:
+    """Staging slot of the message class of ``per_peer_bytes``: two bytes of staging per
+    payload byte, sized for the next power of two so that neighbouring sizes share staging."""
+    cls = 1 << max(0, (max(1, per_peer_bytes) - 1).bit_length())
+    return max(LL_MIN_SLOT_BYTES, 2 * cls)
 
 
 def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
@@ -293,17 +300,18 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
                root: int = 0, dtype_code: int = 3):
     """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store.
     Returns a closure that repeats the call (see ``_launch``) or None."""
-    st = heap._state.get(("coll_ll", kind))
+    slot_bytes = ll_slot_bytes(per_peer_bytes)
+    st = heap._state.get(("coll_ll", kind, slot_bytes))
     if st is None:
         slots = heap.world_size if op in (OP_ALLGATHER, OP_REDUCE_SCATTER) else 1
-        st = {"stage": heap.allocate_zeroed((2 * slots * LL_SLOT_BYTES,), torch.uint8),
+        st = {"stage": heap.allocate_zeroed((2 * slots * slot_bytes,), torch.uint8),
               "counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0,
               "status_ptr": _status(heap).data_ptr(), "fn": getattr(_native.load(),
                                                                    "tccl_collective_ll_launch")}
         st["stage_ptr"], st["counters_ptr"] = st["stage"].data_ptr(), st["counters"].data_ptr()
-        heap._state[("coll_ll", kind)] = st
+        heap._state[("coll_ll", kind, slot_bytes)] = st
     lines = per_peer_bytes // 8 * (heap.world_size - 1)      # lines this rank sends or receives
-    grid = max(1, min(8, lines // 2048))
+    grid = max(1, min(8 if per_peer_bytes <= 65536 else 64, lines // 2048))
     if not heap.emulated and heap.local_group is None:
         fn, rank, ws, stride = st["fn"], heap.rank, heap.world_size, heap.stride
         stage_ptr, counters_ptr, status = st["stage_ptr"], st["counters_ptr"], st["status_ptr"]
@@ -312,7 +320,7 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
         def relaunch():
             st["epoch"] = e = st["epoch"] + 1
             rc = fn(op, dtype_code, rank, ws, root, 3, e & 0xFFFFFFFF, src, dst, stage_ptr,
-                    counters_ptr, stride, per_peer_bytes, grid, status, budget,
+                    counters_ptr, stride, per_peer_bytes, slot_bytes, grid, status, budget,
                     _stream_ptr(dev_index))
             if rc != 0:
                 _native.check("tccl_collective_ll_launch", rc)
@@ -325,7 +333,8 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
 
     def go(mask: int):
         rc = st["fn"](op, dtype_code, heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF,
-                      src, dst, st["stage_ptr"], st["counters_ptr"], heap.stride, per_peer_bytes, grid,
+                      src, dst, st["stage_ptr"], st["counters_ptr"], heap.stride, per_peer_bytes,
+                      slot_bytes, grid,
                       st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_collective_ll_launch", rc)
@@ -337,7 +346,7 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
         return run
 
     phases = [on_dev(1), on_dev(2)] if heap.emulated else [on_dev(3)]
-    _run(heap, ("ll:" + kind, per_peer_bytes, epoch, root), phases)
+    _run(heap, ("ll:" + kind, per_peer_bytes, slot_bytes, epoch, root), phases)
     return None
 
 

@@ -97,7 +97,7 @@ def test_rooted_collectives_with_alternating_roots(ctxs):
         coll.check_status(c.heap)
 
 
-@pytest.mark.parametrize("nbytes, threshold", [(1 << 20, 65536), ((12 << 20) + 4096 * 16, None)])
+@pytest.mark.parametrize("nbytes, threshold", [(2 << 20, 65536), ((12 << 20) + 4096 * 16, None)])
 def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, monkeypatch):
     """Three or more ranks, large message: the root sends every piece once and the other
     ranks forward theirs.  Roots alternate and sizes repeat, so flags and counters of
@@ -186,7 +186,9 @@ def test_allreduce_plan_metadata(ctxs):
     c = ctxs[0]
     small = ops.build_allreduce_plan(c.zeros(1024, dtype=torch.float16), ctx=c)
     big = ops.build_allreduce_plan(c.zeros(1 << 20, dtype=torch.float16), ctx=c)
-    assert small.implementation == "device_one_shot" and small.message_regime == "latency"
+    odd = ops.build_allreduce_plan(c.zeros(1001, dtype=torch.float16), ctx=c)
+    assert small.implementation == "device_one_shot_ll" and small.message_regime == "latency"
+    assert odd.implementation == "device_one_shot"       # not a multiple of 8 bytes: staged copy
     assert big.implementation == "device_two_shot" and big.message_regime == "bandwidth"
     assert big.to_dict()["num_chunks"] == len(ctxs)
     with pytest.raises(ValueError):

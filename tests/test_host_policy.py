@@ -277,7 +277,7 @@ def test_runtime_config_covers_the_measured_choices():
 
     cfg = RuntimeConfig.from_env({})
     assert not cfg.dynamic_tiles and cfg.call_stats and cfg.rs_cta_pairs is None
-    assert cfg.ll_max_bytes == 65536 and cfg.stream_run_shares is None and cfg.stream_copy_streams == 1
+    assert cfg.ll_max_bytes == 1 << 20 and cfg.stream_run_shares is None and cfg.stream_copy_streams == 1
     cfg = RuntimeConfig.from_env({"TILECCL_DYNAMIC_TILES": "1", "TILECCL_STATS": "0",
                                   "TILECCL_RS_CTA_PAIRS": "1", "TILECCL_LL_MAX_BYTES": "4096",
                                   "TILECCL_STREAM_SHARES": "0.85,0.15"})
@@ -352,7 +352,7 @@ def test_cached_config_follows_the_environment(monkeypatch):
     b = config.current()
     assert b is not a and b.ll_max_bytes == 4096
     monkeypatch.delenv("TILECCL_LL_MAX_BYTES")
-    assert config.current().ll_max_bytes == 65536
+    assert config.current().ll_max_bytes == 1 << 20
 
 
 def test_repeat_collective_calls_reuse_the_resolved_launch(monkeypatch):
@@ -376,6 +376,7 @@ def test_repeat_collective_calls_reuse_the_resolved_launch(monkeypatch):
     monkeypatch.setattr(coll, "_stream_ptr", lambda idx: 0)
     monkeypatch.delenv("TILECCL_DEBUG", raising=False)
     monkeypatch.delenv("TILECCL_DISABLE_NVLS", raising=False)
+    monkeypatch.setenv("TILECCL_LL_MAX_BYTES", "0")           # the three-phase kernel's launcher
     dev = torch.device("cpu")
     monkeypatch.setitem(coll._SM_COUNT, dev, 148)
     heap = SimpleNamespace(rank=1, world_size=4, emulated=False, local_group=None, device=dev,

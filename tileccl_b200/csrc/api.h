@@ -199,11 +199,12 @@ int tccl_collective_launch(int32_t op, int32_t dtype, int32_t rank, int32_t worl
                            uint64_t bytes, int32_t grid, uint64_t status, uint64_t budget_ns,
                            uint64_t stream);
 
-// Low-latency form of all-gather, broadcast, scatter (op 0, 4, 5) and reduce-scatter (op 1,
-// `dtype` 0 fp16 / 1 bf16 / 2 fp32; ignored by the copies) for messages of at most 1 MiB
+// Low-latency form of all-gather, broadcast, scatter (op 0, 4, 5), reduce-scatter (op 1) and
+// one-shot all-reduce (op 3, in place: src == dst; `dtype` 0 fp16 / 1 bf16 / 2 fp32 for the
+// two reductions, ignored by the copies) for messages of at most 1 MiB
 // per (source, destination): payload and flag travel in the same 16-byte store.  `stage`:
 // this rank's zeroed staging on the heap, 2 x slots x slot_bytes (slots = world_size for
-// all-gather and reduce-scatter, else 1; slot_bytes >= 2 x bytes, at least 128 KiB);
+// all-gather, reduce-scatter and all-reduce, else 1; slot_bytes >= 2 x bytes, at least 128 KiB);
 // `counters`: 32 zeroed uint32 on the heap; both per collective kind, root and slot size.
 // phase_mask: bit 0 send, bit 1 receive (3 = whole call).
 int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank, int32_t world_size,

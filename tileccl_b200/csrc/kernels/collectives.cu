@@ -235,7 +235,9 @@ __global__ void __launch_bounds__(512) broadcast_relay_kernel(const RelayParams 
 // messages: data and flag travel in the same 16-byte store (device/tile_ll.cuh), so a call
 // is one NVLink write latency plus one poll instead of announce / move / publish / wait.
 // Reduce-scatter: every rank sends chunk d of its input to rank d and sums, in fp32 and in
-// rank order, the lines it receives with its own chunk.
+// rank order, the lines it receives with its own chunk.  All-reduce (one-shot): every rank
+// sends its whole vector to every peer and sums what it receives with its own, in place (a
+// thread sends and later overwrites the same lines, so the send reads before the sum writes).
 // ---------------------------------------------------------------------------
 struct LLParams {
   int32_t op, dtype, rank, world_size, root, phase_mask;
@@ -296,7 +298,8 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
   uint32_t* status = reinterpret_cast<uint32_t*>(p.status);
   uint32_t* counters = reinterpret_cast<uint32_t*>(p.counters);
   const int ws = p.world_size, rank = p.rank;
-  const bool rooted = p.op != kAllGather && p.op != kReduceScatter;
+  const bool reducing = p.op == kReduceScatter || p.op == kAllReduceOneShot;
+  const bool rooted = p.op != kAllGather && !reducing;
   const bool per_dest_chunk = p.op == kScatter || p.op == kReduceScatter;
   const bool sender = !rooted || rank == p.root;
   const bool receiver = !rooted || rank != p.root;
@@ -349,8 +352,9 @@ __global__ void __launch_bounds__(512) ll_copy_kernel(const LLParams p) {
     bool ok = true;
     if (rooted) {
       ok = ll_recv(reinterpret_cast<char*>(p.dst), stage, p.bytes, p.epoch, tid, nthreads, wb);
-    } else if (p.op == kReduceScatter) {
-      const char* own = reinterpret_cast<const char*>(p.src) + static_cast<uint64_t>(rank) * p.bytes;
+    } else if (reducing) {
+      const char* own = reinterpret_cast<const char*>(p.src) +
+                        (per_dest_chunk ? static_cast<uint64_t>(rank) * p.bytes : 0);
       const uint32_t lines = p.bytes >> 3;
       for (uint32_t i = tid; i < lines && ok; i += nthreads) {
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -406,10 +410,13 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank
                                          int64_t heap_stride, uint64_t bytes,
                                          uint64_t slot_bytes, int32_t grid,
                                          uint64_t status, uint64_t budget_ns, uint64_t stream) {
-  TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter || op == kReduceScatter,
-                 "the low-latency path serves all-gather, broadcast, scatter and reduce-scatter");
-  TCCL_CHECK_ARG(op != kReduceScatter || dtype == kF16 || dtype == kBF16 || dtype == kF32,
-                 "reduce-scatter needs a float dtype (0 fp16, 1 bf16, 2 fp32)");
+  TCCL_CHECK_ARG(op == kAllGather || op == kBroadcast || op == kScatter || op == kReduceScatter ||
+                     op == kAllReduceOneShot,
+                 "the low-latency path serves all-gather, broadcast, scatter, reduce-scatter and "
+                 "one-shot all-reduce");
+  TCCL_CHECK_ARG((op != kReduceScatter && op != kAllReduceOneShot) || dtype == kF16 ||
+                     dtype == kBF16 || dtype == kF32,
+                 "a reduction needs a float dtype (0 fp16, 1 bf16, 2 fp32)");
   TCCL_CHECK_ARG(world_size >= 2 && world_size <= kMaxRanks, "world_size must be 2..8");
   TCCL_CHECK_ARG(rank >= 0 && rank < world_size && root >= 0 && root < world_size, "bad rank/root");
   TCCL_CHECK_ARG(bytes > 0 && bytes <= kLLMaxBytes && bytes % 8 == 0,
@@ -424,7 +431,7 @@ extern "C" int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank
   p.op = op; p.dtype = dtype; p.rank = rank; p.world_size = world_size; p.root = root;
   p.phase_mask = phase_mask;
   p.epoch = epoch; p.src = src; p.dst = dst; p.stage = stage; p.slot_bytes = slot_bytes;
-  p.n_slots = (op == kAllGather || op == kReduceScatter) ? world_size : 1;
+  p.n_slots = (op == kAllGather || op == kReduceScatter || op == kAllReduceOneShot) ? world_size : 1;
   p.counters = counters; p.heap_stride = heap_stride; p.bytes = static_cast<uint32_t>(bytes);
   p.status = status; p.budget_ns = budget_ns ? budget_ns : 2000000000ull;
   ll_copy_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);

@@ -12,8 +12,10 @@ all-gather      push own chunk into every rank's output (multimem.st if NVLS)
 reduce-scatter  pull own chunk from every rank and sum in fp32
                 (multimem.ld_reduce if NVLS); chunks up to 64 KiB: every rank
                 sends chunk d to rank d as flag-in-data lines, the owner sums
-all-reduce      <= 256 KiB: one-shot through a double-buffered staging copy;
-                larger: pull-reduce own chunk, push it to every rank
+all-reduce      small (up to 1 MiB at two ranks, 256 KiB at eight): one-shot over
+                flag-in-data lines; <= 256 KiB otherwise: one-shot through a
+                double-buffered staging copy; larger: pull-reduce own chunk, push
+                it to every rank
 broadcast       root pushes to everyone (multimem.st if NVLS); from 8 MiB on three or
                 more ranks: pipelined relay (root sends every byte once, to the other
                 ranks in turn, and each forwards its pieces to the rest)
@@ -296,6 +298,16 @@ def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
             and all(p % 8 == 0 for p in ptrs))
 
 
+LL_ALLREDUCE_MAX_INGRESS = 2 << 20   # payload bytes a rank receives in a low-latency all-reduce
+
+
+def _ll_allreduce_ok(heap, nbytes: int, ptr: int) -> bool:
+    """One-shot all-reduce over flag-in-data lines?  Every rank receives the whole vector
+    from every peer (twice the bytes on the wire), which pays while that stays small."""
+    return (_ll_ok(heap, nbytes, ptr)
+            and nbytes * (heap.world_size - 1) <= LL_ALLREDUCE_MAX_INGRESS)
+
+
 def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int, *,
                root: int = 0, dtype_code: int = 3):
     """One low-latency copy collective (``ll_copy_kernel``): payload and flag share a store.
@@ -303,7 +315,8 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
     slot_bytes = ll_slot_bytes(per_peer_bytes)
     st = heap._state.get(("coll_ll", kind, slot_bytes))
     if st is None:
-        slots = heap.world_size if op in (OP_ALLGATHER, OP_REDUCE_SCATTER) else 1
+        slots = heap.world_size if op in (OP_ALLGATHER, OP_REDUCE_SCATTER,
+                                           OP_ALLREDUCE_ONE_SHOT) else 1
         st = {"stage": heap.allocate_zeroed((2 * slots * slot_bytes,), torch.uint8),
               "counters": heap.allocate_signal_buffer(_COUNTER_WORDS), "epoch": 0,
               "status_ptr": _status(heap).data_ptr(), "fn": getattr(_native.load(),
@@ -458,6 +471,12 @@ def resolve_allreduce_execution(tensor: torch.Tensor, *, heap, op: str = "sum",
         return AllReduceExecutionSpec("noop", "local_identity", "local_identity", regime, nbytes,
                                       tensor.numel(), 1, 1, 0, 0, 0, "none", "none", "none", False)
     grid = _grid_for(nbytes, heap.device) if tensor.is_cuda else 1
+    if _ll_allreduce_ok(heap, nbytes, tensor.data_ptr()):
+        return AllReduceExecutionSpec(
+            "device_one_shot_ll", "flag_in_data_parity_ack", "generic_multi_peer", regime, nbytes,
+            tensor.numel(), 1, 2, max(1, min(64, nbytes // 8 * (ws - 1) // 2048)), _THREADS // 32,
+            2 * ws * ll_slot_bytes(nbytes) + 4 * _COUNTER_WORDS, "epoch_parity_double_buffer",
+            "grid_stride_multi_cta", "monotonic_counter", False)
     if nbytes <= ONE_SHOT_MAX_BYTES:
         slot = (nbytes + 15) // 16 * 16
         return AllReduceExecutionSpec(
@@ -485,7 +504,10 @@ def allreduce(tensor: torch.Tensor, heap=None, op: str = "sum", *, ctx=None,
     nbytes = ex.message_bytes
     code = _DTYPE_CODE[tensor.dtype]
     ptr = tensor.data_ptr()
-    if ex.implementation == "device_one_shot":
+    if ex.implementation == "device_one_shot_ll":
+        again = _launch_ll(heap, "allreduce", OP_ALLREDUCE_ONE_SHOT, ptr, ptr, nbytes,
+                           dtype_code=code)
+    elif ex.implementation == "device_one_shot":
         # One staging area (two parities of the largest one-shot message) and one counter
         # block serve every message size: the parity halves sit at fixed offsets, so calls
         # of different sizes alternate between them just like calls of one size.

@@ -47,7 +47,7 @@ class RuntimeConfig:
     debug: bool = False                    # TILECCL_DEBUG: load the build with recorded bounds checks and check every collective call
     stream_run_shares: Optional[tuple] = None  # TILECCL_STREAM_SHARES: "0.85,0.15" - runs of a host-streamed operand
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
-    ll_max_bytes: int = 65536              # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency collectives (0 = off, at most 1 MiB)
+    ll_max_bytes: int = 1 << 20            # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency collectives (0 = off, at most 1 MiB)
     bcast_relay_min_bytes: int = 8 << 20   # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never)
     bcast_relay_pieces: int = 2048         # TILECCL_BCAST_RELAY_PIECES: pieces a relayed broadcast aims for (16 .. 4096)
     bcast_relay_ctas_per_sm: int = 2       # TILECCL_BCAST_RELAY_CTAS_PER_SM: CTAs per SM of the relay kernel (1 .. 4)
@@ -84,7 +84,7 @@ class RuntimeConfig:
             stream_run_shares=(tuple(float(x) for x in e["TILECCL_STREAM_SHARES"].split(","))
                                if e.get("TILECCL_STREAM_SHARES") else None),
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
-            ll_max_bytes=min(1 << 20, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or 65536))),
+            ll_max_bytes=min(1 << 20, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or (1 << 20)))),
             bcast_relay_min_bytes=max(0, int(e.get("TILECCL_BCAST_RELAY_MIN_BYTES") or (8 << 20))),
             bcast_relay_pieces=min(4096, max(16, int(e.get("TILECCL_BCAST_RELAY_PIECES") or 2048))),
             bcast_relay_ctas_per_sm=min(4, max(1, int(e.get("TILECCL_BCAST_RELAY_CTAS_PER_SM") or 2))),

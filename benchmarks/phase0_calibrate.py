@@ -14,7 +14,7 @@ The launch-level fit above includes kernel-launch latency and the collectives' t
 handshake, so it says little about a TileGroup inside the fused kernel.  The second mode
 fits the push phase *inside* the kernel from its %globaltimer trace and needs no GPU:
 
-    python benchmarks/phase0_calibrate.py --from-trace gpurun_out/trace_n2.log \
+    python benchmarks/phase0_calibrate.py --from-trace trace_n2.log \
         --out calibration/b200.json
 
 reads the JSON lines that ``benchmarks/trace_fused_gemm.py`` prints, regresses "first

@@ -173,9 +173,19 @@ def describe_runtime_support(ctx: Any = None) -> RuntimeSupportMatrix:
         SUPPORTED, "tile_allreduce / tile_allgather / tile_reduce_scatter / tile_broadcast / "
                    "tile_scatter are __device__ functions (csrc/device/tile_collectives.cuh); user "
                    "kernels are built and launched with tileccl_b200.userkernel")
-    collectives["collectives.low_latency_copies"] = SupportStatus(
-        coll.state, "all-gather / broadcast / scatter up to 64 KiB per peer travel as "
-                    "flag-in-data lines (csrc/device/tile_ll.cuh)")
+    collectives["collectives.low_latency"] = SupportStatus(
+        coll.state, "all five collectives travel as flag-in-data lines up to TILECCL_LL_MAX_BYTES "
+                    "(default 1 MiB) per peer (csrc/device/tile_ll.cuh)")
+    collectives["collectives.relay_broadcast"] = SupportStatus(
+        coll.state if ws >= 3 or not has_heap else PARTIAL,
+        "broadcasts from TILECCL_BCAST_RELAY_MIN_BYTES (default 8 MiB) on three or more ranks "
+        "are relayed piece by piece: the root sends every byte once")
+    from . import _build
+
+    collectives["debug.recorded_bounds_checks"] = SupportStatus(
+        SUPPORTED if _build.DEBUG_LIB_PATH.exists() else PARTIAL,
+        "TILECCL_DEBUG=1 loads libtileccl_b200_debug.so (python -m tileccl_b200._build --debug): "
+        "device-side bounds checks that record and skip, epoch invariants after every call")
     mem_ok = SupportStatus(SUPPORTED if has_heap else UNSUPPORTED,
                            f"cuMem VMM heap, mode {heap_mode}, transport {transport}" if has_heap
                            else "no heap attached")

@@ -97,8 +97,9 @@ def test_rooted_collectives_with_alternating_roots(ctxs):
         coll.check_status(c.heap)
 
 
+@pytest.mark.parametrize("bulk", ["1", "0"])
 @pytest.mark.parametrize("nbytes, threshold", [(2 << 20, 65536), ((12 << 20) + 4096 * 16, None)])
-def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, monkeypatch):
+def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, bulk, monkeypatch):
     """Three or more ranks, large message: the root sends every piece once and the other
     ranks forward theirs.  Roots alternate and sizes repeat, so flags and counters of
     several calls are exercised; a guard region after the buffer must stay untouched."""
@@ -110,6 +111,7 @@ def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, monkeypatch):
         pytest.skip("the relay needs three ranks")
     if threshold is not None:
         monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", str(threshold))
+    monkeypatch.setenv("TILECCL_BCAST_RELAY_BULK", bulk)     # bulk copies / register copies
     n = nbytes // 4
     bufs = [c.zeros(n, dtype=torch.float32) for c in ctxs]
     guards = [c.zeros(4096, dtype=torch.int32) for c in ctxs]

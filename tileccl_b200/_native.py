@@ -199,7 +199,7 @@ def _declare(lib: C.CDLL) -> None:
                                       C.c_int64, u64, u64, i32, u64, u64, u64],
         "tccl_p2p_copy": [i32, i32, i32, i32, u64, u64, u64, u64, u64, i32, u64],
         "tccl_broadcast_relay_launch": [i32, i32, i32, i32, u32, u64, u64, u64, u64, u64, u64,
-                                        C.c_int64, i32, u64, u64, u64],
+                                        C.c_int64, i32, i32, u64, u64, u64],
         "tccl_debug_read_primitives": [vp, i32],
         "tccl_debug_read_collectives": [vp, i32],
         "tccl_push_region": [u64, u64, C.c_int64, i32, i32, i32, i32, i32, C.c_int64, u64, u32, u64,

@@ -219,10 +219,12 @@ int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank, int32_t w
 // with a flag; each of those forwards its pieces to the other non-root ranks.  `flags`:
 // 4096 zeroed uint32 on the heap, `counters`: 32 zeroed uint32 on the heap, both per root.
 // phase_mask: 1 announce, 2 root push, 8 relay forwarding, 4 final wait (15 = whole call).
+// `bulk` != 0: bulk copies through shared memory, four pipelines per CTA (grid counts CTAs
+// of 128 threads); 0: register copies by CTAs of 512 threads.
 int tccl_broadcast_relay_launch(int32_t rank, int32_t world_size, int32_t root,
                                 int32_t phase_mask, uint32_t epoch, uint64_t buf, uint64_t bytes,
                                 uint64_t piece_bytes, uint64_t flags, uint64_t counters,
-                                uint64_t heap_base, int64_t heap_stride, int32_t grid,
+                                uint64_t heap_base, int64_t heap_stride, int32_t grid, int32_t bulk,
                                 uint64_t status, uint64_t budget_ns, uint64_t stream);
 
 // --------------------------------------------------------------------------

@@ -401,7 +401,10 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
     # CTAs per SM: while one waits for its stores to be acknowledged (the fence before a
     # flag) the others keep the link busy.
     own = n_pieces if heap.rank == root else -(-n_pieces // (heap.world_size - 1))
-    grid = max(1, min(_sm_count(heap.device) * cfg.bcast_relay_ctas_per_sm, own))
+    bulk = 1 if cfg.bcast_relay_bulk else 0
+    workers_per_cta = 4 if bulk else 1               # the bulk form runs four pipelines per CTA
+    grid = max(1, min(_sm_count(heap.device) * cfg.bcast_relay_ctas_per_sm,
+                      -(-own // workers_per_cta)))
     if not heap.emulated and heap.local_group is None:
         fn, rank, ws = st["fn"], heap.rank, heap.world_size
         flags_ptr, counters_ptr, status = st["flags_ptr"], st["counters_ptr"], st["status_ptr"]
@@ -411,7 +414,7 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
         def relaunch():
             st["epoch"] = e = st["epoch"] + 1
             rc = fn(rank, ws, root, 15, e & 0xFFFFFFFF, ptr, nbytes, piece, flags_ptr,
-                    counters_ptr, local_base, stride, grid, status, budget,
+                    counters_ptr, local_base, stride, grid, bulk, status, budget,
                     _stream_ptr(dev_index))
             if rc != 0:
                 _native.check("tccl_broadcast_relay_launch", rc)
@@ -430,7 +433,8 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
     def go(mask: int):
         rc = st["fn"](heap.rank, heap.world_size, root, mask, epoch & 0xFFFFFFFF, ptr, nbytes,
                       piece, st["flags_ptr"], st["counters_ptr"], heap.local_base, heap.stride,
-                      grid, st["status_ptr"], _budget_ns(), torch.cuda.current_stream().cuda_stream)
+                      grid, bulk, st["status_ptr"], _budget_ns(),
+                      torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             _native.check("tccl_broadcast_relay_launch", rc)
 

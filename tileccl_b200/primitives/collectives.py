@@ -12,7 +12,7 @@ all-gather      push own chunk into every rank's output (multimem.st if NVLS)
 reduce-scatter  pull own chunk from every rank and sum in fp32
                 (multimem.ld_reduce if NVLS); chunks up to 64 KiB: every rank
                 sends chunk d to rank d as flag-in-data lines, the owner sums
-all-reduce      small (up to 1 MiB at two ranks, 256 KiB at eight): one-shot over
+all-reduce      small (up to 1 MiB at two to four ranks, 512 KiB at eight): one-shot over
                 flag-in-data lines; <= 256 KiB otherwise: one-shot through a
                 double-buffered staging copy; larger: pull-reduce own chunk, push
                 it to every rank
@@ -298,7 +298,7 @@ def _ll_ok(heap, per_peer_bytes: int, *ptrs: int) -> bool:
             and all(p % 8 == 0 for p in ptrs))
 
 
-LL_ALLREDUCE_MAX_INGRESS = 2 << 20   # payload bytes a rank receives in a low-latency all-reduce
+LL_ALLREDUCE_MAX_INGRESS = 4 << 20   # payload bytes a rank receives in a low-latency all-reduce
 
 
 def _ll_allreduce_ok(heap, nbytes: int, ptr: int) -> bool:

@@ -324,7 +324,9 @@ def test_relay_broadcast_policy_and_piece_size(monkeypatch):
         piece = coll.relay_piece_bytes(nbytes)
         assert piece % 8192 == 0 and piece >= coll.RELAY_MIN_PIECE
         assert -(-nbytes // piece) <= coll.RELAY_MAX_PIECES
-    assert coll.relay_piece_bytes(256 << 20) == 128 << 10
+    assert coll.relay_piece_bytes(8 << 20) == 16 << 10          # about 1024 pieces, at least 16 KiB
+    assert coll.relay_piece_bytes(256 << 20) == 64 << 10        # capped at the largest piece
+    assert coll.relay_piece_bytes(3 << 30) == 192 << 10         # grows to stay within 16384 pieces
     heap3, heap2 = SimpleNamespace(world_size=3), SimpleNamespace(world_size=2)
     monkeypatch.delenv("TILECCL_BCAST_RELAY_MIN_BYTES", raising=False)
     assert coll._relay_ok(heap3, 8 << 20, 4096)

@@ -215,9 +215,9 @@ int tccl_collective_ll_launch(int32_t op, int32_t dtype, int32_t rank, int32_t w
                               uint64_t budget_ns, uint64_t stream);
 
 // Pipelined relay broadcast for large messages on 3..8 ranks: the root sends piece p of
-// `buf` (pieces of `piece_bytes`, at most 4096 of them) once, to the non-root ranks in turn,
+// `buf` (pieces of `piece_bytes`, at most 16384 of them) once, to the non-root ranks in turn,
 // with a flag; each of those forwards its pieces to the other non-root ranks.  `flags`:
-// 4096 zeroed uint32 on the heap, `counters`: 32 zeroed uint32 on the heap, both per root.
+// 16384 zeroed uint32 on the heap, `counters`: 32 zeroed uint32 on the heap, both per root.
 // phase_mask: 1 announce, 2 root push, 8 relay forwarding, 4 final wait (15 = whole call).
 // `bulk` != 0: bulk copies through shared memory, four pipelines per CTA (grid counts CTAs
 // of 128 threads); 0: register copies by CTAs of 512 threads.

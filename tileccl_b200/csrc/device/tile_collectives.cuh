@@ -447,7 +447,7 @@ __device__ __forceinline__ bool tile_coll_wait_done(const SymmWindow& w, const T
 // (epoch = 1, 2, 3 ... per call on this flag block; zero before first use).  Both functions
 // are CTA-collective; CTA `cta` of `n_ctas` takes every n_ctas-th piece.  `bytes` and
 // `piece_bytes` are multiples of 16.
-static constexpr uint32_t kTileRelayMaxPieces = 4096;
+static constexpr uint32_t kTileRelayMaxPieces = 16384;
 
 __device__ __forceinline__ int relay_rank_of(uint32_t piece, int root, int world_size) {
   const int k = static_cast<int>(piece % static_cast<uint32_t>(world_size - 1));

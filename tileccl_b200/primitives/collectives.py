@@ -363,16 +363,18 @@ def _launch_ll(heap, kind: str, op: int, src: int, dst: int, per_peer_bytes: int
     return None
 
 
-RELAY_MAX_PIECES = 4096
+RELAY_MAX_PIECES = 16384
 RELAY_MIN_PIECE = 16 * 1024
 
 
-def relay_piece_bytes(nbytes: int, target_pieces: int = 2048) -> int:
-    """Piece size of the relay broadcast: about ``target_pieces`` pieces per message (a piece
-    is the unit of pipelining: the relays start one piece time after the root, and every
-    piece costs one flag and one fence), at least 16 KiB, in multiples of 8 KiB (one 16-byte
-    access for each of a CTA's 512 threads)."""
-    piece = max(RELAY_MIN_PIECE, -(-nbytes // max(16, min(RELAY_MAX_PIECES, target_pieces))))
+def relay_piece_bytes(nbytes: int, max_piece: int = 64 * 1024) -> int:
+    """Piece size of the relay broadcast.  A piece is the unit of pipelining: a relay can
+    forward a piece only when all of it has arrived, so the relays start one piece time after
+    the root and finish one piece time after it; small pieces keep that short.  About 1024
+    pieces per message, between 16 KiB and ``max_piece``, in multiples of 8 KiB; larger only
+    where the piece count would exceed the flag block (16384)."""
+    piece = min(max(RELAY_MIN_PIECE, -(-nbytes // 1024)), max(RELAY_MIN_PIECE, max_piece))
+    piece = max(piece, -(-nbytes // RELAY_MAX_PIECES))
     return -(-piece // 8192) * 8192
 
 
@@ -395,14 +397,18 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
         st["flags_ptr"], st["counters_ptr"] = st["flags"].data_ptr(), st["counters"].data_ptr()
         heap._state[("coll_relay", kind)] = st
     cfg = _config()
-    piece = relay_piece_bytes(nbytes, cfg.bcast_relay_pieces)
+    piece = relay_piece_bytes(nbytes, cfg.bcast_relay_piece_kib * 1024)
     n_pieces = -(-nbytes // piece)
-    # the root's CTAs take pieces in turn; a relay owns every (ws - 1)-th piece.  Several
-    # CTAs per SM: while one waits for its stores to be acknowledged (the fence before a
-    # flag) the others keep the link busy.
+    # The root's workers take pieces in turn; a relay owns every (ws - 1)-th piece.  The root
+    # runs few workers: the link is shared by the pieces in flight, so with fewer of them each
+    # piece completes sooner and the relays idle less at the start and at the end (148
+    # pipelines with two 16 KiB slots each still keep well over the 2 MB in flight that the
+    # link needs).  A relay runs as many as it has pieces for.
     own = n_pieces if heap.rank == root else -(-n_pieces // (heap.world_size - 1))
     bulk = 1 if cfg.bcast_relay_bulk else 0
     workers_per_cta = 4 if bulk else 1               # the bulk form runs four pipelines per CTA
+    if heap.rank == root:
+        own = min(own, cfg.bcast_relay_root_workers)
     grid = max(1, min(_sm_count(heap.device) * cfg.bcast_relay_ctas_per_sm,
                       -(-own // workers_per_cta)))
     if not heap.emulated and heap.local_group is None:

@@ -49,7 +49,8 @@ class RuntimeConfig:
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
     ll_max_bytes: int = 1 << 20            # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency collectives (0 = off, at most 1 MiB)
     bcast_relay_min_bytes: int = 8 << 20   # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never)
-    bcast_relay_pieces: int = 2048         # TILECCL_BCAST_RELAY_PIECES: pieces a relayed broadcast aims for (16 .. 4096)
+    bcast_relay_piece_kib: int = 64        # TILECCL_BCAST_RELAY_PIECE_KIB: largest piece of a relayed broadcast (16 .. 1024 KiB; grows only to keep the piece count within 16384)
+    bcast_relay_root_workers: int = 148    # TILECCL_BCAST_RELAY_ROOT_WORKERS: copy pipelines the root runs (few, so that each piece completes soon and the relays start early)
     bcast_relay_ctas_per_sm: int = 1       # TILECCL_BCAST_RELAY_CTAS_PER_SM: CTAs per SM of the relay kernel (1 .. 4)
     bcast_relay_bulk: bool = True          # TILECCL_BCAST_RELAY_BULK: bulk copies through shared memory (0 = register copies)
     comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
@@ -87,7 +88,8 @@ class RuntimeConfig:
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
             ll_max_bytes=min(1 << 20, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or (1 << 20)))),
             bcast_relay_min_bytes=max(0, int(e.get("TILECCL_BCAST_RELAY_MIN_BYTES") or (8 << 20))),
-            bcast_relay_pieces=min(4096, max(16, int(e.get("TILECCL_BCAST_RELAY_PIECES") or 2048))),
+            bcast_relay_piece_kib=min(1024, max(16, int(e.get("TILECCL_BCAST_RELAY_PIECE_KIB") or 64))),
+            bcast_relay_root_workers=max(4, int(e.get("TILECCL_BCAST_RELAY_ROOT_WORKERS") or 148)),
             bcast_relay_ctas_per_sm=min(4, max(1, int(e.get("TILECCL_BCAST_RELAY_CTAS_PER_SM") or 1))),
             bcast_relay_bulk=_flag(e, "TILECCL_BCAST_RELAY_BULK", True),
             comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
@@ -119,7 +121,8 @@ ENV_NAMES = (
     "TILECCL_WAIT_BUDGET_US", "TILECCL_DISABLE_NVLS", "TILECCL_FORCE_NVLS", "TILECCL_CALIBRATION",
     "TILECCL_BOOTSTRAP_TIMEOUT_MS", "TILECCL_NATIVE_LIB", "TILECCL_NO_BUILD", "TILECCL_DEBUG",
     "TILECCL_STREAM_SHARES", "TILECCL_STREAM_COPY_STREAMS", "TILECCL_LL_MAX_BYTES",
-    "TILECCL_BCAST_RELAY_MIN_BYTES", "TILECCL_BCAST_RELAY_PIECES",
+    "TILECCL_BCAST_RELAY_MIN_BYTES", "TILECCL_BCAST_RELAY_PIECE_KIB",
+    "TILECCL_BCAST_RELAY_ROOT_WORKERS",
     "TILECCL_BCAST_RELAY_CTAS_PER_SM", "TILECCL_BCAST_RELAY_BULK", "TILECCL_COMM_SMS",
     "TileCCL_ENABLE_EXPERIMENTAL_MULTIPROCESS_DEVICE_COLLECTIVES",
     "TileCCL_FORCE_MULTIPROCESS_TRANSPORT",

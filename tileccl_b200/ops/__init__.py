@@ -726,7 +726,9 @@ def allreduce(tensor, *, ctx=None, op="sum", storage_kind="symmetric"):
     ctx = _ctx_or_current(ctx)
     if op == "sum" and _coll.try_fast(ctx.heap, "allreduce", tensor):
         return tensor
-    key = ("allreduce", tensor.data_ptr(), tensor.numel(), tensor.dtype, op, storage_kind)
+    # (the plan's execution spec depends on the configuration: part of the key)
+    key = ("allreduce", tensor.data_ptr(), tensor.numel(), tensor.dtype, op, storage_kind,
+           _coll._config_generation())
     return _cached_plan(ctx, key, lambda: build_allreduce_plan(
         tensor, ctx=ctx, op=op, storage_kind=storage_kind)).execute(tensor, validate=False)
 

@@ -418,3 +418,29 @@ def test_low_latency_staging_classes():
     assert coll.ll_slot_bytes(1 << 20) == 2 << 20
     for n in (8, 4096, 65536, 100_000, 1 << 20):
         assert coll.ll_slot_bytes(n) >= 2 * n
+
+
+def test_relay_piece_assignment_covers_every_piece_once():
+    """Mirror of the device-side assignment (relay_rank_of / the workers' strides in
+    csrc/device/tile_collectives.cuh and broadcast_relay_bulk_kernel): the root's workers and
+    each relay's workers visit disjoint pieces, and together every piece exactly once."""
+    def relay_rank_of(piece, root, ws):
+        k = piece % (ws - 1)
+        return k if k < root else k + 1
+
+    for ws, root, n_pieces, root_workers, relay_workers in ((3, 0, 17, 4, 5), (4, 2, 1024, 148, 592),
+                                                            (8, 7, 1000, 148, 592), (8, 3, 5, 148, 592)):
+        sent = []
+        for worker in range(root_workers):
+            sent += list(range(worker, n_pieces, root_workers))
+        assert sorted(sent) == list(range(n_pieces))
+        forwarded = []
+        for rank in range(ws):
+            if rank == root:
+                continue
+            mine = rank if rank < root else rank - 1
+            for worker in range(relay_workers):
+                for piece in range(worker * (ws - 1) + mine, n_pieces, relay_workers * (ws - 1)):
+                    assert relay_rank_of(piece, root, ws) == rank
+                    forwarded.append(piece)
+        assert sorted(forwarded) == list(range(n_pieces))

@@ -55,6 +55,7 @@ def main() -> int:
         ctx.barrier()
         ctx.heap.reset_allocator()
     if ws >= 3:                                             # relay broadcast, debug epilogue too
+        os.environ["TILECCL_BCAST_RELAY_MIN_BYTES"] = str(8 << 20)
         big = ctx.zeros((9 << 20) // 4, dtype=torch.float32)
         for root in (0, ws - 1):
             big.fill_(float(rank + 1))

@@ -190,6 +190,7 @@ def main() -> int:
     # large broadcast: pipelined relay from three ranks on (root sends every piece once, the
     # others forward theirs); sizes repeat and roots alternate so several epochs are covered
     if ws >= 3:
+        os.environ["TILECCL_BCAST_RELAY_MIN_BYTES"] = str(8 << 20)   # (default: from 64 MiB)
         big = ctx.zeros((12 << 20) // 4 + 4096, dtype=torch.float32)
         assert coll._relay_ok(ctx.heap, big.numel() * 4, big.data_ptr())
         for call, root in enumerate([0, ws - 1, 1, 0, 2]):
@@ -200,6 +201,7 @@ def main() -> int:
             check(f"relay broadcast call {call} root {root}", big, want, 1e-7)
         dist.barrier()
         coll.check_status(ctx.heap)
+        del os.environ["TILECCL_BCAST_RELAY_MIN_BYTES"]
 
     tokens, hidden, ffn = 128 * ws * 2, 512, 256 * ws
     mlp = TPMLP(ctx, tokens=tokens, hidden=hidden, ffn=ffn, dtype=torch.bfloat16, seed=3)

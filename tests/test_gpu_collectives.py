@@ -98,7 +98,7 @@ def test_rooted_collectives_with_alternating_roots(ctxs):
 
 
 @pytest.mark.parametrize("bulk", ["1", "0"])
-@pytest.mark.parametrize("nbytes, threshold", [(2 << 20, 65536), ((12 << 20) + 4096 * 16, None)])
+@pytest.mark.parametrize("nbytes, threshold", [(2 << 20, 65536), ((12 << 20) + 4096 * 16, 8 << 20)])
 def test_relay_broadcast_large_messages(ctxs, nbytes, threshold, bulk, monkeypatch):
     """Three or more ranks, large message: the root sends every piece once and the other
     ranks forward theirs.  Roots alternate and sizes repeat, so flags and counters of

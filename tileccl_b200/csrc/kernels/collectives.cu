@@ -234,11 +234,14 @@ __global__ void __launch_bounds__(512) broadcast_relay_kernel(const RelayParams 
 // register copies: each of a CTA's four warps is an independent pipeline driven by its
 // lane 0 (local memory -> 16 KiB slot -> peer).  A piece's flag is written when the bulk
 // groups of THAT pipeline have completed, so publishing a piece waits for one pipeline's
-// stores only; with plain stores every flag needs a system-scope fence, which on a loaded
-// link waits for everything the SM has in flight (measured: 110 us for 16 MiB at 4 ranks
-// against 24 us of wire time).  The flag is a relaxed system-scope store behind
-// cp.async.bulk.wait_group + fence.proxy.async, the same assumption as the fused GEMM's
-// TileGroup signal: a bulk group that has completed has been acknowledged by the peer.
+// stores only; with register copies by 512 threads every flag needs a system-scope fence
+// behind ALL of the CTA's stores, which on a loaded link waits for everything the SM has in
+// flight (measured: 110 us for 16 MiB at 4 ranks against 24 us of wire time).  The flag is a
+// RELEASE store at system scope behind cp.async.bulk.wait_group + fence.proxy.async: a
+// completed bulk group is only promised to be visible to the thread that waited for it, and
+// a relaxed flag was observed to overtake the data (512 MiB and 1 GiB broadcasts at 4 ranks
+// forwarded stale pieces); the release makes the thread's completed writes visible system
+// wide before the flag.
 static constexpr int kRelayWarps = 4;
 static constexpr int kRelaySlots = 2;
 static constexpr uint32_t kRelaySlotBytes = 16 * 1024;
@@ -330,9 +333,9 @@ __global__ void __launch_bounds__(kRelayWarps * 32) broadcast_relay_bulk_kernel(
           ++use;
         }
         if (is_root && ok) {
-          tma_store_wait_all<0>();       // this pipeline's stores of the piece have landed
+          tma_store_wait_all<0>();       // this pipeline's stores of the piece are complete
           fence_proxy_async_all();
-          st_relaxed_sys(coll_detail::peer_of(w, flags, relay_rank_of(piece, p.root, ws)) + piece,
+          st_release_sys(coll_detail::peer_of(w, flags, relay_rank_of(piece, p.root, ws)) + piece,
                          p.epoch);
         }
       }

@@ -30,6 +30,7 @@ def main() -> int:
     from tileccl_b200 import ops
     from tileccl_b200.primitives import collectives as coll
 
+    os.environ.setdefault("TILECCL_BCAST_RELAY_MIN_BYTES", str(8 << 20))   # the relay is opt-in
     ctx = tccl.init(heap_size=(max(args.mib) << 20) + (64 << 20))
     bad = torch.zeros(1, dtype=torch.int64, device=dev)
     for mib in args.mib:

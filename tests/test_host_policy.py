@@ -329,6 +329,8 @@ def test_relay_broadcast_policy_and_piece_size(monkeypatch):
     assert coll.relay_piece_bytes(3 << 30) == 192 << 10         # grows to stay within 16384 pieces
     heap3, heap2 = SimpleNamespace(world_size=3), SimpleNamespace(world_size=2)
     monkeypatch.delenv("TILECCL_BCAST_RELAY_MIN_BYTES", raising=False)
+    assert not coll._relay_ok(heap3, 1 << 30, 4096)             # opt-in: off by default
+    monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", str(64 << 20))
     assert coll._relay_ok(heap3, 64 << 20, 4096)
     assert not coll._relay_ok(heap3, (64 << 20) - 16, 4096)     # below the threshold
     assert not coll._relay_ok(heap2, 256 << 20, 4096)           # one relay only: nothing to gain

@@ -16,9 +16,10 @@ all-reduce      small (up to 1 MiB at two to four ranks, 512 KiB at eight): one-
                 flag-in-data lines; <= 256 KiB otherwise: one-shot through a
                 double-buffered staging copy; larger: pull-reduce own chunk, push
                 it to every rank
-broadcast       root pushes to everyone (multimem.st if NVLS); from 64 MiB on three or
-                more ranks: pipelined relay (root sends every byte once, to the other
-                ranks in turn, and each forwards its pieces to the rest)
+broadcast       root pushes to everyone (multimem.st if NVLS); opt-in
+                (TILECCL_BCAST_RELAY_MIN_BYTES) on three or more ranks: pipelined relay
+                (root sends every byte once, to the other ranks in turn, and each
+                forwards its pieces to the rest)
 scatter         root pushes chunk r to rank r
 =============== =========================================================
 """

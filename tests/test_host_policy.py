@@ -446,3 +446,25 @@ def test_relay_piece_assignment_covers_every_piece_once():
                     assert relay_rank_of(piece, root, ws) == rank
                     forwarded.append(piece)
         assert sorted(forwarded) == list(range(n_pieces))
+
+
+def test_nvls_policy_by_collective_and_size(monkeypatch):
+    from types import SimpleNamespace
+
+    from tileccl_b200.primitives import collectives as coll
+
+    for name in ("TILECCL_DISABLE_NVLS", "TILECCL_FORCE_NVLS"):
+        monkeypatch.delenv(name, raising=False)
+    h8 = SimpleNamespace(world_size=8, has_multicast=True)
+    h2 = SimpleNamespace(world_size=2, has_multicast=True)
+    assert not coll._use_multimem(h2, 1 << 20, "allgather")             # two ranks: plain stores
+    assert coll._use_multimem(h8, 1 << 20, "allgather")                  # 8 MiB in total
+    assert not coll._use_multimem(h8, 2 << 20, "allgather")              # 16 MiB in total
+    assert coll._use_multimem(h8, 8 << 20, "reduce_scatter")             # 64 MiB in total
+    assert not coll._use_multimem(h8, 16 << 20, "reduce_scatter")        # 128 MiB in total
+    assert coll._use_multimem(h8, 1 << 30)                               # all-reduce, broadcast
+    assert not coll._use_multimem(h8, 1000 * 16 + 8, "allgather")        # not a multiple of 16
+    monkeypatch.setenv("TILECCL_FORCE_NVLS", "1")
+    assert coll._use_multimem(h8, 16 << 20, "reduce_scatter") and coll._use_multimem(h2, 4096)
+    monkeypatch.setenv("TILECCL_DISABLE_NVLS", "1")
+    assert not coll._use_multimem(h8, 4096, "allgather")

@@ -173,11 +173,21 @@ def _grid_for(nbytes: int, device: torch.device) -> int:
     return max(1, min(_sm_count(device), -(-vecs // (_THREADS * 2))))
 
 
-def _use_multimem(heap, nbytes: int) -> bool:
+# Total message size from which the plain peer path replaces NVLS (bytes; measured at 8 ranks).
+# A multicast store or a switch-side reduction also moves the caller's own share through the
+# switch (1 / world_size of the traffic on the link for nothing), which costs more than the
+# saved instructions once a call is bandwidth-bound; the all-reduce keeps NVLS at every size
+# (one multimem.ld_reduce + one multimem.st per 16 bytes instead of 2 (n - 1) accesses).
+NVLS_MAX_TOTAL_BYTES = {"allgather": 16 << 20, "reduce_scatter": 128 << 20}
+
+
+def _use_multimem(heap, nbytes: int, kind: str = "") -> bool:
     """NVLS (multimem) path?  With two ranks a multicast store also loops the data back
     to the sender through the switch and measures slower than plain peer stores
-    (about 500 vs 700 GB/s), so the default is NVLS only from three ranks on;
-    ``TILECCL_FORCE_NVLS=1`` uses it whenever it is bound, ``TILECCL_DISABLE_NVLS=1`` never."""
+    (about 500 vs 700 GB/s), so the default is NVLS only from three ranks on, and for
+    all-gather / reduce-scatter only below ``NVLS_MAX_TOTAL_BYTES``;
+    ``TILECCL_FORCE_NVLS=1`` uses it whenever it is bound, ``TILECCL_DISABLE_NVLS=1`` never.
+    ``nbytes`` is the per-rank chunk for all-gather / reduce-scatter."""
     cfg = _config()
     if not heap.has_multicast or cfg.disable_nvls:
         return False
@@ -185,7 +195,10 @@ def _use_multimem(heap, nbytes: int) -> bool:
         return False
     if cfg.force_nvls:
         return True
-    return heap.world_size > 2
+    if heap.world_size <= 2:
+        return False
+    limit = NVLS_MAX_TOTAL_BYTES.get(kind)
+    return limit is None or nbytes * heap.world_size < limit
 
 
 def _validate(name: str, t: torch.Tensor, heap) -> None:
@@ -555,7 +568,7 @@ def allgather(tensor: torch.Tensor, output: torch.Tensor, heap=None, *, ctx=None
                            nbytes)
     else:
         again = _launch(heap, "allgather", OP_ALLGATHER, 3, tensor.data_ptr(), output.data_ptr(),
-                        nbytes, use_multimem=_use_multimem(heap, nbytes),
+                        nbytes, use_multimem=_use_multimem(heap, nbytes, "allgather"),
                         elem_size=tensor.element_size())
     _remember(heap, "allgather", tensor, output, 0, again)
     return output
@@ -587,7 +600,8 @@ def reduce_scatter(tensor: torch.Tensor, output: torch.Tensor, heap=None, op: st
     else:
         again = _launch(heap, "reduce_scatter", OP_REDUCE_SCATTER, _DTYPE_CODE[tensor.dtype],
                         tensor.data_ptr(), output.data_ptr(), nbytes,
-                        use_multimem=_use_multimem(heap, nbytes), elem_size=tensor.element_size())
+                        use_multimem=_use_multimem(heap, nbytes, "reduce_scatter"),
+                        elem_size=tensor.element_size())
     _remember(heap, "reduce_scatter", tensor, output, 0, again)
     return output
 

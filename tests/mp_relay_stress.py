@@ -20,7 +20,9 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--calls", type=int, default=24)
     ap.add_argument("--mib", type=int, nargs="+", default=[512, 96])
+    ap.add_argument("--bulk", type=int, default=0, help="1: the bulk-copy form of the relay")
     args = ap.parse_args()
+    os.environ["TILECCL_BCAST_RELAY_BULK"] = str(args.bulk)
     rank, ws = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)

@@ -56,14 +56,16 @@ def test_debug_mode_checks_every_collective_call(ws):
     assert out.returncode == 0 and "MP_DEBUG_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])
 
 
+@pytest.mark.parametrize("bulk", [0, 1])
 @pytest.mark.parametrize("ws", [4, 8])
-def test_large_relayed_broadcasts_are_checked_call_by_call(ws):
+def test_large_relayed_broadcasts_are_checked_call_by_call(ws, bulk):
     """512 MiB and 96 MiB broadcasts with alternating roots; every element of every call is
     compared on the device (a piece flag that overtakes its data would forward stale pieces)."""
     if not torch.cuda.is_available() or torch.cuda.device_count() < ws:
         pytest.skip(f"needs {ws} GPUs")
     worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "mp_relay_stress.py")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ws}",
-           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker]
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()), worker,
+           "--bulk", str(bulk)]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "MP_RELAY_OK" in out.stdout, (out.stdout[-3000:], out.stderr[-3000:])

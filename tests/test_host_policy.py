@@ -321,15 +321,17 @@ def test_relay_broadcast_policy_and_piece_size(monkeypatch):
     from tileccl_b200.primitives import collectives as coll
 
     for nbytes in (8 << 20, (8 << 20) + 16, 256 << 20, 1 << 30, 3 << 30):
-        piece = coll.relay_piece_bytes(nbytes)
-        assert piece % 8192 == 0 and piece >= coll.RELAY_MIN_PIECE
-        assert -(-nbytes // piece) <= coll.RELAY_MAX_PIECES
-    assert coll.relay_piece_bytes(8 << 20) == 16 << 10          # about 1024 pieces, at least 16 KiB
-    assert coll.relay_piece_bytes(256 << 20) == 64 << 10        # capped at the largest piece
-    assert coll.relay_piece_bytes(3 << 30) == 192 << 10         # grows to stay within 16384 pieces
+        for bulk in (False, True):
+            piece = coll.relay_piece_bytes(nbytes, bulk=bulk)
+            assert piece % 8192 == 0 and piece >= coll.RELAY_MIN_PIECE
+            assert -(-nbytes // piece) <= coll.RELAY_MAX_PIECES
+    assert coll.relay_piece_bytes(256 << 20) == 128 << 10               # about 2048 pieces
+    assert coll.relay_piece_bytes(8 << 20, bulk=True) == 16 << 10       # about 1024, at least 16 KiB
+    assert coll.relay_piece_bytes(256 << 20, bulk=True) == 64 << 10     # capped at the largest piece
+    assert coll.relay_piece_bytes(3 << 30, bulk=True) == 192 << 10      # stays within 16384 pieces
     heap3, heap2 = SimpleNamespace(world_size=3), SimpleNamespace(world_size=2)
     monkeypatch.delenv("TILECCL_BCAST_RELAY_MIN_BYTES", raising=False)
-    assert not coll._relay_ok(heap3, 1 << 30, 4096)             # opt-in: off by default
+    assert coll._relay_ok(heap3, 256 << 20, 4096) and not coll._relay_ok(heap3, 128 << 20, 4096)
     monkeypatch.setenv("TILECCL_BCAST_RELAY_MIN_BYTES", str(64 << 20))
     assert coll._relay_ok(heap3, 64 << 20, 4096)
     assert not coll._relay_ok(heap3, (64 << 20) - 16, 4096)     # below the threshold

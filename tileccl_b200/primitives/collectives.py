@@ -16,10 +16,9 @@ all-reduce      small (up to 1 MiB at two to four ranks, 512 KiB at eight): one-
                 flag-in-data lines; <= 256 KiB otherwise: one-shot through a
                 double-buffered staging copy; larger: pull-reduce own chunk, push
                 it to every rank
-broadcast       root pushes to everyone (multimem.st if NVLS); opt-in
-                (TILECCL_BCAST_RELAY_MIN_BYTES) on three or more ranks: pipelined relay
-                (root sends every byte once, to the other ranks in turn, and each
-                forwards its pieces to the rest)
+broadcast       root pushes to everyone (multimem.st if NVLS); from 256 MiB on three or
+                more ranks: pipelined relay (root sends every byte once, to the other
+                ranks in turn, and each forwards its pieces to the rest)
 scatter         root pushes chunk r to rank r
 =============== =========================================================
 """
@@ -381,14 +380,19 @@ RELAY_MAX_PIECES = 16384
 RELAY_MIN_PIECE = 16 * 1024
 
 
-def relay_piece_bytes(nbytes: int, max_piece: int = 64 * 1024) -> int:
+def relay_piece_bytes(nbytes: int, max_piece: int = 64 * 1024, bulk: bool = False) -> int:
     """Piece size of the relay broadcast.  A piece is the unit of pipelining: a relay can
     forward a piece only when all of it has arrived, so the relays start one piece time after
-    the root and finish one piece time after it; small pieces keep that short.  About 1024
-    pieces per message, between 16 KiB and ``max_piece``, in multiples of 8 KiB; larger only
-    where the piece count would exceed the flag block (16384)."""
-    piece = min(max(RELAY_MIN_PIECE, -(-nbytes // 1024)), max(RELAY_MIN_PIECE, max_piece))
-    piece = max(piece, -(-nbytes // RELAY_MAX_PIECES))
+    the root and finish one piece time after it.  Every piece also costs its sender a
+    system-scope fence.  Register-copy form (the default): about 2048 pieces per message, at
+    least 16 KiB each (a CTA-wide fence per piece wants few, large pieces).  Bulk-copy form:
+    about 1024 pieces between 16 KiB and ``max_piece`` (a fence per pipeline), larger only
+    where the piece count would exceed the flag block (16384).  Multiples of 8 KiB."""
+    if bulk:
+        piece = min(max(RELAY_MIN_PIECE, -(-nbytes // 1024)), max(RELAY_MIN_PIECE, max_piece))
+        piece = max(piece, -(-nbytes // RELAY_MAX_PIECES))
+    else:
+        piece = max(RELAY_MIN_PIECE, -(-nbytes // 2048))
     return -(-piece // 8192) * 8192
 
 
@@ -411,7 +415,7 @@ def _launch_relay(heap, root: int, ptr: int, nbytes: int):
         st["flags_ptr"], st["counters_ptr"] = st["flags"].data_ptr(), st["counters"].data_ptr()
         heap._state[("coll_relay", kind)] = st
     cfg = _config()
-    piece = relay_piece_bytes(nbytes, cfg.bcast_relay_piece_kib * 1024)
+    piece = relay_piece_bytes(nbytes, cfg.bcast_relay_piece_kib * 1024, cfg.bcast_relay_bulk)
     n_pieces = -(-nbytes // piece)
     # The root's workers take pieces in turn; a relay owns every (ws - 1)-th piece.  The root
     # runs few workers: the link is shared by the pieces in flight, so with fewer of them each

@@ -178,9 +178,8 @@ def describe_runtime_support(ctx: Any = None) -> RuntimeSupportMatrix:
                     "(default 1 MiB) per peer (csrc/device/tile_ll.cuh)")
     collectives["collectives.relay_broadcast"] = SupportStatus(
         coll.state if ws >= 3 or not has_heap else PARTIAL,
-        "opt-in: broadcasts from TILECCL_BCAST_RELAY_MIN_BYTES on three or more ranks are relayed "
-        "piece by piece, the root sends every byte once (off by default: with release flags it "
-        "measured slower than multimem.st)")
+        "broadcasts from TILECCL_BCAST_RELAY_MIN_BYTES (default 256 MiB) on three or more ranks are "
+        "relayed piece by piece: the root sends every byte once")
     from . import _build
 
     collectives["debug.recorded_bounds_checks"] = SupportStatus(

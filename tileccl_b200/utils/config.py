@@ -48,11 +48,11 @@ class RuntimeConfig:
     stream_run_shares: Optional[tuple] = None  # TILECCL_STREAM_SHARES: "0.85,0.15" - runs of a host-streamed operand
     stream_copy_streams: int = 1           # TILECCL_STREAM_COPY_STREAMS: copy streams of a host-streamed operand (1 | 2)
     ll_max_bytes: int = 1 << 20            # TILECCL_LL_MAX_BYTES: largest per-peer message of the low-latency collectives (0 = off, at most 1 MiB)
-    bcast_relay_min_bytes: int = 0         # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never, the default: with release flags it measured slower than multimem.st)
+    bcast_relay_min_bytes: int = 256 << 20  # TILECCL_BCAST_RELAY_MIN_BYTES: from this size a broadcast on >= 3 ranks is relayed piece by piece (0 = never)
     bcast_relay_piece_kib: int = 64        # TILECCL_BCAST_RELAY_PIECE_KIB: largest piece of a relayed broadcast (16 .. 1024 KiB; grows only to keep the piece count within 16384)
     bcast_relay_root_workers: int = 148    # TILECCL_BCAST_RELAY_ROOT_WORKERS: copy pipelines the root runs (few, so that each piece completes soon and the relays start early)
     bcast_relay_ctas_per_sm: int = 1       # TILECCL_BCAST_RELAY_CTAS_PER_SM: CTAs per SM of the relay kernel (1 .. 4)
-    bcast_relay_bulk: bool = True          # TILECCL_BCAST_RELAY_BULK: bulk copies through shared memory (0 = register copies)
+    bcast_relay_bulk: bool = False         # TILECCL_BCAST_RELAY_BULK: 1 = bulk copies through shared memory instead of register copies (measured slower once its flags are release stores)
     comm_sms: Optional[int] = None         # TILECCL_COMM_SMS: SMs of a fused launch that only communicate (None = policy)
     push_mode_explicit: bool = False       # TILECCL_PUSH_MODE was set (it then overrides a pattern's own choice)
     # feature gates kept from the reference
@@ -87,11 +87,11 @@ class RuntimeConfig:
                                if e.get("TILECCL_STREAM_SHARES") else None),
             stream_copy_streams=2 if (e.get("TILECCL_STREAM_COPY_STREAMS") or "1") == "2" else 1,
             ll_max_bytes=min(1 << 20, max(0, int(e.get("TILECCL_LL_MAX_BYTES") or (1 << 20)))),
-            bcast_relay_min_bytes=max(0, int(e.get("TILECCL_BCAST_RELAY_MIN_BYTES") or 0)),
+            bcast_relay_min_bytes=max(0, int(e["TILECCL_BCAST_RELAY_MIN_BYTES"]) if e.get("TILECCL_BCAST_RELAY_MIN_BYTES") not in (None, "") else (256 << 20)),
             bcast_relay_piece_kib=min(1024, max(16, int(e.get("TILECCL_BCAST_RELAY_PIECE_KIB") or 64))),
             bcast_relay_root_workers=max(4, int(e.get("TILECCL_BCAST_RELAY_ROOT_WORKERS") or 148)),
             bcast_relay_ctas_per_sm=min(4, max(1, int(e.get("TILECCL_BCAST_RELAY_CTAS_PER_SM") or 1))),
-            bcast_relay_bulk=_flag(e, "TILECCL_BCAST_RELAY_BULK", True),
+            bcast_relay_bulk=_flag(e, "TILECCL_BCAST_RELAY_BULK", False),
             comm_sms=_opt_int(e, "TILECCL_COMM_SMS"),
             push_mode_explicit=bool(e.get("TILECCL_PUSH_MODE")),
             experimental_multiprocess_device_collectives=(
